@@ -1,0 +1,346 @@
+"""
+Headline benchmark: d26 pretraining throughput (tokens/sec over the whole job) on N B200s.
+
+  python bench.py --gpus 1 --steps 3 --warmup 3
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+         --master-port P bench.py --gpus N --steps K --warmup W
+  python bench.py --impl reference ...     # the unmodified reference from baseline/_ref
+
+One "step" is a full optimizer step at the reference's d26 configuration: total batch
+1,048,576 tokens = grad-accum x (device batch x 2048) x N, forward + backward for every
+micro-batch, then MuonAdamW.step() (gradient averaging + Muon/AdamW updates) and gradient
+reset. The total batch is fixed, so per-GPU work shrinks as N grows ("strong" scaling).
+
+Two timed regions, both bracketed by barrier + cuda synchronize, CUDA events, max over ranks:
+  value  - inputs already on the device (kernel-side throughput);
+  e2e    - through the public API with, every micro-step, the host->device copy of that
+           micro-batch from pinned memory, and every step a device->host read of the loss.
+Data are uniform-random token ids, weights random-init (no network on the box).
+"""
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+PUBLISHED_TOK_PER_SEC = 764000.0   # reference d26 fp8, batch 1,048,576, 8xH100 (dev/LEADERBOARD.md run 3)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
+    ap.add_argument("--depth", type=int, default=26)
+    ap.add_argument("--seq-len", type=int, default=2048)
+    ap.add_argument("--device-batch-size", type=int, default=16)
+    ap.add_argument("--total-batch-size", type=int, default=1048576)
+    ap.add_argument("--window-pattern", type=str, default="SSSL")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end region (debugging)")
+    ap.add_argument("--ref-bf16", action="store_true", help="reference arm without --fp8")
+    ap.add_argument("--ref-eager", action="store_true", help="reference arm without torch.compile")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons of this rank's GPU with nvidia-smi during a timed region."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.rows = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-i", str(self.gpu_index), "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._pump, daemon=True)
+        self.thread.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for row in self.rows:
+            parts = [p.strip() for p in row.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def timed_region(torch, dist, world, steps, run_step):
+    """Times `steps` calls of run_step() on the device; returns the max over ranks in milliseconds."""
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        run_step()
+    t1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = torch.tensor([t0.elapsed_time(t1)], device="cuda", dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return ms.item()
+
+
+def build_ours(args, device):
+    import torch
+    from nanochat_b200.models.gpt import GPT, GPTConfig
+    dim = -(-args.depth * 64 // 128) * 128
+    cfg = GPTConfig(sequence_len=args.seq_len, vocab_size=32768, n_layer=args.depth, n_head=dim // 128,
+                    n_kv_head=dim // 128, n_embd=dim, window_pattern=args.window_pattern)
+    with torch.device("meta"):
+        model = GPT(cfg)
+    model.to_empty(device=device)
+    model.init_weights()
+    return model, cfg
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from nanochat_b200 import common, ops
+    rank, local_rank, world = dist_env()
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    _, _, _, _, device = common.compute_init("cuda")
+    assert common.COMPUTE_DTYPE == torch.bfloat16
+    model, cfg = build_ours(args, device)
+    from nanochat_b200.train import TrainStep
+    B, T = args.device_batch_size, args.seq_len
+    assert args.total_batch_size % (B * T * world) == 0
+    accum = args.total_batch_size // (B * T * world)
+    trainer = TrainStep(model, grad_accum=accum, matrix_lr=0.02, weight_decay=0.1)
+    flops_per_token = model.estimate_flops()
+
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    n_buf = min(accum, 8)
+    host = [torch.randint(0, cfg.vocab_size, (2, B, T), generator=gen, dtype=torch.long).pin_memory()
+            for _ in range(n_buf)]
+    dev = [h.to(device) for h in host]
+    staging = [torch.empty_like(dev[0]) for _ in range(2)]
+
+    def step_device():
+        trainer.step(lambda i: (dev[i % n_buf][0], dev[i % n_buf][1]))
+
+    last_loss = [None]
+
+    def step_e2e():
+        def fetch(i):
+            buf = staging[i % 2]
+            buf.copy_(host[i % n_buf], non_blocking=True)   # H2D from pinned memory, every micro-step
+            return buf[0], buf[1]
+        loss = trainer.step(fetch)
+        last_loss[0] = loss.item()                           # D2H read of the step's loss
+
+    for _ in range(args.warmup):
+        step_device()
+    nat = ops.native_module()
+    nat.check_status()
+    launches0 = nat.launch_count()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = timed_region(torch, dist, world, args.steps, step_device)
+    clocks = sampler.stop()
+    launches = nat.launch_count() - launches0
+    nat.check_status()
+
+    e2e = None
+    if not args.no_e2e:
+        step_e2e()
+        e2e_ms = timed_region(torch, dist, world, args.steps, step_e2e)
+        e2e = {"value": args.total_batch_size * args.steps / (e2e_ms / 1e3), "unit": "tokens/s",
+               "ms_per_step": e2e_ms / args.steps,
+               "h2d_bytes_per_step": accum * 2 * B * T * 8, "d2h_bytes_per_step": 4,
+               "last_loss": last_loss[0]}
+    tok_s = args.total_batch_size * args.steps / (ms / 1e3)
+    peak_mem = torch.cuda.max_memory_allocated() / 2**30
+    out = {
+        "metric": "d26 pretrain tokens/sec (whole job)", "value": tok_s, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": tok_s / PUBLISHED_TOK_PER_SEC, "dtype": "bf16", "data": "synthetic",
+        "impl": "ours",
+        "config": {"model": f"d{args.depth}", "global_batch": args.total_batch_size, "seq_len": T,
+                   "device_batch": B, "grad_accum": accum, "window_pattern": args.window_pattern,
+                   "parallelism": f"dp{world}", "optimizer": "MuonAdamW (ZeRO-2 sharded)",
+                   "l2": "inputs larger than L2 (activations of one micro-batch exceed 126 MB)",
+                   "attention": nat.ATTENTION_IMPL},
+        "mfu_bf16_nominal": flops_per_token * tok_s / (world * 2.25e15),
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "peak_mem_gib": peak_mem,
+    }
+    if rank == 0:
+        print(json.dumps(out))
+    common.compute_cleanup()
+
+
+def run_reference(args):
+    """The unmodified reference (baseline/_ref) through its own GPT / fp8 / MuonAdamW / torch.compile."""
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "nanochat")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/nanochat not present on this box"}))
+        return
+    sys.path.insert(0, ref_root)
+    os.environ.setdefault("PYTORCH_ALLOC_CONF", "expandable_segments:True")
+    try:
+        import torch
+        import torch.distributed as dist
+        import torch.nn as nn
+        from nanochat.common import compute_init, compute_cleanup, COMPUTE_DTYPE
+        from nanochat.gpt import GPT, GPTConfig
+    except Exception as e:  # dependency missing on this box
+        print(json.dumps({"impl": "reference", "unavailable": f"import failed: {type(e).__name__}: {e}"}))
+        return
+    rank, local_rank, world = dist_env()
+    _, _, _, _, device = compute_init("cuda")
+    dim = -(-args.depth * 64 // 128) * 128
+    cfg = GPTConfig(sequence_len=args.seq_len, vocab_size=32768, n_layer=args.depth, n_head=dim // 128,
+                    n_kv_head=dim // 128, n_embd=dim, window_pattern=args.window_pattern)
+    with torch.device("meta"):
+        model = GPT(cfg)
+    model.to_empty(device=device)
+    model.init_weights()
+    dtype = "bf16"
+    if not args.ref_bf16:
+        from nanochat.fp8 import Float8LinearConfig, convert_to_float8_training
+
+        def fp8_filter(mod, fqn):   # the filter of the reference's training script
+            if not isinstance(mod, nn.Linear):
+                return False
+            if mod.in_features % 16 != 0 or mod.out_features % 16 != 0:
+                return False
+            return min(mod.in_features, mod.out_features) >= 128
+        convert_to_float8_training(model, config=Float8LinearConfig.from_recipe_name("tensorwise"),
+                                   module_filter_fn=fp8_filter)
+        dtype = "fp8 (tensorwise e4m3/e5m2 linears, bf16 elsewhere)"
+    orig_model = model
+    compiled = not args.ref_eager
+    if compiled:
+        model = torch.compile(model, dynamic=False)
+    optimizer = orig_model.setup_optimizer(weight_decay=0.1)
+    B, T = args.device_batch_size, args.seq_len
+    accum = args.total_batch_size // (B * T * world)
+    gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
+    n_buf = min(accum, 8)
+    host = [torch.randint(0, cfg.vocab_size, (2, B, T), generator=gen, dtype=torch.long).pin_memory()
+            for _ in range(n_buf)]
+    dev = [h.to(device) for h in host]
+    staging = [torch.empty_like(dev[0]) for _ in range(2)]
+
+    def train_step(fetch):
+        for i in range(accum):
+            x, y = fetch(i)
+            loss = model(x, y)
+            (loss / accum).backward()
+        optimizer.step()
+        model.zero_grad(set_to_none=True)
+        return loss.detach()
+
+    def step_device():
+        train_step(lambda i: (dev[i % n_buf][0], dev[i % n_buf][1]))
+
+    last_loss = [None]
+
+    def step_e2e():
+        def fetch(i):
+            buf = staging[i % 2]
+            buf.copy_(host[i % n_buf], non_blocking=True)
+            return buf[0], buf[1]
+        last_loss[0] = train_step(fetch).item()
+
+    try:
+        for _ in range(args.warmup):
+            step_device()
+    except Exception as e:
+        if not compiled:
+            raise
+        # Inductor unavailable on this box: fall back to the reference's eager path and say so
+        print(f"[bench] torch.compile failed ({type(e).__name__}); running the reference eagerly", file=sys.stderr)
+        os.environ["TORCHDYNAMO_DISABLE"] = "1"
+        import torch._dynamo
+        torch._dynamo.reset()
+        torch._dynamo.config.disable = True
+        model = orig_model
+        compiled = False
+        model.zero_grad(set_to_none=True)
+        for _ in range(args.warmup):
+            step_device()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms = timed_region(torch, dist, world, args.steps, step_device)
+    clocks = sampler.stop()
+    e2e = None
+    if not args.no_e2e:
+        step_e2e()
+        e2e_ms = timed_region(torch, dist, world, args.steps, step_e2e)
+        e2e = {"value": args.total_batch_size * args.steps / (e2e_ms / 1e3), "unit": "tokens/s",
+               "ms_per_step": e2e_ms / args.steps, "h2d_bytes_per_step": accum * 2 * B * T * 8,
+               "d2h_bytes_per_step": 4, "last_loss": last_loss[0]}
+    tok_s = args.total_batch_size * args.steps / (ms / 1e3)
+    out = {
+        "metric": "d26 pretrain tokens/sec (whole job)", "value": tok_s, "unit": "tokens/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": tok_s / PUBLISHED_TOK_PER_SEC, "dtype": dtype, "data": "synthetic",
+        "impl": "reference",
+        "config": {"model": f"d{args.depth}", "global_batch": args.total_batch_size, "seq_len": T,
+                   "device_batch": B, "grad_accum": accum, "window_pattern": args.window_pattern,
+                   "parallelism": f"dp{world}", "torch_compile": compiled,
+                   "l2": "inputs larger than L2 (activations of one micro-batch exceed 126 MB)"},
+        "mfu_bf16_nominal": orig_model.estimate_flops() * tok_s / (world * 2.25e15),
+        "clocks": clocks, "e2e": e2e, "peak_mem_gib": torch.cuda.max_memory_allocated() / 2**30,
+    }
+    if rank == 0:
+        print(json.dumps(out))
+    compute_cleanup()
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        if ROOT not in sys.path:
+            sys.path.insert(0, ROOT)
+        run_ours(a)

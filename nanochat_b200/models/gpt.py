@@ -340,6 +340,9 @@ class GPT(nn.Module):
         T0 = 0 if kv_cache is None else kv_cache.get_pos()
         cos_sin = self.cos[:, T0:T0 + T], self.sin[:, T0:T0 + T]
 
+        if kv_cache is None and common.COMPUTE_DTYPE == torch.bfloat16 and ops.use_native(self.transformer.wte.weight):
+            return self._forward_native(idx, targets, cos_sin, loss_reduction)
+
         x = self._embed(idx, kv_cache)
         x0 = x
         backout_layer = self.config.n_layer // 2
@@ -359,6 +362,27 @@ class GPT(nn.Module):
                 loss = loss.view(-1)
             return loss
         return ops.softcap_logits(x, self.lm_head.weight, self.config.vocab_size)
+
+    def _forward_native(self, idx, targets, cos_sin, loss_reduction):
+        """Whole-sequence forward on the sm_100a kernels: one fused autograd node per layer."""
+        nat = ops.native_module()
+        assert idx.size(1) > 1, "Training forward pass should have T > 1"
+        x, _ = nat.embed_norm_smear(idx, self.transformer.wte.weight, self.smear_gate.weight, self.smear_lambda)
+        x0 = x
+        backout_layer = self.config.n_layer // 2
+        x_backout = None
+        for i, block in enumerate(self.transformer.h):
+            ve_w = self.value_embeds[str(i)].weight if str(i) in self.value_embeds else None
+            x = nat.layer_forward(block, x, x0, idx, ve_w, cos_sin, self.window_sizes[i],
+                                  self.resid_lambdas, self.x0_lambdas, i)
+            if i == backout_layer:
+                x_backout = x
+        if targets is not None:
+            loss = nat.head_loss(x, x_backout, self.backout_lambda, self.lm_head.weight, targets,
+                                 self.config.vocab_size, loss_reduction)
+            return loss.view(-1) if loss_reduction == "none" else loss
+        x = ops.backout_norm(x, x_backout, self.backout_lambda)
+        return nat.softcap_logits(x, self.lm_head.weight, self.config.vocab_size)
 
     @torch.inference_mode()
     def generate(self, tokens, max_tokens, temperature=1.0, top_k=None, seed=42):

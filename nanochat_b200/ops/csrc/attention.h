@@ -1,0 +1,23 @@
+// Host interface of the sm_100a flash-attention kernels (attention.cu).
+#pragma once
+
+#include <cuda_runtime.h>
+
+namespace nc {
+
+// q: (B, Tq, H, D), k/v: (B, Tk, Hkv, D), o like q; strides in elements (innermost dim contiguous, D = 128).
+// Causal with queries aligned to the END of the keys; `window` = number of keys to the left a query may
+// see in addition to itself (< 0 = unlimited). lse: (B, H, Tq) fp32, natural-log sum-exp of scaled scores.
+struct AttnDesc {
+  const void *q, *k, *v;
+  void* o;
+  float* lse;
+  long long q_bat, q_tok, q_head, k_bat, k_tok, k_head, v_bat, v_tok, v_head, o_bat, o_tok, o_head;
+  int B, Tq, Tk, H, Hkv, D;
+  int window;
+  float scale;
+};
+
+cudaError_t attention_fwd(const AttnDesc& d, int* status, cudaStream_t stream);
+
+}  // namespace nc

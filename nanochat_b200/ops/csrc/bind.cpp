@@ -1,0 +1,275 @@
+// Python bindings: unpack torch tensors into raw pointers / strides and call the launchers.
+// No math happens here and nothing is allocated except the one status word.
+#include <torch/extension.h>
+#include <atomic>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+
+#include "attention.h"
+#include "fused.h"
+#include "gemm.h"
+#include "optim.h"
+
+namespace {
+
+using at::Tensor;
+using c10::optional;
+
+static std::atomic<long long> g_launches{0};   // kernels of this extension launched so far
+
+#define NC_CHECK(expr)                                                                         \
+  do {                                                                                         \
+    ++g_launches;                                                                              \
+    cudaError_t _e = (expr);                                                                   \
+    TORCH_CHECK(_e == cudaSuccess, "nanochat_b200 kernel launch failed: ", cudaGetErrorString(_e), \
+                " at " #expr);                                                                 \
+  } while (0)
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+Tensor& status_tensor(const at::Device& dev) {
+  static std::vector<Tensor> per_dev(64);
+  Tensor& t = per_dev[dev.index()];
+  if (!t.defined()) t = torch::zeros({4}, torch::dtype(torch::kInt32).device(dev));
+  return t;
+}
+int* status_ptr(const Tensor& like) { return status_tensor(like.device()).data_ptr<int>(); }
+
+void check_bf16(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16, name, " must be a CUDA bf16 tensor");
+}
+const void* optptr(const optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+
+// ------------------------------------------------------------------------------ GEMM
+void gemm(const Tensor& A, const Tensor& B, Tensor& C, const optional<Tensor>& aux, bool a_mn, bool b_mn,
+          double alpha, double beta, int64_t epi, int64_t bn) {
+  check_bf16(A, "A");
+  check_bf16(B, "B");
+  TORCH_CHECK(C.is_cuda() && (C.scalar_type() == at::kBFloat16 || C.scalar_type() == at::kFloat), "C dtype");
+  TORCH_CHECK(A.dim() == B.dim() && A.dim() == C.dim() && (A.dim() == 2 || A.dim() == 3), "gemm rank");
+  const c10::cuda::CUDAGuard guard(A.device());
+  const int nd = A.dim();
+  auto chk = [&](const Tensor& t, const char* n) {
+    TORCH_CHECK(t.stride(nd - 1) == 1, n, ": innermost dim must be contiguous");
+  };
+  chk(A, "A"); chk(B, "B"); chk(C, "C");
+  nc::GemmDesc d{};
+  d.batch = nd == 3 ? (int)C.size(0) : 1;
+  d.M = (int)C.size(nd - 2);
+  d.N = (int)C.size(nd - 1);
+  d.K = (int)(a_mn ? A.size(nd - 2) : A.size(nd - 1));
+  TORCH_CHECK((a_mn ? A.size(nd - 1) : A.size(nd - 2)) == d.M, "A shape does not match C");
+  TORCH_CHECK((b_mn ? B.size(nd - 1) : B.size(nd - 2)) == d.N, "B shape does not match C");
+  TORCH_CHECK((b_mn ? B.size(nd - 2) : B.size(nd - 1)) == d.K, "A/B reduction dims differ");
+  d.A = A.data_ptr(); d.a_mn = a_mn; d.lda = A.stride(nd - 2); d.bsa = nd == 3 ? A.stride(0) : 0;
+  d.B = B.data_ptr(); d.b_mn = b_mn; d.ldb = B.stride(nd - 2); d.bsb = nd == 3 ? B.stride(0) : 0;
+  d.C = C.data_ptr(); d.c_f32 = C.scalar_type() == at::kFloat; d.ldc = C.stride(nd - 2);
+  d.bsc = nd == 3 ? C.stride(0) : 0;
+  if (aux.has_value() && aux->defined()) {
+    TORCH_CHECK(aux->scalar_type() == C.scalar_type() && aux->stride(nd - 1) == 1, "aux must match C");
+    d.aux = aux->data_ptr(); d.ldaux = aux->stride(nd - 2); d.bsaux = nd == 3 ? aux->stride(0) : 0;
+  }
+  d.alpha = (float)alpha; d.beta = (float)beta; d.epi = (int)epi; d.bn = (int)bn;
+  NC_CHECK(nc::gemm_bf16(d, status_ptr(A), cur_stream()));
+}
+
+int64_t gemm_pick_bn(int64_t M, int64_t N, int64_t batch) { return nc::gemm_pick_bn((int)M, (int)N, (int)batch); }
+
+std::vector<int64_t> read_status(const Tensor& like) {
+  Tensor h = status_tensor(like.device()).cpu();
+  status_tensor(like.device()).zero_();
+  auto a = h.accessor<int, 1>();
+  return {a[0], a[1], a[2], a[3]};
+}
+
+// --------------------------------------------------------------------- layer kernels
+void mixnorm_fwd(const Tensor& x, const Tensor& x0, const Tensor& lam_r, const Tensor& lam_0, int64_t layer,
+                 Tensor& xm, Tensor& xn) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int C = (int)x.size(-1), M = (int)(x.numel() / C);
+  NC_CHECK(nc::mixnorm_fwd(x.data_ptr(), x0.data_ptr(), lam_r.data_ptr<float>(), lam_0.data_ptr<float>(), (int)layer,
+                           xm.data_ptr(), xn.data_ptr(), M, C, cur_stream()));
+}
+void norm_fwd(const Tensor& x, Tensor& y) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int C = (int)x.size(-1), M = (int)(x.numel() / C);
+  NC_CHECK(nc::norm_fwd(x.data_ptr(), y.data_ptr(), M, C, cur_stream()));
+}
+void normadd_bwd(const Tensor& dy, const Tensor& x, const optional<Tensor>& dres, Tensor& dx) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int C = (int)x.size(-1), M = (int)(x.numel() / C);
+  NC_CHECK(nc::normadd_bwd(dy.data_ptr(), x.data_ptr(), optptr(dres), dx.data_ptr(), M, C, cur_stream()));
+}
+void mixnorm_bwd(const Tensor& dxn, const Tensor& dres, const optional<Tensor>& dgate, const Tensor& xm,
+                 const Tensor& x, const Tensor& x0, const Tensor& lam_r, const Tensor& lam_0, int64_t layer,
+                 Tensor& dx, Tensor& dx0, bool accumulate_dx0, Tensor& dlam_r, Tensor& dlam_0) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int C = (int)x.size(-1), M = (int)(x.numel() / C);
+  NC_CHECK(nc::mixnorm_bwd(dxn.data_ptr(), dres.data_ptr(), (const float*)optptr(dgate), xm.data_ptr(), x.data_ptr(),
+                           x0.data_ptr(), lam_r.data_ptr<float>(), lam_0.data_ptr<float>(), (int)layer, dx.data_ptr(),
+                           dx0.data_ptr(), accumulate_dx0, dlam_r.data_ptr<float>(), dlam_0.data_ptr<float>(), M, C,
+                           cur_stream()));
+}
+void backout_norm_fwd(const Tensor& x, const optional<Tensor>& xb, const Tensor& lam, Tensor& y) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int C = (int)x.size(-1), M = (int)(x.numel() / C);
+  NC_CHECK(nc::backout_norm_fwd(x.data_ptr(), optptr(xb), lam.data_ptr<float>(), y.data_ptr(), M, C, cur_stream()));
+}
+void backout_norm_bwd(const Tensor& dy, const Tensor& x, const optional<Tensor>& xb, const Tensor& lam, Tensor& dx,
+                      const optional<Tensor>& dxb, Tensor& dlam) {
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int C = (int)x.size(-1), M = (int)(x.numel() / C);
+  NC_CHECK(nc::backout_norm_bwd(dy.data_ptr(), x.data_ptr(), optptr(xb), lam.data_ptr<float>(), dx.data_ptr(),
+                                const_cast<void*>(optptr(dxb)), dlam.data_ptr<float>(), M, C, cur_stream()));
+}
+void qkv_post_fwd(Tensor& qkv, int64_t H, int64_t Hkv, const Tensor& cos_t, const Tensor& sin_t, int64_t T,
+                  Tensor& rstd, const optional<Tensor>& xn, const optional<Tensor>& wg, const optional<Tensor>& ve,
+                  const optional<Tensor>& idx) {
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  const int M = (int)(qkv.numel() / qkv.size(-1));
+  const bool has_ve = ve.has_value() && ve->defined();
+  NC_CHECK(nc::qkv_post_fwd(qkv.data_ptr(), qkv.stride(-2), (int)H, (int)Hkv, cos_t.data_ptr(), sin_t.data_ptr(),
+                            (int)T, rstd.data_ptr<float>(), has_ve ? xn->data_ptr() : nullptr,
+                            has_ve ? xn->stride(-2) : 0, has_ve ? wg->data_ptr<float>() : nullptr,
+                            has_ve ? ve->data_ptr() : nullptr, has_ve ? (const long long*)idx->data_ptr<int64_t>() : nullptr,
+                            M, cur_stream()));
+}
+void qkv_post_bwd(Tensor& dqkv, const Tensor& qkv, int64_t H, int64_t Hkv, const Tensor& cos_t, const Tensor& sin_t,
+                  int64_t T, const Tensor& rstd, const optional<Tensor>& xn, const optional<Tensor>& wg,
+                  const optional<Tensor>& ve, const optional<Tensor>& idx, const optional<Tensor>& dve,
+                  const optional<Tensor>& dwg, const optional<Tensor>& dgate_x) {
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  const int M = (int)(qkv.numel() / qkv.size(-1));
+  const bool has_ve = ve.has_value() && ve->defined();
+  TORCH_CHECK(dqkv.stride(-2) == qkv.stride(-2), "dqkv/qkv pitch mismatch");
+  NC_CHECK(nc::qkv_post_bwd(dqkv.data_ptr(), qkv.data_ptr(), qkv.stride(-2), (int)H, (int)Hkv, cos_t.data_ptr(),
+                            sin_t.data_ptr(), (int)T, rstd.data_ptr<float>(), has_ve ? xn->data_ptr() : nullptr,
+                            has_ve ? xn->stride(-2) : 0, has_ve ? wg->data_ptr<float>() : nullptr,
+                            has_ve ? ve->data_ptr() : nullptr,
+                            has_ve ? (const long long*)idx->data_ptr<int64_t>() : nullptr,
+                            has_ve ? dve->data_ptr<float>() : nullptr, has_ve ? dwg->data_ptr<float>() : nullptr,
+                            has_ve ? dgate_x->data_ptr<float>() : nullptr, M, cur_stream()));
+}
+void embed_fwd(const Tensor& idx, const Tensor& wte, const Tensor& gate_w, const Tensor& lam, Tensor& x,
+               const optional<Tensor>& e_last) {
+  const c10::cuda::CUDAGuard guard(wte.device());
+  const int C = (int)wte.size(1), T = (int)idx.size(1), M = (int)idx.numel();
+  NC_CHECK(nc::embed_fwd((const long long*)idx.data_ptr<int64_t>(), wte.data_ptr(), gate_w.data_ptr<float>(),
+                         lam.data_ptr<float>(), x.data_ptr(), const_cast<void*>(optptr(e_last)), M, T, C, cur_stream()));
+}
+void embed_bwd(const Tensor& dx, const Tensor& idx, const Tensor& wte, const Tensor& gate_w, const Tensor& lam,
+               Tensor& dwte, Tensor& dgate_w, Tensor& dlam) {
+  const c10::cuda::CUDAGuard guard(wte.device());
+  const int C = (int)wte.size(1), T = (int)idx.size(1), M = (int)idx.numel();
+  NC_CHECK(nc::embed_bwd(dx.data_ptr(), (const long long*)idx.data_ptr<int64_t>(), wte.data_ptr(),
+                         gate_w.data_ptr<float>(), lam.data_ptr<float>(), dwte.data_ptr<float>(),
+                         dgate_w.data_ptr<float>(), dlam.data_ptr<float>(), M, T, C, cur_stream()));
+}
+void cast_f32_bf16(const Tensor& src, Tensor& dst) {
+  const c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.is_contiguous() && dst.is_contiguous() && src.numel() == dst.numel(), "cast shapes");
+  NC_CHECK(nc::cast_f32_bf16(src.data_ptr<float>(), dst.data_ptr(), (size_t)src.numel(), cur_stream()));
+}
+
+// ------------------------------------------------------------------------------ loss
+void softcap_ce_fwd(const Tensor& logits, const Tensor& targets, Tensor& loss, Tensor& lse, int64_t V, double cap) {
+  const c10::cuda::CUDAGuard guard(logits.device());
+  NC_CHECK(nc::softcap_ce_fwd(logits.data_ptr(), logits.stride(0), (const long long*)targets.data_ptr<int64_t>(),
+                              loss.data_ptr<float>(), lse.data_ptr<float>(), (int)logits.size(0), (int)V, (float)cap,
+                              cur_stream()));
+}
+void softcap_ce_bwd(Tensor& logits, const Tensor& targets, const Tensor& lse, const Tensor& gscale, int64_t V,
+                    double cap) {
+  const c10::cuda::CUDAGuard guard(logits.device());
+  NC_CHECK(nc::softcap_ce_bwd(logits.data_ptr(), logits.stride(0), (const long long*)targets.data_ptr<int64_t>(),
+                              lse.data_ptr<float>(), gscale.data_ptr<float>(), gscale.numel() > 1 ? 1 : 0,
+                              (int)logits.size(0), (int)V, (int)logits.size(1), (float)cap, cur_stream()));
+}
+void softcap_logits(const Tensor& logits, Tensor& out, int64_t V, double cap) {
+  const c10::cuda::CUDAGuard guard(logits.device());
+  NC_CHECK(nc::softcap_logits(logits.data_ptr(), logits.stride(0), out.data_ptr<float>(), (int)logits.size(0), (int)V,
+                              (float)cap, cur_stream()));
+}
+
+// ------------------------------------------------------------------------- optimizer
+void adamw_step(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const optional<Tensor>& shadow, double lr,
+                double beta1, double beta2, double eps, double wd, int64_t step, double grad_scale) {
+  const c10::cuda::CUDAGuard guard(p.device());
+  TORCH_CHECK(p.is_contiguous() && g.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "adamw: contiguous");
+  TORCH_CHECK(m.scalar_type() == p.scalar_type() && v.scalar_type() == p.scalar_type(), "adamw: state dtype");
+  nc::AdamWArgs a;
+  a.lr = (float)lr; a.beta1 = (float)beta1; a.beta2 = (float)beta2; a.eps = (float)eps; a.wd = (float)wd;
+  a.bias1 = (float)(1.0 - std::pow(beta1, (double)step));
+  a.bias2 = (float)(1.0 - std::pow(beta2, (double)step));
+  a.grad_scale = (float)grad_scale;
+  NC_CHECK(nc::adamw_step(p.data_ptr(), p.scalar_type() == at::kBFloat16, g.data_ptr(),
+                          g.scalar_type() == at::kBFloat16, m.data_ptr(), v.data_ptr(),
+                          const_cast<void*>(optptr(shadow)), (size_t)p.numel(), a, cur_stream()));
+}
+void muon_momentum(const Tensor& g, Tensor& buf, Tensor& X, Tensor& rowss, Tensor& total, double mu,
+                   double grad_scale) {
+  const c10::cuda::CUDAGuard guard(g.device());
+  NC_CHECK(nc::muon_momentum(g.data_ptr<float>(), buf.data_ptr<float>(), X.data_ptr(), rowss.data_ptr<float>(),
+                             total.data_ptr<float>(), (float)mu, (float)grad_scale, (int)g.size(0), (int)g.size(1),
+                             (int)g.size(2), cur_stream()));
+  g_launches += 1;   // momentum + per-matrix total
+}
+void muon_equilibrate(Tensor& X, const Tensor& rowss, const Tensor& total, Tensor& rowss2, Tensor& total2) {
+  const c10::cuda::CUDAGuard guard(X.device());
+  NC_CHECK(nc::muon_equilibrate(X.data_ptr(), rowss.data_ptr<float>(), total.data_ptr<float>(),
+                                rowss2.data_ptr<float>(), total2.data_ptr<float>(), (int)X.size(0), (int)X.size(1),
+                                (int)X.size(2), cur_stream()));
+  g_launches += 2;   // equilibrate + total + scale
+}
+void muon_finish(Tensor& p, const Tensor& X, Tensor& second_buf, Tensor& ss, Tensor& scale,
+                 const optional<Tensor>& shadow, double lr, double wd, double beta2) {
+  const c10::cuda::CUDAGuard guard(X.device());
+  NC_CHECK(nc::muon_finish(p.data_ptr<float>(), X.data_ptr(), second_buf.data_ptr<float>(), ss.data_ptr<float>(),
+                           scale.data_ptr<float>(), const_cast<void*>(optptr(shadow)), (int)X.size(0), (int)X.size(1),
+                           (int)X.size(2), (float)lr, (float)wd, (float)beta2, cur_stream()));
+  g_launches += 2;   // sumsq + stats + apply
+}
+int64_t launch_count() { return (int64_t)g_launches.load(); }
+
+// ------------------------------------------------------------------------- attention
+void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tensor& lse, int64_t window,
+              double scale) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  nc::AttnDesc d{};
+  d.B = (int)q.size(0); d.Tq = (int)q.size(1); d.H = (int)q.size(2); d.D = (int)q.size(3);
+  d.Tk = (int)k.size(1); d.Hkv = (int)k.size(2);
+  d.q = q.data_ptr(); d.k = k.data_ptr(); d.v = v.data_ptr(); d.o = o.data_ptr(); d.lse = lse.data_ptr<float>();
+  d.q_tok = q.stride(1); d.k_tok = k.stride(1); d.v_tok = v.stride(1); d.o_tok = o.stride(1);
+  d.q_bat = q.stride(0); d.k_bat = k.stride(0); d.v_bat = v.stride(0); d.o_bat = o.stride(0);
+  d.q_head = q.stride(2); d.k_head = k.stride(2); d.v_head = v.stride(2); d.o_head = o.stride(2);
+  d.window = (int)window; d.scale = (float)scale;
+  NC_CHECK(nc::attention_fwd(d, status_ptr(q), cur_stream()));
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm);
+  m.def("gemm_pick_bn", &gemm_pick_bn);
+  m.def("read_status", &read_status);
+  m.def("launch_count", &launch_count);
+  m.def("mixnorm_fwd", &mixnorm_fwd);
+  m.def("norm_fwd", &norm_fwd);
+  m.def("normadd_bwd", &normadd_bwd);
+  m.def("mixnorm_bwd", &mixnorm_bwd);
+  m.def("backout_norm_fwd", &backout_norm_fwd);
+  m.def("backout_norm_bwd", &backout_norm_bwd);
+  m.def("qkv_post_fwd", &qkv_post_fwd);
+  m.def("qkv_post_bwd", &qkv_post_bwd);
+  m.def("embed_fwd", &embed_fwd);
+  m.def("embed_bwd", &embed_bwd);
+  m.def("cast_f32_bf16", &cast_f32_bf16);
+  m.def("softcap_ce_fwd", &softcap_ce_fwd);
+  m.def("softcap_ce_bwd", &softcap_ce_bwd);
+  m.def("softcap_logits", &softcap_logits);
+  m.def("adamw_step", &adamw_step);
+  m.def("muon_momentum", &muon_momentum);
+  m.def("muon_equilibrate", &muon_equilibrate);
+  m.def("muon_finish", &muon_finish);
+  m.def("attn_fwd", &attn_fwd);
+}

@@ -1,0 +1,352 @@
+// bf16 GEMM for sm_100a: TMA -> 128B-swizzled shared-memory ring -> tcgen05.mma
+// (cta_group::1, 128 x BN x 16 per instruction) -> fp32 accumulators in TMEM ->
+// tcgen05.ld epilogue. One persistent CTA per SM walks a grouped tile order; two
+// TMEM accumulator stages let the epilogue of tile i overlap the main loop of
+// tile i+1.
+//
+//   C[b] (M x N) = epi( alpha * A[b] * B[b]^T , aux[b] )
+//
+// Operand storage is described per operand ("K-major" = reduction dim contiguous,
+// "MN-major" = output dim contiguous), which covers the three GEMMs of a linear
+// layer without any transposed copies:
+//   forward  y  = x  W^T : A = x  (K-major),   B = W  (K-major)
+//   dgrad    dx = dy W   : A = dy (K-major),   B = W  (MN-major)
+//   wgrad    dW = dy^T x : A = dy (MN-major),  B = x  (MN-major), fp32 accumulate
+// and the Newton-Schulz products of the Muon optimizer (X X^T, A A, B X, X^T X).
+//
+// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer
+// (one elected lane), warps 2..5 = epilogue (each owns the TMEM lane quadrant
+// warp_id % 4). All waits are bounded (ptx.cuh); a failed wait raises the CTA abort
+// flag, records a status word and the kernel drains and exits normally.
+#include "gemm.h"
+#include "host_utils.cuh"
+#include "ptx.cuh"
+
+namespace nc {
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+constexpr int CHUNK_BYTES = 64 * BK * 2;   // one MN-major TMA box: 64 k-rows x 128 B
+
+struct GemmKernelArgs {
+  int M, N, K, batch;
+  void* C;
+  long long ldc, bsc;
+  const void* aux;
+  long long ldaux, bsaux;
+  float alpha, beta;
+  int epi;
+  int c_f32;
+  int m_blocks, n_blocks, group_m;
+  int* status;
+};
+
+constexpr int next_pow2_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : 256; }
+
+template <int BN, bool A_MN, bool B_MN>
+struct Cfg {
+  static constexpr int BN_SMEM = (BN + 63) / 64 * 64;
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = BN_SMEM * BK * 2;
+  static constexpr int B_TX = B_MN ? B_BYTES : BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int MAX_STAGES = (227 * 1024 - 2048) / STAGE_BYTES;
+  static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
+  static constexpr int ACC_STRIDE = next_pow2_cols(BN);
+  static constexpr int TMEM_COLS = 2 * ACC_STRIDE;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+};
+
+__device__ __forceinline__ void tile_coords(int t, const GemmKernelArgs& a, int& b, int& mb, int& nb) {
+  int per_batch = a.m_blocks * a.n_blocks;
+  b = t / per_batch;
+  int r = t - b * per_batch;
+  int group_tiles = a.group_m * a.n_blocks;
+  int g = r / group_tiles;
+  int first_m = g * a.group_m;
+  int gm = min(a.group_m, a.m_blocks - first_m);
+  int in_g = r - g * group_tiles;
+  mb = first_m + in_g % gm;
+  nb = in_g / gm;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmKernelArgs args) {
+  using C = Cfg<BN, A_MN, B_MN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* acc_full = empty + C::STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = (args.K + BK - 1) / BK;
+  const int total_tiles = args.m_blocks * args.n_blocks * args.batch;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
+  if (warp == 1) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int b, mb, nb; tile_coords(t, args, b, mb, nb);
+        const int m0 = mb * BM, n0 = nb * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, args.status, ST_WAIT_EMPTY, t)) { ok = false; break; }
+          uint8_t* sA = tiles + stage * C::STAGE_BYTES;
+          uint8_t* sB = sA + C::A_BYTES;
+          mbar_arrive_expect_tx(&full[stage], C::A_BYTES + C::B_TX);
+          const int k0 = kb * BK;
+          if constexpr (A_MN) {
+            tma_load_3d(sA, &tmA, &full[stage], m0, k0, b);
+            tma_load_3d(sA + CHUNK_BYTES, &tmA, &full[stage], m0 + 64, k0, b);
+          } else {
+            tma_load_3d(sA, &tmA, &full[stage], k0, m0, b);
+          }
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int j = 0; j < C::BN_SMEM / 64; ++j)
+              tma_load_3d(sB + j * CHUNK_BYTES, &tmB, &full[stage], n0 + 64 * j, k0, b);
+          } else {
+            tma_load_3d(sB, &tmB, &full[stage], k0, n0, b);
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      int acc = 0; uint32_t acc_phase = 0;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, args.status, ST_WAIT_TMEM_EMPTY, t)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * C::ACC_STRIDE;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, args.status, ST_WAIT_FULL, t)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + stage * C::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + C::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t a_desc = A_MN ? umma_desc_sw128(a_addr + k * (UMMA_K * 128), CHUNK_BYTES, 1024)
+                                         : umma_desc_sw128(a_addr + k * (UMMA_K * 2), 16, 1024);
+            const uint64_t b_desc = B_MN ? umma_desc_sw128(b_addr + k * (UMMA_K * 128), CHUNK_BYTES, 1024)
+                                         : umma_desc_sw128(b_addr + k * (UMMA_K * 2), 16, 1024);
+            mma_f16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0);
+          }
+          mma_commit(&empty[stage]);   // frees the smem stage once these MMAs have read it
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit(&acc_full[acc]);    // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quad = warp & 3;
+    int acc = 0; uint32_t acc_phase = 0; bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int b, mb, nb; tile_coords(t, args, b, mb, nb);
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, args.status, ST_WAIT_TMEM_FULL, t)) { ok = false; break; }
+      tc_fence_after();
+      const int row = mb * BM + quad * 32 + lane;
+      const int n0 = nb * BN;
+      const bool row_ok = row < args.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC_STRIDE;
+      const float alpha = args.alpha, beta = args.beta;
+#pragma unroll 1
+      for (int c = 0; c < BN / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld16(taddr + c * 16, r);
+        tmem_wait_ld();
+        const int col = n0 + c * 16;
+        if (row_ok && col < args.N) {
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) * alpha;
+          if (args.c_f32) {
+            float* crow = reinterpret_cast<float*>(args.C) + b * args.bsc + static_cast<long long>(row) * args.ldc + col;
+            const float* xrow = args.aux ? reinterpret_cast<const float*>(args.aux) + b * args.bsaux +
+                                               static_cast<long long>(row) * args.ldaux + col
+                                         : nullptr;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              if (col + q4 * 4 + 4 <= args.N) {
+                float4 o = make_float4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+                if (xrow) {
+                  float4 x = *reinterpret_cast<const float4*>(xrow + q4 * 4);
+                  o.x += beta * x.x; o.y += beta * x.y; o.z += beta * x.z; o.w += beta * x.w;
+                }
+                *reinterpret_cast<float4*>(crow + q4 * 4) = o;
+              }
+            }
+          } else {
+            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(args.C) + b * args.bsc +
+                                  static_cast<long long>(row) * args.ldc + col;
+            const __nv_bfloat16* xrow = args.aux ? reinterpret_cast<const __nv_bfloat16*>(args.aux) + b * args.bsaux +
+                                                       static_cast<long long>(row) * args.ldaux + col
+                                                 : nullptr;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              if (col + h * 8 + 8 <= args.N) {
+                float* vv = v + h * 8;
+                if (args.epi == EPI_RELU2) {
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) { float tpos = fmaxf(vv[j], 0.f); vv[j] = tpos * tpos; }
+                } else if (xrow) {
+                  uint4 xa = *reinterpret_cast<const uint4*>(xrow + h * 8);
+                  const uint32_t xs[4] = {xa.x, xa.y, xa.z, xa.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    float2 f = unpack_bf16(xs[j]);
+                    if (args.epi == EPI_MUL2SQRT) {
+                      vv[2 * j] *= 2.f * sqrtf(f.x);
+                      vv[2 * j + 1] *= 2.f * sqrtf(f.y);
+                    } else {
+                      vv[2 * j] += beta * f.x;
+                      vv[2 * j + 1] += beta * f.y;
+                    }
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16(vv[0], vv[1]); o.y = pack_bf16(vv[2], vv[3]);
+                o.z = pack_bf16(vv[4], vv[5]); o.w = pack_bf16(vv[6], vv[7]);
+                *reinterpret_cast<uint4*>(crow + h * 8) = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncthreads();
+  if (*abort_flag) {
+    // give copies that are still in flight time to land before shared memory is released
+    unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
+// ----------------------------------------------------------------------------- host
+
+template <int BN, bool A_MN, bool B_MN>
+static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t stream) {
+  using C = Cfg<BN, A_MN, B_MN>;
+  static bool configured = false;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  CUtensorMap tmA, tmB;
+  const uint64_t batch = static_cast<uint64_t>(d.batch);
+  {
+    uint64_t dims[3], str[2]; uint32_t box[3];
+    if (A_MN) { dims[0] = d.M; dims[1] = d.K; box[0] = 64; box[1] = BK; }
+    else      { dims[0] = d.K; dims[1] = d.M; box[0] = BK; box[1] = BM; }
+    dims[2] = batch; box[2] = 1;
+    str[0] = static_cast<uint64_t>(d.lda) * 2;
+    str[1] = d.batch > 1 ? static_cast<uint64_t>(d.bsa) * 2 : str[0] * dims[1];
+    if (!make_tmap(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d.A, dims, str, box)) return cudaErrorInvalidValue;
+  }
+  {
+    uint64_t dims[3], str[2]; uint32_t box[3];
+    if (B_MN) { dims[0] = d.N; dims[1] = d.K; box[0] = 64; box[1] = BK; }
+    else      { dims[0] = d.K; dims[1] = d.N; box[0] = BK; box[1] = BN; }
+    dims[2] = batch; box[2] = 1;
+    str[0] = static_cast<uint64_t>(d.ldb) * 2;
+    str[1] = d.batch > 1 ? static_cast<uint64_t>(d.bsb) * 2 : str[0] * dims[1];
+    if (!make_tmap(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d.B, dims, str, box)) return cudaErrorInvalidValue;
+  }
+  GemmKernelArgs a;
+  a.M = d.M; a.N = d.N; a.K = d.K; a.batch = d.batch;
+  a.C = d.C; a.ldc = d.ldc; a.bsc = d.bsc;
+  a.aux = d.aux; a.ldaux = d.ldaux; a.bsaux = d.bsaux;
+  a.alpha = d.alpha; a.beta = d.beta; a.epi = d.epi; a.c_f32 = d.c_f32;
+  a.m_blocks = (d.M + BM - 1) / BM;
+  a.n_blocks = (d.N + BN - 1) / BN;
+  a.group_m = 16;
+  a.status = status;
+  const long long tiles = 1ll * a.m_blocks * a.n_blocks * d.batch;
+  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  kern<<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, a);
+  return cudaGetLastError();
+}
+
+template <bool A_MN, bool B_MN>
+static cudaError_t launch_bn(int bn, const GemmDesc& d, int* status, cudaStream_t s) {
+  switch (bn) {
+    case 256: return launch_cfg<256, A_MN, B_MN>(d, status, s);
+    case 208: return launch_cfg<208, A_MN, B_MN>(d, status, s);
+    case 128: return launch_cfg<128, A_MN, B_MN>(d, status, s);
+    case 64:  return launch_cfg<64, A_MN, B_MN>(d, status, s);
+    case 32:  return launch_cfg<32, A_MN, B_MN>(d, status, s);
+    default:  return cudaErrorInvalidValue;
+  }
+}
+
+int gemm_pick_bn(int M, int N, int batch) {
+  // maximise (useful columns / padded columns) x (tiles / tiles rounded up to whole waves) x tile efficiency
+  static const int cand[5] = {256, 208, 128, 64, 32};
+  static const double eff[5] = {1.0, 0.98, 0.86, 0.62, 0.36};
+  const int sms = sm_count();
+  const long long mb = (M + BM - 1) / BM;
+  double best = -1; int pick = 128;
+  for (int i = 0; i < 5; ++i) {
+    const int bn = cand[i];
+    const long long nb = (N + bn - 1) / bn;
+    const long long tiles = mb * nb * batch;
+    const long long waves = (tiles + sms - 1) / sms;
+    const double score = eff[i] * (double(N) / double(nb * bn)) * (double(tiles) / double(waves * sms));
+    if (score > best + 1e-9) { best = score; pick = bn; }
+  }
+  return pick;
+}
+
+cudaError_t gemm_bf16(const GemmDesc& d, int* status, cudaStream_t stream) {
+  if (d.M <= 0 || d.N <= 0 || d.K <= 0 || d.batch <= 0) return cudaErrorInvalidValue;
+  if ((d.N & 7) || (d.lda & 7) || (d.ldb & 7) || (d.ldc & 3)) return cudaErrorInvalidValue;
+  const int bn = d.bn > 0 ? d.bn : gemm_pick_bn(d.M, d.N, d.batch);
+  if (d.a_mn && d.b_mn) return launch_bn<true, true>(bn, d, status, stream);
+  if (!d.a_mn && d.b_mn) return launch_bn<false, true>(bn, d, status, stream);
+  if (!d.a_mn && !d.b_mn) return launch_bn<false, false>(bn, d, status, stream);
+  return launch_bn<true, false>(bn, d, status, stream);
+}
+
+}  // namespace nc

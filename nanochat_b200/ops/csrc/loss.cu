@@ -1,0 +1,118 @@
+// Soft-capped cross entropy over bf16 logits, one CTA per row.
+//
+// With z = cap*tanh(l/cap) every z lies in [-cap, cap] (cap = 15), so sum(exp(z)) over a
+// 32768-wide vocabulary stays far inside fp32 range and the log-sum-exp needs a single
+// pass with no running maximum. The backward overwrites the logits with
+// d loss/d l = (softmax(z) - onehot) * (1 - (z/cap)^2) * gscale, so the tensor handed to the
+// dgrad / wgrad GEMMs is produced in place (the full fp32 logit matrix never exists).
+#include "fused.h"
+#include "rowops.cuh"
+
+namespace nc {
+
+constexpr int CE_THREADS = 256;
+
+__device__ __forceinline__ float softcap(float l, float cap, float inv_cap) {
+  // cap * tanh(l/cap) via one exp: tanh(u) = 1 - 2/(exp(2u)+1)
+  const float e = __expf(2.f * l * inv_cap);
+  return cap * (1.f - __fdividef(2.f, e + 1.f));
+}
+
+__device__ __forceinline__ float block_sum(float v, float* smem) {
+  v = warp_sum(v);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < (blockDim.x >> 5)) ? smem[threadIdx.x] : 0.f;
+  if (warp == 0) t = warp_sum(t);
+  if (threadIdx.x == 0) smem[0] = t;
+  __syncthreads();
+  const float r = smem[0];
+  __syncthreads();
+  return r;
+}
+
+__global__ void __launch_bounds__(CE_THREADS)
+softcap_ce_fwd_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ targets,
+                      float* __restrict__ loss, float* __restrict__ lse_out, int V, float cap) {
+  __shared__ float red[CE_THREADS / 32];
+  const int row = blockIdx.x;
+  const __nv_bfloat16* lrow = logits + (size_t)row * ld;
+  const float inv_cap = 1.f / cap;
+  const int nvec = V >> 3;
+  float acc = 0.f;
+  for (int vi = threadIdx.x; vi < nvec; vi += CE_THREADS) {
+    float f[8];
+    unpack8(__ldg(reinterpret_cast<const uint4*>(lrow) + vi), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc += __expf(softcap(f[j], cap, inv_cap));
+  }
+  for (int c = (nvec << 3) + threadIdx.x; c < V; c += CE_THREADS)
+    acc += __expf(softcap(__bfloat162float(lrow[c]), cap, inv_cap));
+  const float total = block_sum(acc, red);
+  if (threadIdx.x == 0) {
+    const float lse = logf(total);
+    lse_out[row] = lse;
+    const long long tgt = targets[row];
+    loss[row] = tgt >= 0 ? lse - softcap(__bfloat162float(lrow[tgt]), cap, inv_cap) : 0.f;
+  }
+}
+
+__global__ void __launch_bounds__(CE_THREADS)
+softcap_ce_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ targets,
+                      const float* __restrict__ lse_in, const float* __restrict__ gscale, int gscale_stride,
+                      int V, int V_padded, float cap) {
+  const int row = blockIdx.x;
+  __nv_bfloat16* lrow = logits + (size_t)row * ld;
+  const float inv_cap = 1.f / cap;
+  const long long tgt = targets[row];
+  const float gs = tgt >= 0 ? gscale[(size_t)row * gscale_stride] : 0.f;
+  const float lse = lse_in[row];
+  const int nvec = V_padded >> 3;
+  for (int vi = threadIdx.x; vi < nvec; vi += CE_THREADS) {
+    float f[8];
+    unpack8(*(reinterpret_cast<const uint4*>(lrow) + vi), f);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c = vi * 8 + j;
+      const float z = softcap(f[j], cap, inv_cap);
+      float dz = __expf(z - lse) - (c == tgt ? 1.f : 0.f);
+      const float u = z * inv_cap;
+      f[j] = (c < V) ? gs * dz * (1.f - u * u) : 0.f;
+    }
+    *(reinterpret_cast<uint4*>(lrow) + vi) = pack8(f);
+  }
+}
+
+__global__ void __launch_bounds__(CE_THREADS)
+softcap_logits_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, float* __restrict__ out, int V,
+                      float cap) {
+  const int row = blockIdx.x;
+  const __nv_bfloat16* lrow = logits + (size_t)row * ld;
+  const float inv_cap = 1.f / cap;
+  for (int c = threadIdx.x; c < V; c += CE_THREADS)
+    out[(size_t)row * V + c] = cap * tanhf(__bfloat162float(lrow[c]) * inv_cap);
+}
+
+cudaError_t softcap_ce_fwd(const void* logits, long long ld, const long long* targets, float* loss, float* lse,
+                           int M, int V, float cap, cudaStream_t s) {
+  if (ld & 7) return cudaErrorInvalidValue;
+  softcap_ce_fwd_kernel<<<M, CE_THREADS, 0, s>>>((const __nv_bfloat16*)logits, ld, targets, loss, lse, V, cap);
+  return cudaGetLastError();
+}
+
+cudaError_t softcap_ce_bwd(void* logits, long long ld, const long long* targets, const float* lse,
+                           const float* gscale, int gscale_stride, int M, int V, int V_padded, float cap,
+                           cudaStream_t s) {
+  if ((ld & 7) || (V_padded & 7)) return cudaErrorInvalidValue;
+  softcap_ce_bwd_kernel<<<M, CE_THREADS, 0, s>>>((__nv_bfloat16*)logits, ld, targets, lse, gscale, gscale_stride, V,
+                                                 V_padded, cap);
+  return cudaGetLastError();
+}
+
+cudaError_t softcap_logits(const void* logits, long long ld, float* out, int M, int V, float cap, cudaStream_t s) {
+  softcap_logits_kernel<<<M, CE_THREADS, 0, s>>>((const __nv_bfloat16*)logits, ld, out, V, cap);
+  return cudaGetLastError();
+}
+
+}  // namespace nc

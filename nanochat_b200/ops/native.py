@@ -1,0 +1,622 @@
+"""
+Autograd wrappers over the hand-written sm_100a kernels (`nanochat_b200._C`).
+
+Granularity is chosen for the hardware, not for the autograd graph: one
+`torch.autograd.Function` per transformer LAYER (forward = 4 GEMMs + 4 fused
+elementwise kernels + flash attention; backward hand-derived, 9 GEMMs + 4 fused
+kernels), one for embedding+norm+smear, one for backout+norm+lm_head+soft-capped
+cross entropy. Consequences:
+
+  * weights are consumed from bf16 shadow copies that the optimizer kernels refresh
+    when they write the fp32 master (no per-forward cast);
+  * weight gradients are accumulated by the wgrad GEMM epilogue directly into the fp32
+    `.grad` buffer (fp32 += A^T B), embedding-table gradients into fp32 `grad32`
+    buffers by atomic scatter; these Functions therefore return None for parameters;
+  * relu^2 is the epilogue of the c_fc GEMM, its derivative the epilogue of the c_proj
+    dgrad GEMM (2*sqrt(out) recovers relu(h) from the saved output), residual adds are
+    GEMM epilogues, and rotary + QK-norm + value-embedding gating is one in-place pass
+    over the fused QKV buffer.
+
+Reference semantics: nanochat/gpt.py:84-153,459-521 (forward math); the oracle for
+every function here is `ops/reference.py`.
+"""
+
+import math
+import weakref
+
+import torch
+from torch.autograd import Function
+
+from nanochat_b200.ops import reference as ref_ops
+from nanochat_b200.utils.build import load_cuda_extension
+
+_C = load_cuda_extension()
+
+EPI_LINEAR, EPI_RELU2, EPI_MUL2SQRT = 0, 1, 2
+BF16 = torch.bfloat16
+
+# 'native' = tcgen05 flash attention kernels, 'sdpa' = PyTorch SDPA (bring-up / oracle)
+ATTENTION_IMPL = "sdpa"
+
+
+def check_status(like=None):
+    """Raise if any kernel recorded a failed (timed-out) wait since the last check. Synchronises."""
+    dev = like if like is not None else torch.empty(0, device="cuda")
+    st = _C.read_status(dev)
+    if st[0] != 0:
+        code, detail = st[0] >> 24, st[0] & 0xFFFFFF
+        raise RuntimeError(f"nanochat_b200 kernel reported a failed wait: code={code} detail={detail}")
+
+
+def launch_count():
+    """Number of kernels this extension has launched in this process (host-side counter)."""
+    return _C.launch_count()
+
+
+# ----------------------------------------------------------------------------- shadows
+
+_shadow = weakref.WeakKeyDictionary()
+
+
+def shadow_of(w):
+    """bf16 operand copy of a (usually fp32) weight, refreshed when the weight's version moves."""
+    if w.dtype == BF16:
+        return w
+    ent = _shadow.get(w)
+    ver = w._version
+    if ent is not None and ent[0] == ver and ent[2] == w.data_ptr():
+        return ent[1]
+    buf = ent[1] if ent is not None and ent[1].shape == w.shape else torch.empty_like(w, dtype=BF16)
+    src = w.detach()
+    if src.dtype == torch.float32 and src.is_contiguous() and src.numel() % 8 == 0:
+        _C.cast_f32_bf16(src, buf)
+    else:
+        buf.copy_(src)
+    _shadow[w] = (ver, buf, w.data_ptr())
+    return buf
+
+
+def shadow_buffer(w):
+    """The shadow tensor itself (created if needed) so an optimizer kernel can write it in place."""
+    shadow_of(w)
+    return _shadow[w][1] if w.dtype != BF16 else None
+
+
+def mark_shadow_fresh(w):
+    ent = _shadow.get(w)
+    if ent is not None:
+        _shadow[w] = (w._version, ent[1], w.data_ptr())
+
+
+# -------------------------------------------------------------------------------- GEMM
+
+def gemm(A, B, out, *, a_mn=False, b_mn=False, aux=None, alpha=1.0, beta=0.0, epi=EPI_LINEAR, bn=0):
+    """out = epilogue(alpha * A @ B^T, aux); see csrc/gemm.h for the operand conventions."""
+    _C.gemm(A, B, out, aux, a_mn, b_mn, alpha, beta, epi, bn)
+    return out
+
+
+def _rows(x):
+    x2 = x.reshape(-1, x.shape[-1])
+    return x2 if x2.stride(-1) == 1 else x2.contiguous()
+
+
+def _accumulate_wgrad(w, dy2, x2):
+    """w.grad (fp32) += dy2^T @ x2, fused in the GEMM epilogue."""
+    if w.grad is None:
+        w.grad = torch.empty_like(w, dtype=w.dtype)
+        gemm(dy2, x2, w.grad, a_mn=True, b_mn=True)
+    else:
+        gemm(dy2, x2, w.grad, a_mn=True, b_mn=True, aux=w.grad, beta=1.0)
+
+
+def _grad_buffer(p, dtype=torch.float32):
+    """fp32 gradient accumulator of a parameter: `.grad` for fp32 params, `.grad32` otherwise."""
+    if p.dtype == dtype:
+        if p.grad is None:
+            p.grad = torch.zeros_like(p)
+        return p.grad
+    g = getattr(p, "grad32", None)
+    if g is None:
+        g = torch.zeros(p.shape, dtype=dtype, device=p.device)
+        p.grad32 = g
+    return g
+
+
+# ------------------------------------------------------------------------ generic ops
+
+class _LinearFn(Function):
+    @staticmethod
+    def forward(ctx, x, w, relu2):
+        x2 = _rows(x)
+        y = torch.empty(x2.shape[0], w.shape[0], dtype=BF16, device=x.device)
+        gemm(x2, shadow_of(w), y, epi=EPI_RELU2 if relu2 else EPI_LINEAR)
+        ctx.relu2 = relu2
+        ctx.save_for_backward(x2, w, y if relu2 else None)
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, y = ctx.saved_tensors
+        dy2 = _rows(dy)
+        if ctx.relu2:
+            dy2 = dy2 * (2.0 * y.float().sqrt()).to(BF16)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty_like(x2)
+            gemm(dy2, shadow_of(w), dx, b_mn=True)
+            dx = dx.view(*dy.shape[:-1], x2.shape[-1])
+        if w.requires_grad:
+            _accumulate_wgrad(w, dy2, x2)
+        return dx, None, None
+
+
+def _gemm_ok(x, w):
+    return x.shape[-1] % 8 == 0 and w.shape[0] % 8 == 0 and x.dtype == BF16
+
+
+def linear(x, w):
+    if not _gemm_ok(x, w):
+        return ref_ops.linear(x, w)
+    return _LinearFn.apply(x, w, False)
+
+
+def linear_relu2(x, w):
+    if not _gemm_ok(x, w):
+        return ref_ops.linear_relu2(x, w)
+    return _LinearFn.apply(x, w, True)
+
+
+class _RmsNormFn(Function):
+    @staticmethod
+    def forward(ctx, x):
+        xc = x.contiguous()
+        y = torch.empty_like(xc)
+        _C.norm_fwd(xc, y)
+        ctx.save_for_backward(xc)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        dx = torch.empty_like(x)
+        _C.normadd_bwd(dy.contiguous(), x, None, dx)
+        return dx
+
+
+def rms_norm(x):
+    if x.shape[-1] % 8 != 0 or x.shape[-1] > 4096:
+        return ref_ops.rms_norm(x)
+    return _RmsNormFn.apply(x)
+
+
+# ops without a dedicated standalone kernel run their reference body on the GPU
+ve_gate_add = ref_ops.ve_gate_add
+rope_qknorm = ref_ops.rope_qknorm
+add_norm = ref_ops.add_norm
+embed_norm_smear_ref = ref_ops.embed_norm_smear
+
+
+def embed_norm_smear(idx, wte, gate_w, lam):
+    return _EmbedFn.apply(idx, wte, gate_w, lam)
+
+
+def resid_mix_norm(x, x0, resid_lambdas, x0_lambdas, layer):
+    return ref_ops.resid_mix_norm(x, x0, resid_lambdas[layer], x0_lambdas[layer])
+
+
+def backout_norm(x, x_backout, lam):
+    return ref_ops.backout_norm(x, x_backout, lam)
+
+
+def softcap_logits(x, w, vocab_size, softcap=ref_ops.SOFTCAP):
+    x2 = _rows(x)
+    logits = torch.empty(x2.shape[0], w.shape[0], dtype=BF16, device=x.device)
+    gemm(x2, shadow_of(w), logits)
+    out = torch.empty(x2.shape[0], vocab_size, dtype=torch.float32, device=x.device)
+    _C.softcap_logits(logits, out, vocab_size, softcap)
+    return out.view(*x.shape[:-1], vocab_size)
+
+
+# --------------------------------------------------------------------------- attention
+
+def _attention_sdpa_fwd(q, k, v, window):
+    return ref_ops.attention(q, k, v, window)
+
+
+def attention_forward(q, k, v, window):
+    """Returns (y, lse); lse is None on the SDPA bring-up path."""
+    if ATTENTION_IMPL == "native":
+        B, T, H, D = q.shape
+        y = torch.empty(B, T, H, D, dtype=BF16, device=q.device)
+        lse = torch.empty(B, H, T, dtype=torch.float32, device=q.device)
+        _C.attn_fwd(q, k, v, y, lse, window if 0 <= window < k.shape[1] else -1, 1.0 / math.sqrt(D))
+        return y, lse
+    return _attention_sdpa_fwd(q, k, v, window), None
+
+
+def attention_backward(dy, q, k, v, y, lse, window, dqkv_views):
+    """Writes dq, dk, dv into the given (strided) views."""
+    dq_v, dk_v, dv_v = dqkv_views
+    with torch.enable_grad():
+        q_ = q.detach().requires_grad_(True)
+        k_ = k.detach().requires_grad_(True)
+        v_ = v.detach().requires_grad_(True)
+        y_ = ref_ops.attention(q_, k_, v_, window)
+        dq, dk, dv = torch.autograd.grad(y_, (q_, k_, v_), dy)
+    dq_v.copy_(dq)
+    dk_v.copy_(dk)
+    dv_v.copy_(dv)
+
+
+class _AttentionFn(Function):
+    @staticmethod
+    def forward(ctx, q, k, v, window):
+        y, lse = attention_forward(q, k, v, window)
+        ctx.window = window
+        ctx.save_for_backward(q, k, v, y, lse)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        q, k, v, y, lse = ctx.saved_tensors
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        attention_backward(dy.contiguous(), q, k, v, y, lse, ctx.window, (dq, dk, dv))
+        return dq, dk, dv, None
+
+
+def attention(q, k, v, window_left):
+    return _AttentionFn.apply(q, k, v, window_left)
+
+
+def attention_kvcache(q, k_cache, v_cache, k, v, cache_seqlens, window_left):
+    """In-place cache append + attention over the filled prefix (positions read on the host)."""
+    Tn = q.shape[1]
+    pos = int(cache_seqlens[0].item())
+    if k is not None and v is not None:
+        k_cache[:, pos:pos + Tn] = k
+        v_cache[:, pos:pos + Tn] = v
+    end = pos + Tn
+    return ref_ops.attention(q, k_cache[:, :end], v_cache[:, :end], window_left)
+
+
+# ------------------------------------------------------------------- embedding function
+
+class _EmbedFn(Function):
+    @staticmethod
+    def forward(ctx, idx, wte, gate_w, lam):
+        B, T = idx.shape
+        x = torch.empty(B, T, wte.shape[1], dtype=BF16, device=wte.device)
+        e_last = torch.empty(B, 1, wte.shape[1], dtype=BF16, device=wte.device)
+        idx = idx.contiguous()
+        _C.embed_fwd(idx, wte, gate_w.detach().float().contiguous().view(-1), lam.detach().float(), x, e_last)
+        ctx.save_for_backward(idx, wte, gate_w, lam)
+        ctx.mark_non_differentiable(e_last)
+        return x, e_last
+
+    @staticmethod
+    def backward(ctx, dx, _dlast=None):
+        idx, wte, gate_w, lam = ctx.saved_tensors
+        dwte = _grad_buffer(wte)
+        dgate = _grad_buffer(gate_w)
+        dlam = _grad_buffer(lam)
+        _C.embed_bwd(dx.contiguous(), idx, wte, gate_w.detach().float().contiguous().view(-1), lam.detach().float(),
+                     dwte, dgate.view(-1), dlam)
+        return None, None, None, None
+
+
+# ----------------------------------------------------------------------- layer function
+
+def _contiguous_rows(ws):
+    """If the tensors are consecutive row blocks of one buffer, return the stacked (sum_rows, K) view."""
+    first = ws[0]
+    K = first.shape[1]
+    ptr = first.data_ptr()
+    store = first.untyped_storage().data_ptr()
+    for w in ws:
+        if (not w.is_contiguous() or w.shape[1] != K or w.data_ptr() != ptr or w.dtype != first.dtype
+                or w.untyped_storage().data_ptr() != store):
+            return None
+        ptr += w.numel() * w.element_size()
+    rows = sum(w.shape[0] for w in ws)
+    return torch.as_strided(first, (rows, K), (K, 1))
+
+
+class _LayerFn(Function):
+    """One transformer block: mix+norm, attention (with VE gating, rotary, QK-norm), MLP."""
+
+    @staticmethod
+    def forward(ctx, x, x0, idx, cos, sin, resid_lambdas, x0_lambdas, layer, wq, wk, wv, wo, wfc, wpr,
+                wgate, ve_w, window, n_head, n_kv_head):
+        B, T, C = x.shape
+        M = B * T
+        D = C // n_head
+        dev = x.device
+        x2, x02 = x.reshape(M, C), x0.reshape(M, C)
+        xm = torch.empty(M, C, dtype=BF16, device=dev)
+        xn = torch.empty(M, C, dtype=BF16, device=dev)
+        _C.mixnorm_fwd(x2, x02, resid_lambdas, x0_lambdas, layer, xm, xn)
+
+        nq, nkv = n_head * D, n_kv_head * D
+        qkv = torch.empty(M, nq + 2 * nkv, dtype=BF16, device=dev)
+        sq, sk, sv = shadow_of(wq), shadow_of(wk), shadow_of(wv)
+        fused_w = _contiguous_rows([sq, sk, sv])
+        if fused_w is not None:
+            gemm(xn, fused_w, qkv)
+        else:
+            gemm(xn, sq, qkv[:, :nq])
+            gemm(xn, sk, qkv[:, nq:nq + nkv])
+            gemm(xn, sv, qkv[:, nq + nkv:])
+        rstd = torch.empty(M, n_head + n_kv_head, dtype=torch.float32, device=dev)
+        cos2, sin2 = cos.reshape(-1, D // 2), sin.reshape(-1, D // 2)
+        idx_c = idx.contiguous()
+        has_ve = ve_w is not None
+        wg32 = wgate.detach().float().contiguous() if has_ve else None
+        _C.qkv_post_fwd(qkv, n_head, n_kv_head, cos2, sin2, T, rstd,
+                        xn if has_ve else None, wg32, ve_w if has_ve else None, idx_c if has_ve else None)
+        q = qkv[:, :nq].view(B, T, n_head, D)
+        k = qkv[:, nq:nq + nkv].view(B, T, n_kv_head, D)
+        v = qkv[:, nq + nkv:].view(B, T, n_kv_head, D)
+        y, lse = attention_forward(q, k, v, window)
+        y2 = y.reshape(M, nq)
+
+        xa = torch.empty(M, C, dtype=BF16, device=dev)
+        gemm(y2, shadow_of(wo), xa, aux=xm, beta=1.0)
+        xn2 = torch.empty(M, C, dtype=BF16, device=dev)
+        _C.norm_fwd(xa, xn2)
+        h = torch.empty(M, wfc.shape[0], dtype=BF16, device=dev)
+        gemm(xn2, shadow_of(wfc), h, epi=EPI_RELU2)
+        xo = torch.empty(M, C, dtype=BF16, device=dev)
+        gemm(h, shadow_of(wpr), xo, aux=xa, beta=1.0)
+
+        ctx.meta = (B, T, C, D, n_head, n_kv_head, layer, window, has_ve)
+        ctx.save_for_backward(x2, x02, idx_c, cos2, sin2, resid_lambdas, x0_lambdas, wq, wk, wv, wo, wfc, wpr,
+                              wgate, ve_w, xm, xn, qkv, rstd, y2, lse, xa, xn2, h)
+        return xo.view(B, T, C)
+
+    @staticmethod
+    def backward(ctx, dxo):
+        (x2, x02, idx, cos2, sin2, resid_lambdas, x0_lambdas, wq, wk, wv, wo, wfc, wpr, wgate, ve_w,
+         xm, xn, qkv, rstd, y2, lse, xa, xn2, h) = ctx.saved_tensors
+        B, T, C, D, n_head, n_kv_head, layer, window, has_ve = ctx.meta
+        M = B * T
+        dev = dxo.device
+        nq, nkv = n_head * D, n_kv_head * D
+        dxo2 = _rows(dxo)
+
+        # ---- MLP
+        dh = torch.empty_like(h)
+        gemm(dxo2, shadow_of(wpr), dh, b_mn=True, aux=h, epi=EPI_MUL2SQRT)
+        _accumulate_wgrad(wpr, dxo2, h)
+        dxn2 = torch.empty(M, C, dtype=BF16, device=dev)
+        gemm(dh, shadow_of(wfc), dxn2, b_mn=True)
+        _accumulate_wgrad(wfc, dh, xn2)
+        del dh
+        dxa = torch.empty(M, C, dtype=BF16, device=dev)
+        _C.normadd_bwd(dxn2, xa, dxo2, dxa)
+
+        # ---- attention output projection
+        dy = dxn2  # reuse
+        gemm(dxa, shadow_of(wo), dy, b_mn=True)
+        _accumulate_wgrad(wo, dxa, y2)
+
+        # ---- attention core
+        dqkv = torch.empty_like(qkv)
+        q = qkv[:, :nq].view(B, T, n_head, D)
+        k = qkv[:, nq:nq + nkv].view(B, T, n_kv_head, D)
+        v = qkv[:, nq + nkv:].view(B, T, n_kv_head, D)
+        views = (dqkv[:, :nq].view(B, T, n_head, D), dqkv[:, nq:nq + nkv].view(B, T, n_kv_head, D),
+                 dqkv[:, nq + nkv:].view(B, T, n_kv_head, D))
+        attention_backward(dy.view(B, T, n_head, D), q, k, v, y2.view(B, T, n_head, D), lse, window, views)
+
+        # ---- rotary / QK-norm / VE gate
+        dgate_x = None
+        if has_ve:
+            dgate_x = torch.empty(M, 12, dtype=torch.float32, device=dev)
+            wg32 = wgate.detach().float().contiguous()
+            _C.qkv_post_bwd(dqkv, qkv, n_head, n_kv_head, cos2, sin2, T, rstd, xn, wg32, ve_w, idx,
+                            _grad_buffer(ve_w), _grad_buffer(wgate), dgate_x)
+        else:
+            _C.qkv_post_bwd(dqkv, qkv, n_head, n_kv_head, cos2, sin2, T, rstd, None, None, None, None,
+                            None, None, None)
+
+        # ---- QKV projections
+        dxn = dy  # reuse again
+        sq, sk, sv = shadow_of(wq), shadow_of(wk), shadow_of(wv)
+        fused_w = _contiguous_rows([sq, sk, sv])
+        if fused_w is not None:
+            gemm(dqkv, fused_w, dxn, b_mn=True)
+        else:
+            gemm(dqkv[:, :nq], sq, dxn, b_mn=True)
+            gemm(dqkv[:, nq:nq + nkv], sk, dxn, b_mn=True, aux=dxn, beta=1.0)
+            gemm(dqkv[:, nq + nkv:], sv, dxn, b_mn=True, aux=dxn, beta=1.0)
+        fused_g = None
+        if all(w.grad is not None for w in (wq, wk, wv)):
+            fused_g = _contiguous_rows([wq.grad, wk.grad, wv.grad])
+        if fused_g is not None:
+            gemm(dqkv, xn, fused_g, a_mn=True, b_mn=True, aux=fused_g, beta=1.0)
+        else:
+            _accumulate_wgrad(wq, dqkv[:, :nq], xn)
+            _accumulate_wgrad(wk, dqkv[:, nq:nq + nkv], xn)
+            _accumulate_wgrad(wv, dqkv[:, nq + nkv:], xn)
+
+        # ---- mix + norm
+        dx = torch.empty(M, C, dtype=BF16, device=dev)
+        dx0 = torch.empty(M, C, dtype=BF16, device=dev)
+        _C.mixnorm_bwd(dxn, dxa, dgate_x, xm, x2, x02, resid_lambdas, x0_lambdas, layer, dx, dx0, False,
+                       _grad_buffer(resid_lambdas), _grad_buffer(x0_lambdas))
+        return (dx.view(B, T, C), dx0.view(B, T, C)) + (None,) * 17
+
+
+def layer_forward(block, x, x0, idx, ve_weight, cos_sin, window_size, resid_lambdas, x0_lambdas, layer):
+    attn, mlp = block.attn, block.mlp
+    return _LayerFn.apply(
+        x, x0, idx, cos_sin[0], cos_sin[1], resid_lambdas, x0_lambdas, layer,
+        attn.c_q.weight, attn.c_k.weight, attn.c_v.weight, attn.c_proj.weight,
+        mlp.c_fc.weight, mlp.c_proj.weight,
+        attn.ve_gate.weight if ve_weight is not None else None, ve_weight,
+        window_size[0], attn.n_head, attn.n_kv_head)
+
+
+# ------------------------------------------------------------------------ head function
+
+class _HeadFn(Function):
+    """backout + norm + lm_head + soft-capped cross entropy."""
+
+    @staticmethod
+    def forward(ctx, x, x_backout, lam, w, targets, vocab_size, softcap, reduction):
+        B, T, C = x.shape
+        M = B * T
+        dev = x.device
+        x2 = x.reshape(M, C)
+        xb2 = x_backout.reshape(M, C) if x_backout is not None else None
+        lam32 = lam.detach().float()
+        xn = torch.empty(M, C, dtype=BF16, device=dev)
+        _C.backout_norm_fwd(x2, xb2, lam32, xn)
+        logits = torch.empty(M, w.shape[0], dtype=BF16, device=dev)
+        gemm(xn, shadow_of(w), logits)
+        tgt = targets.reshape(-1).contiguous()
+        loss_rows = torch.empty(M, dtype=torch.float32, device=dev)
+        lse = torch.empty(M, dtype=torch.float32, device=dev)
+        _C.softcap_ce_fwd(logits, tgt, loss_rows, lse, vocab_size, softcap)
+        n_valid = None
+        if reduction == "mean":
+            n_valid = (tgt >= 0).sum().clamp_min(1).float()
+            out = loss_rows.sum() / n_valid
+        else:
+            out = loss_rows
+        ctx.meta = (B, T, C, vocab_size, softcap, reduction)
+        ctx.save_for_backward(x2, xb2, lam, w, tgt, xn, logits, lse, n_valid)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        x2, xb2, lam, w, tgt, xn, logits, lse, n_valid = ctx.saved_tensors
+        B, T, C, vocab_size, softcap, reduction = ctx.meta
+        M = B * T
+        dev = x2.device
+        if reduction == "mean":
+            gscale = (dout.float() / n_valid).reshape(1)
+        else:
+            gscale = dout.float().contiguous().view(-1)
+        _C.softcap_ce_bwd(logits, tgt, lse, gscale, vocab_size, softcap)     # logits <- dlogits
+        dxn = torch.empty(M, C, dtype=BF16, device=dev)
+        gemm(logits, shadow_of(w), dxn, b_mn=True)
+        _accumulate_wgrad(w, logits, xn)
+        dx = torch.empty(M, C, dtype=BF16, device=dev)
+        dxb = torch.empty(M, C, dtype=BF16, device=dev) if xb2 is not None else None
+        _C.backout_norm_bwd(dxn, x2, xb2, lam.detach().float(), dx, dxb, _grad_buffer(lam))
+        return (dx.view(B, T, C), dxb.view(B, T, C) if dxb is not None else None) + (None,) * 6
+
+
+def softcap_cross_entropy(x, w, targets, vocab_size, reduction="mean", softcap=ref_ops.SOFTCAP):
+    """Standalone form (no backout): norm is NOT applied here; x is already normalised."""
+    x2 = _rows(x)
+    logits = _LinearFn.apply(x2, w, False)
+    return ref_ops.F.cross_entropy(
+        (softcap * torch.tanh(logits[..., :vocab_size].float() / softcap)), targets.reshape(-1),
+        ignore_index=-1, reduction=reduction)
+
+
+def head_loss(x, x_backout, lam, w, targets, vocab_size, reduction, softcap=ref_ops.SOFTCAP):
+    return _HeadFn.apply(x, x_backout, lam, w, targets, vocab_size, softcap, reduction)
+
+
+# --------------------------------------------------------------------------- optimizer
+
+def adamw_update(p, grad, exp_avg, exp_avg_sq, step, lr, beta1, beta2, eps, wd, master=None):
+    """Fused AdamW on a contiguous slice; refreshes the bf16 shadow of fp32 masters in the same pass."""
+    shadow = None
+    owner = master if master is not None else p
+    if p.dtype == torch.float32 and owner in _shadow and p.numel() >= 1024:
+        full = _shadow[owner][1]
+        if p.data_ptr() == owner.data_ptr() and p.numel() == owner.numel():
+            shadow = full
+        elif p.is_contiguous() and owner.is_contiguous():
+            off = (p.data_ptr() - owner.data_ptr()) // owner.element_size()
+            shadow = full.view(-1)[off:off + p.numel()]
+    if not (p.is_contiguous() and grad.is_contiguous()) or grad.dtype not in (torch.float32, BF16) \
+            or p.dtype not in (torch.float32, BF16):
+        return ref_ops.adamw_update(p, grad, exp_avg, exp_avg_sq, step, lr, beta1, beta2, eps, wd)
+    _C.adamw_step(p, grad, exp_avg, exp_avg_sq, shadow, lr, beta1, beta2, eps, wd, step, 1.0)
+    if shadow is not None:
+        mark_shadow_fresh(owner)     # every rank's slice kernel keeps its part of the shadow current
+    elif owner in _shadow:
+        del _shadow[owner]           # written behind autograd's back: force a re-cast on next use
+
+
+_muon_scratch = {}
+
+
+def _scratch(name, shape, dtype, device):
+    key = (name, tuple(shape), dtype, str(device))
+    t = _muon_scratch.get(key)
+    if t is None:
+        t = torch.empty(shape, dtype=dtype, device=device)
+        _muon_scratch[key] = t
+    return t
+
+
+def polar_express_native(X, ns_steps):
+    """Five quintic steps on a bf16 (k,r,c) stack with the tcgen05 GEMM; returns the result stack."""
+    k, r, c = X.shape
+    tall = r > c
+    n = c if tall else r
+    A = _scratch("ns_A", (k, n, n), BF16, X.device)
+    Bm = _scratch("ns_B", (k, n, n), BF16, X.device)
+    Y = _scratch("ns_Y", (k, r, c), BF16, X.device)
+    cur, nxt = X, Y
+    for a, b, cc in ref_ops.POLAR_EXPRESS_COEFFS[:ns_steps]:
+        if tall:
+            gemm(cur, cur, A, a_mn=True, b_mn=True)                  # A = X^T X
+            gemm(A, A, Bm, aux=A, alpha=cc, beta=b)                  # B = b A + c A A   (A symmetric)
+            gemm(cur, Bm, nxt, aux=cur, alpha=1.0, beta=a)           # X = a X + X B     (B symmetric)
+        else:
+            gemm(cur, cur, A)                                        # A = X X^T
+            gemm(A, A, Bm, aux=A, alpha=cc, beta=b)
+            gemm(Bm, cur, nxt, b_mn=True, aux=cur, alpha=1.0, beta=a)  # X = a X + B X
+        cur, nxt = nxt, cur
+    return cur
+
+
+def muon_update(grads, params_stack, momentum_buf, second_buf, momentum, lr, wd, beta2, ns_steps, red_dim,
+                params=None):
+    """Native Muon step on fp32 (k,r,c) stacks; `params` (list) lets per-parameter shadows be refreshed."""
+    k, r, c = grads.shape
+    dev = grads.device
+    if (r % 8) or (c % 8) or not (grads.is_contiguous() and params_stack.is_contiguous()
+                                   and momentum_buf.is_contiguous() and second_buf.is_contiguous()):
+        return ref_ops.muon_update(grads, params_stack, momentum_buf, second_buf, momentum, lr, wd, beta2,
+                                   ns_steps, red_dim, use_bf16=True)
+    X = _scratch("muon_X", (k, r, c), BF16, dev)
+    rowss = _scratch("muon_rowss", (k * r,), torch.float32, dev)
+    rowss2 = _scratch("muon_rowss2", (k * r,), torch.float32, dev)
+    total = _scratch("muon_total", (k,), torch.float32, dev)
+    total2 = _scratch("muon_total2", (k,), torch.float32, dev)
+    _C.muon_momentum(grads, momentum_buf, X, rowss, total, momentum, 1.0)
+    _C.muon_equilibrate(X, rowss, total, rowss2, total2)
+    Xo = polar_express_native(X, ns_steps)
+    n = max(r, c)
+    ss = _scratch("muon_ss", (k * n,), torch.float32, dev)
+    scale = _scratch("muon_scale", (k * n,), torch.float32, dev)
+    shadow = None
+    if params is not None and all(p in _shadow for p in params):
+        shadow = _contiguous_stack([_shadow[p][1] for p in params])
+    _C.muon_finish(params_stack, Xo, second_buf.view(k, -1), ss, scale, shadow, lr, wd, beta2)
+    if params is not None:
+        for p in params:
+            if shadow is not None:
+                mark_shadow_fresh(p)
+            elif p in _shadow:
+                del _shadow[p]
+
+
+def _contiguous_stack(ts):
+    first = ts[0]
+    ptr = first.data_ptr()
+    store = first.untyped_storage().data_ptr()
+    for t in ts:
+        if not t.is_contiguous() or t.data_ptr() != ptr or t.untyped_storage().data_ptr() != store:
+            return None
+        ptr += t.numel() * t.element_size()
+    return torch.as_strided(first, (len(ts), *first.shape), (first.numel(), *first.stride()))

@@ -71,6 +71,10 @@ class MuonAdamW(torch.optim.Optimizer):
         for p in group["params"]:
             shard = adamw_shard(tuple(p.shape), comm.rank, comm.world)
             grad = p.grad
+            grad32 = getattr(p, "grad32", None)   # fp32 accumulator kept by the native embedding kernels
+            if grad32 is not None:
+                grad = grad32
+                self._consumed.append(grad32)
             if comm.world == 1:
                 jobs.append((p, shard, grad, None))
             elif shard.replicated:
@@ -179,6 +183,7 @@ class MuonAdamW(torch.optim.Optimizer):
         if getattr(comm, "fused", False):
             return comm.fused_step(self)
         launched = []
+        self._consumed = []
         for group in self.param_groups:
             if group["kind"] == "adamw":
                 launched.append(self._launch_adamw(group, comm))
@@ -196,3 +201,6 @@ class MuonAdamW(torch.optim.Optimizer):
             work.wait()
             if params is not None:
                 torch._foreach_copy_([p.data for p in params], list(stacked[:len(params)].unbind(0)))
+        for g in self._consumed:
+            g.zero_()
+        self._consumed = []

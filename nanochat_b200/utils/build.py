@@ -1,0 +1,176 @@
+"""
+In-tree build of the native extensions with explicit compiler commands.
+
+  nanochat_b200/_C*.so    CUDA kernels (nvcc, sm_100a only) + torch bindings
+  nanochat_b200/_tok*.so  C++ tokenizer (BPE trainer / encoder) + best-fit packer
+
+The shared objects are written next to the package so they are found wherever the
+source tree is copied; a content hash of the sources is stored beside each one and a
+rebuild happens only when the hash differs (or the .so is missing). Build from the
+command line with `python -m nanochat_b200.utils.build`.
+"""
+
+import os
+import sys
+import glob
+import hashlib
+import importlib.util
+import subprocess
+import sysconfig
+from concurrent.futures import ThreadPoolExecutor
+
+PKG_DIR = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+CSRC = os.path.join(PKG_DIR, "ops", "csrc")
+TOK_SRC = os.path.join(PKG_DIR, "csrc", "tokenizer")
+BUILD_DIR = os.path.join(PKG_DIR, "_build")
+EXT_SUFFIX = sysconfig.get_config_var("EXT_SUFFIX") or ".so"
+
+NVCC_ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+
+
+def _hash_files(paths, extra=""):
+    h = hashlib.sha256(extra.encode())
+    for p in sorted(paths):
+        h.update(os.path.basename(p).encode())
+        with open(p, "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()
+
+
+def _run(cmd):
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("build command failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+    return r.stdout + r.stderr
+
+
+def _nvcc():
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    path = os.path.join(cuda_home, "bin", "nvcc")
+    return path if os.path.exists(path) else "nvcc"
+
+
+def _stale(so_path, digest):
+    stamp = so_path + ".hash"
+    if not os.path.exists(so_path) or not os.path.exists(stamp):
+        return True
+    with open(stamp) as f:
+        return f.read().strip() != digest
+
+
+def _load(name, so_path):
+    spec = importlib.util.spec_from_file_location(name, so_path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    sys.modules[name] = mod
+    return mod
+
+
+# ------------------------------------------------------------------------------- CUDA
+
+def cuda_sources():
+    return sorted(glob.glob(os.path.join(CSRC, "*.cu"))), sorted(glob.glob(os.path.join(CSRC, "*.cpp")))
+
+
+def build_cuda_extension(verbose=False, force=False):
+    """Compile every .cu for sm_100a and link `_C`. Returns the path of the shared object."""
+    import torch
+    from torch.utils import cpp_extension as ce
+    name = "_C"
+    so_path = os.path.join(PKG_DIR, name + EXT_SUFFIX)
+    cus, cpps = cuda_sources()
+    headers = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh"))
+    digest = _hash_files(cus + cpps + headers, extra=torch.__version__)
+    if not force and not _stale(so_path, digest):
+        return so_path
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    incs = []
+    for p in ce.include_paths("cuda"):
+        incs += ["-I", p]
+    incs += ["-I", sysconfig.get_paths()["include"], "-I", CSRC]
+    abi = int(torch._C._GLIBCXX_USE_CXX11_ABI)
+    common_defs = [f"-DTORCH_EXTENSION_NAME={name}", "-DTORCH_API_INCLUDE_EXTENSION_H",
+                   f"-D_GLIBCXX_USE_CXX11_ABI={abi}"]
+    nvcc = _nvcc()
+    jobs = []
+    for src in cus:
+        obj = os.path.join(BUILD_DIR, os.path.basename(src) + ".o")
+        cmd = [nvcc, *NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", "--use_fast_math", "-Xcompiler", "-fPIC",
+               "-Xptxas", "-v" if verbose else "-O3", "-I", CSRC, "-c", src, "-o", obj]
+        jobs.append((cmd, obj))
+    for src in cpps:
+        obj = os.path.join(BUILD_DIR, os.path.basename(src) + ".o")
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", *common_defs, *incs, "-c", src, "-o", obj]
+        jobs.append((cmd, obj))
+    with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as pool:
+        logs = list(pool.map(lambda j: _run(j[0]), jobs))
+    if verbose:
+        for (cmd, _), log in zip(jobs, logs):
+            print(" ".join(cmd))
+            print(log)
+    libs = []
+    for p in ce.library_paths("cuda"):
+        libs += ["-L", p, f"-Wl,-rpath,{p}"]
+    link = ["g++", "-shared", "-o", so_path, *[j[1] for j in jobs], *libs,
+            "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python", "-lcudart"]
+    _run(link)
+    with open(so_path + ".hash", "w") as f:
+        f.write(digest)
+    return so_path
+
+
+_cuda_ext = None
+
+
+def load_cuda_extension():
+    """Import `_C`, building it first if it is missing or out of date."""
+    global _cuda_ext
+    if _cuda_ext is None:
+        import torch  # noqa: F401  (libtorch must be loaded before the extension)
+        _cuda_ext = _load("nanochat_b200._C", build_cuda_extension())
+    return _cuda_ext
+
+
+# -------------------------------------------------------------------------- tokenizer
+
+def build_tokenizer_extension(force=False):
+    import pybind11
+    name = "_tok"
+    so_path = os.path.join(PKG_DIR, name + EXT_SUFFIX)
+    srcs = sorted(glob.glob(os.path.join(TOK_SRC, "*.cpp")))
+    if not srcs:
+        raise FileNotFoundError("tokenizer sources not found")
+    headers = glob.glob(os.path.join(TOK_SRC, "*.h")) + glob.glob(os.path.join(TOK_SRC, "*.inc"))
+    digest = _hash_files(srcs + headers)
+    if not force and not _stale(so_path, digest):
+        return so_path
+    cmd = ["g++", "-O3", "-std=c++17", "-fPIC", "-shared", "-pthread", "-I", pybind11.get_include(),
+           "-I", sysconfig.get_paths()["include"], "-I", TOK_SRC, *srcs, "-o", so_path]
+    _run(cmd)
+    with open(so_path + ".hash", "w") as f:
+        f.write(digest)
+    return so_path
+
+
+_tok_ext = None
+
+
+def load_tokenizer_extension():
+    global _tok_ext
+    if _tok_ext is None:
+        _tok_ext = _load("nanochat_b200._tok", build_tokenizer_extension())
+    return _tok_ext
+
+
+def build_all(verbose=False, force=False):
+    out = [build_cuda_extension(verbose=verbose, force=force)]
+    try:
+        out.append(build_tokenizer_extension(force=force))
+    except FileNotFoundError:
+        pass
+    return out
+
+
+if __name__ == "__main__":
+    for path in build_all(verbose="-v" in sys.argv, force="-f" in sys.argv):
+        print("built", path)

@@ -1,0 +1,247 @@
+"""
+GPU numerics: every hand-written kernel against a plain PyTorch fp32 reference of the same op.
+"""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+BF16 = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def nat():
+    from nanochat_b200.ops import native
+    return native
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def _mk(shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, device="cuda", generator=g) * scale).to(BF16)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K,bn", [
+    (128, 256, 64, 256), (256, 208, 128, 208), (384, 128, 320, 128), (200, 72, 136, 64),
+    (96, 32, 64, 32), (1024, 1664, 1664, 0), (512, 4992, 1664, 0),
+])
+def test_gemm_layouts(nat, M, N, K, bn, a_mn, b_mn):
+    A = _mk((K, M) if a_mn else (M, K), seed=1)
+    B = _mk((K, N) if b_mn else (N, K), seed=2)
+    C = torch.empty(M, N, dtype=BF16, device="cuda")
+    nat.gemm(A, B, C, a_mn=a_mn, b_mn=b_mn, bn=bn)
+    Af = A.float().t() if a_mn else A.float()
+    Bf = B.float() if b_mn else B.float().t()
+    ref = Af @ Bf
+    nat.check_status(C)
+    assert _rel_err(C, ref) < 1e-2, (M, N, K, bn, a_mn, b_mn)
+
+
+def test_gemm_epilogues_and_fp32_accumulate(nat):
+    M, N, K = 512, 384, 256
+    A, B = _mk((M, K), seed=3), _mk((N, K), seed=4)
+    ref = A.float() @ B.float().t()
+    out = torch.empty(M, N, dtype=BF16, device="cuda")
+    nat.gemm(A, B, out, epi=nat.EPI_RELU2)
+    assert _rel_err(out, torch.relu(ref) ** 2) < 1e-2
+    aux = _mk((M, N), seed=5)
+    nat.gemm(A, B, out, aux=aux, alpha=0.5, beta=2.0)
+    assert _rel_err(out, 0.5 * ref + 2.0 * aux.float()) < 1e-2
+    pos = aux.float().abs().to(BF16)
+    nat.gemm(A, B, out, aux=pos, epi=nat.EPI_MUL2SQRT)
+    assert _rel_err(out, ref * 2 * pos.float().sqrt()) < 1e-2
+    # wgrad form: fp32 C += A^T B with both operands MN-major
+    dy, x = _mk((K, M), seed=6), _mk((K, N), seed=7)       # reduction dim first
+    acc = torch.randn(M, N, device="cuda")
+    want = acc + dy.float().t() @ x.float()
+    nat.gemm(dy, x, acc, a_mn=True, b_mn=True, aux=acc, beta=1.0)
+    nat.check_status(acc)
+    assert _rel_err(acc, want) < 2e-3
+
+
+def test_gemm_batched_and_strided(nat):
+    k, r, c = 5, 256, 384
+    X = _mk((k, r, c), seed=8)
+    A = torch.empty(k, r, r, dtype=BF16, device="cuda")
+    nat.gemm(X, X, A)
+    assert _rel_err(A, X.float() @ X.float().mT) < 1e-2
+    At = torch.empty(k, c, c, dtype=BF16, device="cuda")
+    nat.gemm(X, X, At, a_mn=True, b_mn=True)
+    assert _rel_err(At, X.float().mT @ X.float()) < 1e-2
+    # column-sliced output (ldc > N) as used by the unfused QKV path
+    big = torch.zeros(r, 3 * 128, dtype=BF16, device="cuda")
+    W = _mk((128, c), seed=9)
+    nat.gemm(X[0], W, big[:, 128:256])
+    assert _rel_err(big[:, 128:256], X[0].float() @ W.float().t()) < 1e-2
+    assert big[:, :128].abs().max().item() == 0 and big[:, 256:].abs().max().item() == 0
+    nat.check_status(big)
+
+
+def test_gemm_deterministic(nat):
+    A, B = _mk((1024, 512), seed=10), _mk((768, 512), seed=11)
+    o1 = torch.empty(1024, 768, dtype=BF16, device="cuda")
+    o2 = torch.empty_like(o1)
+    nat.gemm(A, B, o1)
+    nat.gemm(A, B, o2)
+    assert torch.equal(o1, o2)
+
+
+def _torch_layer_reference(model, x, x0, idx, i):
+    """One block through the reference op bodies (autograd-capable)."""
+    from nanochat_b200 import ops
+    ops.set_kernel_mode("torch")
+    try:
+        T = x.shape[1]
+        cos_sin = model.cos[:, :T], model.sin[:, :T]
+        from nanochat_b200.ops import reference as R
+        xm, xn = R.resid_mix_norm(x, x0, model.resid_lambdas[i], model.x0_lambdas[i])
+        ve_w = model.value_embeds[str(i)].weight if str(i) in model.value_embeds else None
+        return model.transformer.h[i](xm, xn, idx, ve_w, cos_sin, model.window_sizes[i], None)
+    finally:
+        ops.set_kernel_mode("native")
+
+
+def _tiny_model(n_layer=2, n_embd=256, n_head=2, seq=256, window="SL"):
+    from nanochat_b200.models.gpt import GPT, GPTConfig
+    cfg = GPTConfig(sequence_len=seq, vocab_size=2048, n_layer=n_layer, n_head=n_head, n_kv_head=n_head,
+                    n_embd=n_embd, window_pattern=window)
+    torch.manual_seed(0)
+    with torch.device("meta"):
+        m = GPT(cfg)
+    m.to_empty(device="cuda")
+    m.init_weights()
+    # projections are zero-initialised; randomise them so every gradient path carries signal
+    with torch.no_grad():
+        for blk in m.transformer.h:
+            blk.attn.c_proj.weight.normal_(0, 0.02)
+            blk.mlp.c_proj.weight.normal_(0, 0.02)
+        m.lm_head.weight.normal_(0, 0.05)
+        m.smear_lambda.fill_(0.3)
+    return m
+
+
+@pytest.mark.parametrize("layer", [0, 1])
+def test_layer_forward_backward_matches_reference(nat, layer):
+    m = _tiny_model()
+    B, T, C = 2, 256, 256
+    idx = torch.randint(0, 2048, (B, T), device="cuda")
+    x = _mk((B, T, C), seed=20).requires_grad_(True)
+    x0 = _mk((B, T, C), seed=21).requires_grad_(True)
+    ve_w = m.value_embeds[str(layer)].weight if str(layer) in m.value_embeds else None
+    cos_sin = m.cos[:, :T], m.sin[:, :T]
+    out = nat.layer_forward(m.transformer.h[layer], x, x0, idx, ve_w, cos_sin, m.window_sizes[layer],
+                            m.resid_lambdas, m.x0_lambdas, layer)
+    g = _mk((B, T, C), seed=22)
+    out.backward(g)
+    nat.check_status(out)
+    got = dict(out=out.detach().clone(), dx=x.grad.clone(), dx0=x0.grad.clone(),
+               dfc=m.transformer.h[layer].mlp.c_fc.weight.grad.clone(),
+               dq=m.transformer.h[layer].attn.c_q.weight.grad.clone(),
+               dv=m.transformer.h[layer].attn.c_v.weight.grad.clone(),
+               dlr=m.resid_lambdas.grad.clone(), dl0=m.x0_lambdas.grad.clone())
+    if ve_w is not None:
+        got["dve"] = ve_w.grad32.clone()
+        got["dwg"] = m.transformer.h[layer].attn.ve_gate.weight.grad.clone()
+    m.zero_grad(set_to_none=True)
+    x.grad = x0.grad = None
+    ref_out = _torch_layer_reference(m, x, x0, idx, layer)
+    ref_out.backward(g)
+    want = dict(out=ref_out.detach(), dx=x.grad, dx0=x0.grad,
+                dfc=m.transformer.h[layer].mlp.c_fc.weight.grad,
+                dq=m.transformer.h[layer].attn.c_q.weight.grad,
+                dv=m.transformer.h[layer].attn.c_v.weight.grad,
+                dlr=m.resid_lambdas.grad, dl0=m.x0_lambdas.grad)
+    if ve_w is not None:
+        want["dve"] = ve_w.grad
+        want["dwg"] = m.transformer.h[layer].attn.ve_gate.weight.grad
+    for key in got:
+        err = _rel_err(got[key], want[key])
+        assert err < 4e-2, f"{key}: rel err {err}"
+
+
+def test_model_loss_and_grads_match_torch_path(nat):
+    from nanochat_b200 import ops
+    m = _tiny_model(n_layer=4, window="SSSL")
+    B, T = 2, 256
+    idx = torch.randint(0, 2048, (B, T), device="cuda")
+    tgt = torch.randint(0, 2048, (B, T), device="cuda")
+    tgt[0, :7] = -1
+    loss = m(idx, tgt)
+    loss.backward()
+    nat.check_status(loss)
+    got = {n: (getattr(p, "grad32", None) if p.grad is None else p.grad).clone() for n, p in m.named_parameters()}
+    for p in m.parameters():
+        p.grad = None
+        if hasattr(p, "grad32"):
+            p.grad32.zero_()
+    ops.set_kernel_mode("torch")
+    try:
+        ref_loss = m(idx, tgt)
+        ref_loss.backward()
+    finally:
+        ops.set_kernel_mode("native")
+    assert abs(loss.item() - ref_loss.item()) < 2e-2, (loss.item(), ref_loss.item())
+    bad = []
+    for n, p in m.named_parameters():
+        err = _rel_err(got[n], p.grad)
+        if err > 8e-2:
+            bad.append((n, err))
+    assert not bad, bad
+    per_tok = m(idx, tgt, loss_reduction="none")
+    ops.set_kernel_mode("torch")
+    try:
+        ref_tok = m(idx, tgt, loss_reduction="none")
+    finally:
+        ops.set_kernel_mode("native")
+    assert per_tok.shape == ref_tok.shape
+    assert (per_tok - ref_tok).abs().max().item() < 5e-2
+    logits = m(idx)
+    assert logits.shape == (B, T, 2048) and logits.dtype == torch.float32
+
+
+def test_adamw_kernel_matches_reference(nat):
+    from nanochat_b200.ops import reference as R
+    for dtype in (torch.float32, BF16):
+        p = torch.randn(4096, 64, device="cuda").to(dtype)
+        g = torch.randn(4096, 64, device="cuda")
+        m1, v1 = torch.zeros_like(p), torch.zeros_like(p)
+        p2, m2, v2 = p.clone(), m1.clone(), v1.clone()
+        for step in range(1, 4):
+            nat.adamw_update(p, g, m1, v1, step, 0.01, 0.8, 0.95, 1e-10, 0.01)
+            R.adamw_update(p2, g, m2, v2, step, 0.01, 0.8, 0.95, 1e-10, 0.01)
+        tol = 1e-5 if dtype == torch.float32 else 2e-2
+        assert _rel_err(p, p2) < tol
+
+
+@pytest.mark.parametrize("shape", [(3, 256, 256), (2, 256, 512), (2, 512, 256)])
+def test_muon_kernel_matches_reference(nat, shape):
+    from nanochat_b200.ops import reference as R
+    k, r, c = shape
+    torch.manual_seed(1)
+    p = torch.randn(shape, device="cuda") * 0.02
+    g = torch.randn(shape, device="cuda")
+    mom = torch.zeros_like(p)
+    sec = torch.zeros((k, r, 1) if r >= c else (k, 1, c), device="cuda")
+    p2, g2, mom2, sec2 = p.clone(), g.clone(), mom.clone(), sec.clone()
+    red_dim = -1 if r >= c else -2
+    for _ in range(2):
+        nat.muon_update(g.clone(), p, mom, sec, 0.95, 0.02, 0.1, 0.9, 5, red_dim)
+        R.muon_update(g2.clone(), p2, mom2, sec2, 0.95, 0.02, 0.1, 0.9, 5, red_dim, use_bf16=True)
+    nat.check_status(p)
+    assert _rel_err(mom, mom2) < 1e-5
+    assert _rel_err(sec, sec2) < 5e-2
+    upd, upd2 = p - torch.randn_like(p) * 0, p2
+    assert _rel_err(p, p2) < 5e-2
+    # the first update must be close to semi-orthogonal
+    p3 = torch.zeros(1, r, c, device="cuda")
+    nat.muon_update(torch.randn(1, r, c, device="cuda"), p3, torch.zeros_like(p3),
+                    torch.zeros((1, r, 1) if r >= c else (1, 1, c), device="cuda"), 0.95, 1.0, 0.0, 0.9, 5, red_dim)
+    s = torch.linalg.svdvals(p3[0].float())
+    assert (s.max() / s.min()).item() < 4
