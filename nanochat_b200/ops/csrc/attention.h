@@ -20,4 +20,16 @@ struct AttnDesc {
 
 cudaError_t attention_fwd(const AttnDesc& d, int* status, cudaStream_t stream);
 
+// Backward: fwd holds q,k,v,o,lse and the problem geometry of the forward call. d_o like o; dq like q;
+// dk, dv like k, v (strides in elements). delta: (B, H, Tq) fp32 scratch written by the pre-pass.
+struct AttnBwdDesc {
+  AttnDesc fwd;
+  const void* d_o;
+  long long do_bat, do_tok, do_head;
+  void *dq, *dk, *dv;
+  long long dq_bat, dq_tok, dq_head, dk_bat, dk_tok, dk_head, dv_bat, dv_tok, dv_head;
+  float* delta;
+};
+cudaError_t attention_bwd(const AttnBwdDesc& d, int* status, cudaStream_t stream);
+
 }  // namespace nc

@@ -1,0 +1,415 @@
+// Flash attention backward for sm_100a (head dim 128, bf16, causal + optional left window).
+//
+// Two launches of one kernel template share a pipeline skeleton:
+//
+//   MODE_DKV  CTA = (128-key block, kv head, batch). Outer tiles X1 = K, X2 = V stay resident;
+//             the inner loop walks 64-query blocks (Y1 = Q, Y2 = dO) of every query head that
+//             shares the kv head. Scores are kept transposed (rows = keys):
+//               S'  = K Q^T,  dP' = V dO^T                      (tcgen05, TMEM 2 x 64 columns, double buffered)
+//               P'  = exp2(S' * c - lse_q),  dS' = P' * (dP' - delta_q)   (one thread per key row)
+//               dV += P' dO,  dK += dS' Q                        (A from the bf16 smem tile, B = Y tile MN-major)
+//   MODE_DQ   CTA = (128-query block, head, batch). X1 = Q, X2 = dO resident, inner 64-key blocks
+//             (Y1 = K, Y2 = V): S = Q K^T, dP = dO V^T, dS = P (dP - delta),  dQ += dS K.
+//
+// Recomputing S and dP in both launches costs 7 tile products instead of 5 but keeps every
+// accumulator in TMEM (no atomics, deterministic) and every operand in its natural layout.
+// delta = rowsum(dO * O) comes from a small pre-pass. All waits are bounded.
+#include "attention.h"
+#include "host_utils.cuh"
+#include "ptx.cuh"
+
+namespace nc {
+
+namespace ab {
+constexpr int BX = 128;                  // outer rows per CTA
+constexpr int BY = 64;                   // inner block
+constexpr int D = 128;
+constexpr int THREADS = 192;
+constexpr int X_HALF = 128 * 64 * 2;     // 16 KB box of an outer tile
+constexpr int X_TILE = 2 * X_HALF;       // 32 KB
+constexpr int Y_HALF = 64 * 64 * 2;      // 8 KB box of an inner tile
+constexpr int Y_TILE = 2 * Y_HALF;       // 16 KB
+constexpr int P_TILE = 128 * 64 * 2;     // 16 KB: 128 rows x 64 bf16 (one swizzle row each)
+// smem: X1, X2 | 2 stages x (Y1, Y2) | 2 x (P, dS)
+constexpr int SMEM_BYTES = 2 * X_TILE + 2 * 2 * Y_TILE + 2 * 2 * P_TILE + 1024 /*col vectors*/ + 1024 + 256;
+constexpr int TMEM_COLS = 512;
+constexpr int COL_S = 0, COL_DP = 128, COL_ACC1 = 256, COL_ACC2 = 384;
+}  // namespace ab
+
+struct AttnBwdArgs {
+  const float* lse;      // (B, H, Tq)
+  const float* delta;    // (B, H, Tq)
+  void* out1;            // MODE_DKV: dV ; MODE_DQ: dQ
+  void* out2;            // MODE_DKV: dK ; MODE_DQ: unused
+  long long o1_bat, o1_tok, o1_head, o2_bat, o2_tok, o2_head;
+  int Tq, Tk, H, Hkv;
+  int window;
+  float scale, scale_log2;
+  int* status;
+};
+
+template <bool DKV>
+__global__ void __launch_bounds__(ab::THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
+                const __grid_constant__ CUtensorMap tmY1, const __grid_constant__ CUtensorMap tmY2,
+                const AttnBwdArgs args) {
+  using namespace ab;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sX1 = smem;
+  uint8_t* sX2 = sX1 + X_TILE;
+  uint8_t* sY = sX2 + X_TILE;                     // stage s: Y1 at s*2*Y_TILE, Y2 right after
+  uint8_t* sPD = sY + 2 * 2 * Y_TILE;             // buffer b: P at b*2*P_TILE, dS right after
+  float* col_vec = reinterpret_cast<float*>(sPD + 2 * 2 * P_TILE);   // [2 buffers][2 (lse, delta)][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(col_vec) + 1024);
+  uint64_t* out_full = bars;
+  uint64_t* in_full = bars + 1;       // [2]
+  uint64_t* in_empty = bars + 3;      // [2]
+  uint64_t* s_full = bars + 5;        // [2]
+  uint64_t* s_free = bars + 7;        // [2]
+  uint64_t* p_ready = bars + 9;       // [2]
+  uint64_t* p_free = bars + 11;       // [2]
+  uint64_t* done = bars + 13;
+  uint64_t* cv_ready = bars + 14;     // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int xb = DKV ? blockIdx.x : (gridDim.x - 1 - blockIdx.x);
+  const int hx = blockIdx.y, b = blockIdx.z;       // DKV: kv head ; DQ: q head
+  const int group = args.H / args.Hkv;
+  const int x0 = xb * BX;
+  const int off = args.Tk - args.Tq;
+
+  // inner range [y_lo, y_hi] in 64-blocks, and the heads the inner loop covers
+  int lo, hi;
+  if (DKV) {
+    lo = x0 - off; if (lo < 0) lo = 0;
+    hi = args.window < 0 ? args.Tq - 1 : min(args.Tq - 1, x0 + BX - 1 + args.window - off);
+  } else {
+    lo = args.window < 0 ? 0 : max(0, x0 + off - args.window);
+    hi = min(args.Tk - 1, x0 + BX - 1 + off);
+  }
+  const int y_lo = lo / BY;
+  const int per_head = hi >= lo ? (hi / BY - y_lo + 1) : 0;
+  const int n_heads_inner = DKV ? group : 1;
+  const int n_items = per_head * n_heads_inner;
+  const int hkv = DKV ? hx : hx / group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(out_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&in_full[s], 1); mbar_init(&in_empty[s], 1); mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 4);
+      mbar_init(&p_ready[s], 4); mbar_init(&p_free[s], 1); mbar_init(&cv_ready[s], 4);
+    }
+    mbar_init(done, 1);
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmX1); tma_prefetch_desc(&tmX2); tma_prefetch_desc(&tmY1); tma_prefetch_desc(&tmY2);
+      const int head_x = DKV ? hkv : hx;
+      mbar_arrive_expect_tx(out_full, 2 * X_TILE);
+      tma_load_4d(sX1, &tmX1, out_full, 0, x0, head_x, b);
+      tma_load_4d(sX1 + X_HALF, &tmX1, out_full, 64, x0, head_x, b);
+      tma_load_4d(sX2, &tmX2, out_full, 0, x0, head_x, b);
+      tma_load_4d(sX2 + X_HALF, &tmX2, out_full, 64, x0, head_x, b);
+      for (int it = 0; it < n_items; ++it) {
+        const int s = it & 1; const uint32_t ph = (it >> 1) & 1;
+        const int hi_idx = it / per_head;
+        const int y0 = (y_lo + it - hi_idx * per_head) * BY;
+        const int head_y = DKV ? hkv * group + hi_idx : hkv;
+        if (!mbar_wait(&in_empty[s], ph ^ 1, abort_flag, args.status, ST_WAIT_EMPTY, it)) break;
+        uint8_t* y1 = sY + s * 2 * Y_TILE;
+        uint8_t* y2 = y1 + Y_TILE;
+        mbar_arrive_expect_tx(&in_full[s], 2 * Y_TILE);
+        tma_load_4d(y1, &tmY1, &in_full[s], 0, y0, head_y, b);
+        tma_load_4d(y1 + Y_HALF, &tmY1, &in_full[s], 64, y0, head_y, b);
+        tma_load_4d(y2, &tmY2, &in_full[s], 0, y0, head_y, b);
+        tma_load_4d(y2 + Y_HALF, &tmY2, &in_full[s], 64, y0, head_y, b);
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(BX, BY, false, false);
+      constexpr uint32_t idesc_acc = umma_idesc_bf16(BX, D, false, true);
+      const uint32_t x1 = smem_u32(sX1), x2 = smem_u32(sX2);
+      bool ok = mbar_wait(out_full, 0, abort_flag, args.status, ST_WAIT_FULL, 0xfff);
+      auto accumulate = [&](int i) -> bool {
+        const int bfr = i & 1; const uint32_t ph = (i >> 1) & 1;
+        if (!mbar_wait(&p_ready[bfr], ph, abort_flag, args.status, ST_WAIT_PEER, i)) return false;
+        tc_fence_after();
+        const uint32_t y1 = smem_u32(sY + bfr * 2 * Y_TILE), y2 = y1 + Y_TILE;
+        const uint32_t p = smem_u32(sPD + bfr * 2 * P_TILE), ds = p + P_TILE;
+#pragma unroll
+        for (int kk = 0; kk < BY / 16; ++kk) {
+          const uint64_t bdesc1 = umma_desc_sw128(y1 + kk * 2048, Y_HALF, 1024);   // Y1 as [red 64][out 128]
+          if (DKV) {
+            const uint64_t bdesc2 = umma_desc_sw128(y2 + kk * 2048, Y_HALF, 1024);
+            mma_f16(tmem_base + COL_ACC1, umma_desc_sw128(p + kk * 32, 16, 1024), bdesc2, idesc_acc, (i | kk) != 0);
+            mma_f16(tmem_base + COL_ACC2, umma_desc_sw128(ds + kk * 32, 16, 1024), bdesc1, idesc_acc, (i | kk) != 0);
+          } else {
+            mma_f16(tmem_base + COL_ACC1, umma_desc_sw128(ds + kk * 32, 16, 1024), bdesc1, idesc_acc, (i | kk) != 0);
+          }
+        }
+        mma_commit(&in_empty[bfr]);
+        mma_commit(&p_free[bfr]);
+        return true;
+      };
+      for (int it = 0; it < n_items && ok; ++it) {
+        const int s = it & 1; const uint32_t ph = (it >> 1) & 1;
+        if (!mbar_wait(&in_full[s], ph, abort_flag, args.status, ST_WAIT_FULL, it)) { ok = false; break; }
+        if (!mbar_wait(&s_free[s], ph ^ 1, abort_flag, args.status, ST_WAIT_TMEM_EMPTY, it)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t y1 = smem_u32(sY + s * 2 * Y_TILE), y2 = y1 + Y_TILE;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t xo = (kk >> 2) * X_HALF + (kk & 3) * 32;
+          const uint32_t yo = (kk >> 2) * Y_HALF + (kk & 3) * 32;
+          mma_f16(tmem_base + COL_S + s * BY, umma_desc_sw128(x1 + xo, 16, 1024), umma_desc_sw128(y1 + yo, 16, 1024),
+                  idesc_s, kk != 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t xo = (kk >> 2) * X_HALF + (kk & 3) * 32;
+          const uint32_t yo = (kk >> 2) * Y_HALF + (kk & 3) * 32;
+          mma_f16(tmem_base + COL_DP + s * BY, umma_desc_sw128(x2 + xo, 16, 1024), umma_desc_sw128(y2 + yo, 16, 1024),
+                  idesc_s, kk != 0);
+        }
+        mma_commit(&s_full[s]);
+        if (it > 0 && !accumulate(it - 1)) { ok = false; break; }
+      }
+      if (ok && n_items > 0) ok = accumulate(n_items - 1);
+      mma_commit(done);
+    }
+  } else {
+    // ------------------------------------------------------------------ compute
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int tid_c = threadIdx.x - 64;             // 0..127 among the compute threads
+    const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
+    const int xi = x0 + r;                          // DKV: key index ; DQ: query index
+    float row_lse = 0.f, row_delta = 0.f;
+    if (!DKV && xi < args.Tq) {
+      const long long o = ((long long)b * args.H + hx) * args.Tq + xi;
+      row_lse = args.lse[o] * 1.4426950408889634f;
+      row_delta = args.delta[o];
+    }
+    bool ok = true;
+    for (int it = 0; it < n_items && ok; ++it) {
+      const int s = it & 1; const uint32_t ph = (it >> 1) & 1;
+      const int hi_idx = it / per_head;
+      const int y0 = (y_lo + it - hi_idx * per_head) * BY;
+      float* cv = col_vec + s * 128;
+      float col_stat = 0.f;
+      if (DKV) {
+        // per-query (column) statistics of this inner block: fetched early, published to smem below
+        const int hq = hkv * group + hi_idx;
+        const int qi = y0 + (tid_c & 63);
+        if (qi < args.Tq) {
+          const long long o = ((long long)b * args.H + hq) * args.Tq + qi;
+          col_stat = tid_c < 64 ? args.lse[o] * 1.4426950408889634f : args.delta[o];
+        }
+      }
+      if (!mbar_wait(&s_full[s], ph, abort_flag, args.status, ST_WAIT_TMEM_FULL, it)) { ok = false; break; }
+      tc_fence_after();
+      uint32_t sv[64], dv[64];
+      {
+        uint32_t t32[32];
+        tmem_ld32(tmem_base + lane_sel + COL_S + s * BY, t32);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sv[j] = t32[j];
+        tmem_ld32(tmem_base + lane_sel + COL_S + s * BY + 32, t32);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) sv[32 + j] = t32[j];
+        tmem_ld32(tmem_base + lane_sel + COL_DP + s * BY, t32);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dv[j] = t32[j];
+        tmem_ld32(tmem_base + lane_sel + COL_DP + s * BY + 32, t32);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dv[32 + j] = t32[j];
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[s]);
+      // the tiles and column vectors of buffer s were last used by item it-2; its accumulate MMAs are done
+      // (and therefore every compute warp has finished that item) once p_free[s] flips
+      if (!mbar_wait(&p_free[s], ph ^ 1, abort_flag, args.status, ST_WAIT_EMPTY, 0x200 + it)) { ok = false; break; }
+      if (DKV) {
+        cv[tid_c] = col_stat;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&cv_ready[s]);
+        if (!mbar_wait(&cv_ready[s], ph, abort_flag, args.status, ST_WAIT_PEER, 0x400 + it)) { ok = false; break; }
+      }
+      uint8_t* prow = sPD + s * 2 * P_TILE + r * 128;
+      uint8_t* dsrow = prow + P_TILE;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        uint32_t pp[4], dd[4];
+#pragma unroll
+        for (int j2 = 0; j2 < 4; ++j2) {
+          float pv[2], dsv[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int c = u * 8 + j2 * 2 + e;
+            const int yi = y0 + c;
+            const int qi = DKV ? yi : xi;
+            const int kj = DKV ? xi : yi;
+            const float lse2 = DKV ? cv[c] : row_lse;
+            const float dl = DKV ? cv[64 + c] : row_delta;
+            const bool valid = (kj <= qi + off) && (args.window < 0 || qi + off - kj <= args.window) &&
+                               (kj < args.Tk) && (qi < args.Tq);
+            const float p = valid ? exp2f(__uint_as_float(sv[c]) * args.scale_log2 - lse2) : 0.f;
+            pv[e] = p;
+            dsv[e] = p * (__uint_as_float(dv[c]) - dl);
+          }
+          pp[j2] = pack_bf16(pv[0], pv[1]);
+          dd[j2] = pack_bf16(dsv[0], dsv[1]);
+        }
+        const int unit = u ^ (r & 7);
+        if (DKV) *reinterpret_cast<uint4*>(prow + unit * 16) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
+        *reinterpret_cast<uint4*>(dsrow + unit * 16) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_ready[s]);
+    }
+    // -------------------------------------------------------------- write-out
+    if (ok) ok = mbar_wait(done, 0, abort_flag, args.status, ST_WAIT_TMEM_FULL, 0x300);
+    tc_fence_after();
+    const int limit = DKV ? args.Tk : args.Tq;
+    if (ok && xi < limit) {
+      for (int which = 0; which < (DKV ? 2 : 1); ++which) {
+        const float mul = (DKV && which == 0) ? 1.f : args.scale;
+        __nv_bfloat16* orow =
+            which == 0 ? reinterpret_cast<__nv_bfloat16*>(args.out1) + (long long)b * args.o1_bat +
+                             (long long)xi * args.o1_tok + (long long)hx * args.o1_head
+                       : reinterpret_cast<__nv_bfloat16*>(args.out2) + (long long)b * args.o2_bat +
+                             (long long)xi * args.o2_tok + (long long)hx * args.o2_head;
+        const uint32_t col0 = which == 0 ? COL_ACC1 : COL_ACC2;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t v[32];
+          if (n_items > 0) {
+            tmem_ld32(tmem_base + lane_sel + col0 + c * 32, v);
+            tmem_wait_ld();
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = 0u;
+          }
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(v[j]) * mul, __uint_as_float(v[j + 1]) * mul);
+            w.y = pack_bf16(__uint_as_float(v[j + 2]) * mul, __uint_as_float(v[j + 3]) * mul);
+            w.z = pack_bf16(__uint_as_float(v[j + 4]) * mul, __uint_as_float(v[j + 5]) * mul);
+            w.w = pack_bf16(__uint_as_float(v[j + 6]) * mul, __uint_as_float(v[j + 7]) * mul);
+            *reinterpret_cast<uint4*>(orow + c * 32 + j) = w;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, ab::TMEM_COLS);
+  }
+}
+
+// delta[b,h,t] = sum_d dO * O ; one warp per (b,t,h) row
+__global__ void __launch_bounds__(128)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                  long long o_bat, long long o_tok, long long o_head, long long g_bat, long long g_tok,
+                  long long g_head, float* __restrict__ delta, int B, int T, int H) {
+  const int lane = threadIdx.x & 31;
+  const long long rows = (long long)B * T * H;
+  for (long long row = blockIdx.x * 4ll + (threadIdx.x >> 5); row < rows; row += gridDim.x * 4ll) {
+    const int h = (int)(row % H);
+    const long long bt = row / H;
+    const int t = (int)(bt % T);
+    const int b = (int)(bt / T);
+    const uint2 a = *reinterpret_cast<const uint2*>(o + b * o_bat + t * o_tok + h * o_head + lane * 4);
+    const uint2 g = *reinterpret_cast<const uint2*>(d_o + b * g_bat + t * g_tok + h * g_head + lane * 4);
+    float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), g0 = unpack_bf16(g.x), g1 = unpack_bf16(g.y);
+    float s = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
+#pragma unroll
+    for (int w = 16; w > 0; w >>= 1) s += __shfl_xor_sync(0xffffffffu, s, w);
+    if (lane == 0) delta[((long long)b * H + h) * T + t] = s;
+  }
+}
+
+static bool map4(CUtensorMap* m, const void* base, int T, int Hn, int B, long long tok, long long head,
+                 long long bat, int box_rows) {
+  uint64_t dims[4] = {128, (uint64_t)T, (uint64_t)Hn, (uint64_t)B};
+  uint64_t str[3] = {(uint64_t)tok * 2, (uint64_t)head * 2, (uint64_t)bat * 2};
+  uint32_t box[4] = {64, (uint32_t)box_rows, 1, 1};
+  return make_tmap(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims, str, box);
+}
+
+cudaError_t attention_bwd(const AttnBwdDesc& d, int* status, cudaStream_t stream) {
+  const AttnDesc& f = d.fwd;
+  if (f.D != 128 || f.H % f.Hkv != 0 || f.Tq > f.Tk) return cudaErrorInvalidValue;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ab::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ab::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  {
+    const long long rows = (long long)f.B * f.Tq * f.H;
+    const int grid = (int)((rows + 3) / 4 < 148 * 16 ? (rows + 3) / 4 : 148 * 16);
+    attn_delta_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)f.o, (const __nv_bfloat16*)d.d_o, f.o_bat,
+                                                f.o_tok, f.o_head, d.do_bat, d.do_tok, d.do_head, d.delta, f.B,
+                                                f.Tq, f.H);
+  }
+  CUtensorMap q128, do128, k128, v128, q64, do64, k64, v64;
+  bool okm = map4(&q128, f.q, f.Tq, f.H, f.B, f.q_tok, f.q_head, f.q_bat, 128) &&
+             map4(&do128, d.d_o, f.Tq, f.H, f.B, d.do_tok, d.do_head, d.do_bat, 128) &&
+             map4(&k128, f.k, f.Tk, f.Hkv, f.B, f.k_tok, f.k_head, f.k_bat, 128) &&
+             map4(&v128, f.v, f.Tk, f.Hkv, f.B, f.v_tok, f.v_head, f.v_bat, 128) &&
+             map4(&q64, f.q, f.Tq, f.H, f.B, f.q_tok, f.q_head, f.q_bat, 64) &&
+             map4(&do64, d.d_o, f.Tq, f.H, f.B, d.do_tok, d.do_head, d.do_bat, 64) &&
+             map4(&k64, f.k, f.Tk, f.Hkv, f.B, f.k_tok, f.k_head, f.k_bat, 64) &&
+             map4(&v64, f.v, f.Tk, f.Hkv, f.B, f.v_tok, f.v_head, f.v_bat, 64);
+  if (!okm) return cudaErrorInvalidValue;
+  AttnBwdArgs a;
+  a.lse = f.lse; a.delta = d.delta;
+  a.Tq = f.Tq; a.Tk = f.Tk; a.H = f.H; a.Hkv = f.Hkv; a.window = f.window;
+  a.scale = f.scale; a.scale_log2 = f.scale * 1.4426950408889634f;
+  a.status = status;
+  // dK, dV
+  a.out1 = d.dv; a.o1_bat = d.dv_bat; a.o1_tok = d.dv_tok; a.o1_head = d.dv_head;
+  a.out2 = d.dk; a.o2_bat = d.dk_bat; a.o2_tok = d.dk_tok; a.o2_head = d.dk_head;
+  dim3 grid_kv((f.Tk + ab::BX - 1) / ab::BX, f.Hkv, f.B);
+  attn_bwd_kernel<true><<<grid_kv, ab::THREADS, ab::SMEM_BYTES, stream>>>(k128, v128, q64, do64, a);
+  // dQ
+  a.out1 = d.dq; a.o1_bat = d.dq_bat; a.o1_tok = d.dq_tok; a.o1_head = d.dq_head;
+  a.out2 = nullptr;
+  dim3 grid_q((f.Tq + ab::BX - 1) / ab::BX, f.H, f.B);
+  attn_bwd_kernel<false><<<grid_q, ab::THREADS, ab::SMEM_BYTES, stream>>>(q128, do128, k64, v64, a);
+  return cudaGetLastError();
+}
+
+}  // namespace nc

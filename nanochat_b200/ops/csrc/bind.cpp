@@ -246,6 +246,30 @@ void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tens
   NC_CHECK(nc::attention_fwd(d, status_ptr(q), cur_stream()));
 }
 
+void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& lse,
+              const Tensor& d_o, Tensor& dq, Tensor& dk, Tensor& dv, Tensor& delta, int64_t window, double scale) {
+  const c10::cuda::CUDAGuard guard(q.device());
+  nc::AttnBwdDesc d{};
+  nc::AttnDesc& f = d.fwd;
+  f.B = (int)q.size(0); f.Tq = (int)q.size(1); f.H = (int)q.size(2); f.D = (int)q.size(3);
+  f.Tk = (int)k.size(1); f.Hkv = (int)k.size(2);
+  f.q = q.data_ptr(); f.k = k.data_ptr(); f.v = v.data_ptr(); f.o = const_cast<void*>(o.data_ptr());
+  f.lse = const_cast<float*>(lse.data_ptr<float>());
+  f.q_tok = q.stride(1); f.k_tok = k.stride(1); f.v_tok = v.stride(1); f.o_tok = o.stride(1);
+  f.q_bat = q.stride(0); f.k_bat = k.stride(0); f.v_bat = v.stride(0); f.o_bat = o.stride(0);
+  f.q_head = q.stride(2); f.k_head = k.stride(2); f.v_head = v.stride(2); f.o_head = o.stride(2);
+  f.window = (int)window; f.scale = (float)scale;
+  TORCH_CHECK(q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1 && o.stride(3) == 1 && d_o.stride(3) == 1 &&
+              dq.stride(3) == 1 && dk.stride(3) == 1 && dv.stride(3) == 1, "attention: head dim must be contiguous");
+  d.d_o = d_o.data_ptr(); d.do_bat = d_o.stride(0); d.do_tok = d_o.stride(1); d.do_head = d_o.stride(2);
+  d.dq = dq.data_ptr(); d.dq_bat = dq.stride(0); d.dq_tok = dq.stride(1); d.dq_head = dq.stride(2);
+  d.dk = dk.data_ptr(); d.dk_bat = dk.stride(0); d.dk_tok = dk.stride(1); d.dk_head = dk.stride(2);
+  d.dv = dv.data_ptr(); d.dv_bat = dv.stride(0); d.dv_tok = dv.stride(1); d.dv_head = dv.stride(2);
+  d.delta = delta.data_ptr<float>();
+  NC_CHECK(nc::attention_bwd(d, status_ptr(q), cur_stream()));
+  g_launches += 2;   // delta pre-pass + dK/dV kernel + dQ kernel
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -272,4 +296,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("muon_equilibrate", &muon_equilibrate);
   m.def("muon_finish", &muon_finish);
   m.def("attn_fwd", &attn_fwd);
+  m.def("attn_bwd", &attn_bwd);
 }

@@ -35,8 +35,9 @@ _C = load_cuda_extension()
 EPI_LINEAR, EPI_RELU2, EPI_MUL2SQRT = 0, 1, 2
 BF16 = torch.bfloat16
 
-# 'native' = tcgen05 flash attention kernels, 'sdpa' = PyTorch SDPA (bring-up / oracle)
-ATTENTION_IMPL = "sdpa"
+# 'native' = tcgen05 flash attention kernels, 'sdpa' = PyTorch SDPA (oracle for A/B runs)
+import os as _os
+ATTENTION_IMPL = _os.environ.get("NANOCHAT_ATTENTION", "native")
 
 
 def check_status(like=None):
@@ -55,7 +56,37 @@ def launch_count():
 
 # ----------------------------------------------------------------------------- shadows
 
-_shadow = weakref.WeakKeyDictionary()
+class _ShadowTable:
+    """id-keyed map from a weight to (version, bf16 copy, data_ptr); entries die with their weight."""
+
+    def __init__(self):
+        self._d = {}
+
+    def get(self, w):
+        ent = self._d.get(id(w))
+        if ent is None or ent[3]() is not w:
+            return None
+        return ent
+
+    def __contains__(self, w):
+        return self.get(w) is not None
+
+    def __getitem__(self, w):
+        ent = self.get(w)
+        if ent is None:
+            raise KeyError("no shadow for this tensor")
+        return ent
+
+    def set(self, w, version, buf):
+        key = id(w)
+        self._d[key] = (version, buf, w.data_ptr(), weakref.ref(w, lambda _r, k=key: self._d.pop(k, None)))
+
+    def discard(self, w):
+        if self.get(w) is not None:
+            del self._d[id(w)]
+
+
+_shadow = _ShadowTable()
 
 
 def shadow_of(w):
@@ -72,20 +103,22 @@ def shadow_of(w):
         _C.cast_f32_bf16(src, buf)
     else:
         buf.copy_(src)
-    _shadow[w] = (ver, buf, w.data_ptr())
+    _shadow.set(w, ver, buf)
     return buf
 
 
 def shadow_buffer(w):
     """The shadow tensor itself (created if needed) so an optimizer kernel can write it in place."""
+    if w.dtype == BF16:
+        return None
     shadow_of(w)
-    return _shadow[w][1] if w.dtype != BF16 else None
+    return _shadow[w][1]
 
 
 def mark_shadow_fresh(w):
     ent = _shadow.get(w)
     if ent is not None:
-        _shadow[w] = (w._version, ent[1], w.data_ptr())
+        _shadow.set(w, w._version, ent[1])
 
 
 # -------------------------------------------------------------------------------- GEMM
@@ -225,8 +258,8 @@ def _attention_sdpa_fwd(q, k, v, window):
 
 
 def attention_forward(q, k, v, window):
-    """Returns (y, lse); lse is None on the SDPA bring-up path."""
-    if ATTENTION_IMPL == "native":
+    """Returns (y, lse); lse is None on the SDPA path."""
+    if ATTENTION_IMPL == "native" and q.shape[-1] == 128 and q.shape[1] <= k.shape[1]:
         B, T, H, D = q.shape
         y = torch.empty(B, T, H, D, dtype=BF16, device=q.device)
         lse = torch.empty(B, H, T, dtype=torch.float32, device=q.device)
@@ -238,6 +271,12 @@ def attention_forward(q, k, v, window):
 def attention_backward(dy, q, k, v, y, lse, window, dqkv_views):
     """Writes dq, dk, dv into the given (strided) views."""
     dq_v, dk_v, dv_v = dqkv_views
+    if ATTENTION_IMPL == "native" and lse is not None:
+        B, T, H, D = q.shape
+        delta = torch.empty(B, H, T, dtype=torch.float32, device=q.device)
+        _C.attn_bwd(q, k, v, y, lse, dy, dq_v, dk_v, dv_v, delta,
+                    window if 0 <= window < k.shape[1] else -1, 1.0 / math.sqrt(D))
+        return
     with torch.enable_grad():
         q_ = q.detach().requires_grad_(True)
         k_ = k.detach().requires_grad_(True)
@@ -541,8 +580,8 @@ def adamw_update(p, grad, exp_avg, exp_avg_sq, step, lr, beta1, beta2, eps, wd, 
     _C.adamw_step(p, grad, exp_avg, exp_avg_sq, shadow, lr, beta1, beta2, eps, wd, step, 1.0)
     if shadow is not None:
         mark_shadow_fresh(owner)     # every rank's slice kernel keeps its part of the shadow current
-    elif owner in _shadow:
-        del _shadow[owner]           # written behind autograd's back: force a re-cast on next use
+    else:
+        _shadow.discard(owner)       # written behind autograd's back: force a re-cast on next use
 
 
 _muon_scratch = {}
@@ -607,8 +646,8 @@ def muon_update(grads, params_stack, momentum_buf, second_buf, momentum, lr, wd,
         for p in params:
             if shadow is not None:
                 mark_shadow_fresh(p)
-            elif p in _shadow:
-                del _shadow[p]
+            else:
+                _shadow.discard(p)
 
 
 def _contiguous_stack(ts):

@@ -1,0 +1,71 @@
+"""Best-fit packing (C++ vs Python oracle) and the parquet -> batch pipeline on a tiny local corpus."""
+import os
+import random
+
+import pyarrow as pa
+import pyarrow.parquet as pq
+import pytest
+import torch
+
+from nanochat_b200 import dataloader as dl
+
+
+def _docs(seed, n, lo=2, hi=300):
+    rng = random.Random(seed)
+    return [[rng.randrange(1000) for _ in range(rng.randint(lo, hi))] for _ in range(n)]
+
+
+def test_cpp_packer_matches_python_oracle():
+    tok = pytest.importorskip("nanochat_b200.utils.build").load_tokenizer_extension()
+    cap, buf = 129, 50
+    feed_a, feed_b = iter(_docs(1, 5000)), iter(_docs(1, 5000))
+    pool = []
+    packer = tok.BestFitPacker(cap, buf)
+    refill_py = lambda: pool.extend(next(feed_a) for _ in range(7))
+    refill_cpp = lambda: packer.add_documents([next(feed_b) for _ in range(7)])
+    for _ in range(5):
+        want = dl.pack_rows_python(pool, 8, cap, refill_py, buf)
+        got = torch.from_numpy(packer.pack(8, refill_cpp))
+        assert torch.equal(want, got)
+
+
+def test_rows_start_documents_and_are_full():
+    cap, buf = 65, 20
+    bos = 999999
+    feed = iter([[bos] + d for d in _docs(2, 3000, 1, 200)])
+    pool = []
+    rows = dl.pack_rows_python(pool, 16, cap, lambda: pool.append(next(feed)), buf)
+    assert rows.shape == (16, cap) and (rows[:, 0] == bos).all()
+
+
+class _ByteTok:
+    def get_bos_token_id(self):
+        return 256
+
+    def encode(self, texts, prepend=None, num_threads=1):
+        return [([prepend] if prepend is not None else []) + list(t.encode()) for t in texts]
+
+
+def test_loader_shapes_shift_and_resume_state(tmp_path, monkeypatch):
+    monkeypatch.setenv("NANOCHAT_BASE_DIR", str(tmp_path))
+    d = tmp_path / "base_data_climbmix"
+    os.makedirs(d)
+    rng = random.Random(0)
+    for shard in range(3):
+        texts = ["".join(rng.choice("abcdefgh ") for _ in range(rng.randint(5, 120))) for _ in range(64)]
+        pq.write_table(pa.table({"text": texts}), d / f"shard_{shard:05d}.parquet", row_group_size=16)
+    loader = dl.tokenizing_distributed_data_loader_with_state_bos_bestfit(
+        _ByteTok(), B=4, T=32, split="train", device="cpu", buffer_size=16, tokenizer_batch_size=8)
+    x, y, state = next(loader)
+    assert x.shape == (4, 32) and y.shape == (4, 32) and x.dtype == torch.long
+    assert torch.equal(x[:, 1:], y[:, :-1]) and (x[:, 0] == 256).all()
+    assert set(state) == {"pq_idx", "rg_idx", "epoch"} and state["epoch"] == 1
+    for _ in range(40):                      # runs past the two training shards -> next epoch
+        x, y, state = next(loader)
+    assert state["epoch"] >= 2
+    val = dl.tokenizing_distributed_data_loader_bos_bestfit(_ByteTok(), 2, 16, "val", device="cpu", buffer_size=8)
+    vx, vy = next(val)
+    assert vx.shape == (2, 16)
+    resumed = dl._document_batches("train", {"pq_idx": 1, "rg_idx": 1, "epoch": 3}, 8)
+    _, (pq_idx, rg_idx, epoch) = next(resumed)
+    assert (pq_idx, rg_idx, epoch) == (1, 2, 3)

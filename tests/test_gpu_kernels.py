@@ -245,3 +245,61 @@ def test_muon_kernel_matches_reference(nat, shape):
                     torch.zeros((1, r, 1) if r >= c else (1, 1, c), device="cuda"), 0.95, 1.0, 0.0, 0.9, 5, red_dim)
     s = torch.linalg.svdvals(p3[0].float())
     assert (s.max() / s.min()).item() < 4
+
+
+@pytest.mark.parametrize("B,T,H,Hkv,window", [
+    (2, 256, 2, 2, -1), (1, 512, 4, 4, 128), (2, 384, 4, 2, 256), (1, 1024, 2, 2, 256), (1, 200, 2, 1, 64),
+])
+def test_flash_attention_forward(nat, B, T, H, Hkv, window):
+    from nanochat_b200.ops import reference as R
+    D = 128
+    qkv = _mk((B, T, (H + 2 * Hkv) * D), seed=30)
+    q = qkv[..., :H * D].view(B, T, H, D)                      # strided views, as the layer uses them
+    k = qkv[..., H * D:(H + Hkv) * D].view(B, T, Hkv, D)
+    v = qkv[..., (H + Hkv) * D:].view(B, T, Hkv, D)
+    y = torch.empty(B, T, H, D, dtype=BF16, device="cuda")
+    lse = torch.empty(B, H, T, dtype=torch.float32, device="cuda")
+    nat._C.attn_fwd(q, k, v, y, lse, window, 1.0 / math.sqrt(D))
+    nat.check_status(y)
+    ref = R.attention(q.float(), k.float(), v.float(), window)
+    assert _rel_err(y, ref) < 2e-2
+    # log-sum-exp against an explicit computation
+    kk = k.float().repeat_interleave(H // Hkv, dim=2)
+    s = torch.einsum("bthd,bshd->bhts", q.float(), kk) / math.sqrt(D)
+    i = torch.arange(T, device="cuda")[:, None]
+    j = torch.arange(T, device="cuda")[None, :]
+    mask = j <= i
+    if window >= 0:
+        mask = mask & (i - j <= window)
+    s = s.masked_fill(~mask, float("-inf"))
+    assert (lse - torch.logsumexp(s, dim=-1)).abs().max().item() < 2e-2
+
+
+@pytest.mark.parametrize("B,T,H,Hkv,window", [
+    (2, 256, 2, 2, -1), (1, 512, 4, 4, 128), (2, 384, 4, 2, 256), (1, 200, 2, 1, 64), (1, 1024, 2, 2, 512),
+])
+def test_flash_attention_backward(nat, B, T, H, Hkv, window):
+    from nanochat_b200.ops import reference as R
+    D = 128
+    qkv = _mk((B, T, (H + 2 * Hkv) * D), seed=40)
+    q = qkv[..., :H * D].view(B, T, H, D)
+    k = qkv[..., H * D:(H + Hkv) * D].view(B, T, Hkv, D)
+    v = qkv[..., (H + Hkv) * D:].view(B, T, Hkv, D)
+    dy = _mk((B, T, H, D), seed=41)
+    y = torch.empty(B, T, H, D, dtype=BF16, device="cuda")
+    lse = torch.empty(B, H, T, dtype=torch.float32, device="cuda")
+    scale = 1.0 / math.sqrt(D)
+    nat._C.attn_fwd(q, k, v, y, lse, window, scale)
+    dqkv = torch.zeros_like(qkv)
+    dq = dqkv[..., :H * D].view(B, T, H, D)
+    dk = dqkv[..., H * D:(H + Hkv) * D].view(B, T, Hkv, D)
+    dv = dqkv[..., (H + Hkv) * D:].view(B, T, Hkv, D)
+    delta = torch.empty(B, H, T, dtype=torch.float32, device="cuda")
+    nat._C.attn_bwd(q, k, v, y, lse, dy, dq, dk, dv, delta, window, scale)
+    nat.check_status(y)
+    qf, kf, vf = (t.float().detach().requires_grad_(True) for t in (q, k, v))
+    ref = R.attention(qf, kf, vf, window)
+    ref.backward(dy.float())
+    assert _rel_err(dq, qf.grad) < 3e-2, "dq"
+    assert _rel_err(dk, kf.grad) < 3e-2, "dk"
+    assert _rel_err(dv, vf.grad) < 3e-2, "dv"
