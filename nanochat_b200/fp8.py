@@ -1,0 +1,170 @@
+"""
+FP8 linear layers for training.
+
+Public surface of the reference module (nanochat/fp8.py:195-266): `Float8Linear`,
+`Float8LinearConfig.from_recipe_name`, `convert_to_float8_training(module, config=, module_filter_fn=)`.
+The swapped-in module shares the original weight; evaluation code can switch all FP8 layers back to
+bf16 for the duration of a `with fp8_disabled(model):` block (what the reference does by swapping
+modules around its evaluations, scripts/base_train.py:195-240).
+
+Recipes
+  tensorwise  one dynamic scale per tensor: e4m3 inputs and weights in the forward GEMM, e5m2 output
+              gradients in the two backward GEMMs (the reference's only recipe). Runs on
+              `torch._scaled_mm`; kept as the numerical comparison point.
+  mxfp8       block scaling: every 32 consecutive elements along the reduction dim share one
+              power-of-two (E8M0) scale, so quantisation needs no global amax pass and can be fused
+              into the producer of the tensor. Executed by the tcgen05 block-scaled GEMM when the
+              extension provides it, otherwise emulated (quantise-dequantise to bf16 + bf16 GEMM)
+              so the numerics can be studied anywhere.
+`rowwise` is accepted by the command line of the reference but rejected here exactly as there.
+"""
+
+from contextlib import contextmanager
+
+import torch
+import torch.nn as nn
+
+from nanochat_b200 import common
+
+EPS = 1e-12
+
+
+@torch.no_grad()
+def _tensorwise_quant(x, dtype):
+    """(fp8 tensor, inverse scale) with scale = fp8_max / amax computed in float64."""
+    fmax = torch.finfo(dtype).max
+    amax = x.float().abs().max()
+    scale = (fmax / amax.double().clamp(min=EPS)).float()
+    q = (x.float() * scale).clamp(-fmax, fmax).to(dtype)
+    return q, scale.reciprocal()
+
+
+def _col_major(t):
+    return t.t().contiguous().t()
+
+
+class _TensorwiseMatmul(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x2, w):
+        xq, xs = _tensorwise_quant(x2, torch.float8_e4m3fn)
+        wq, ws = _tensorwise_quant(w, torch.float8_e4m3fn)
+        ctx.save_for_backward(xq, xs, wq, ws)
+        return torch._scaled_mm(xq, wq.t(), scale_a=xs, scale_b=ws, out_dtype=x2.dtype, use_fast_accum=True)
+
+    @staticmethod
+    def backward(ctx, dy):
+        xq, xs, wq, ws = ctx.saved_tensors
+        gq, gs = _tensorwise_quant(dy, torch.float8_e5m2)
+        dx = torch._scaled_mm(gq, _col_major(wq), scale_a=gs, scale_b=ws, out_dtype=dy.dtype, use_fast_accum=False)
+        dw = torch._scaled_mm(gq.t().contiguous(), _col_major(xq), scale_a=gs, scale_b=xs, out_dtype=dy.dtype,
+                              use_fast_accum=False)
+        return dx, dw
+
+
+@torch.no_grad()
+def mx_quant_dequant(x, dtype=torch.float8_e4m3fn, block=32):
+    """Round-trip through MXFP8: per 32-element block along the last dim, scale = 2^(floor(log2 amax) - emax)."""
+    shape = x.shape
+    xb = x.float().reshape(-1, block)
+    amax = xb.abs().amax(dim=1, keepdim=True).clamp_min(2.0 ** -127)
+    emax = 8 if dtype == torch.float8_e4m3fn else 15          # exponent of the largest power of two in range
+    scale = torch.exp2(torch.floor(torch.log2(amax)) - emax)
+    fmax = torch.finfo(dtype).max
+    q = (xb / scale).clamp(-fmax, fmax).to(dtype).float() * scale
+    return q.reshape(shape).to(x.dtype)
+
+
+class _MxEmulatedMatmul(torch.autograd.Function):
+    """MXFP8 numerics with bf16 GEMMs: operands are block-quantised along each GEMM's reduction dim."""
+
+    @staticmethod
+    def forward(ctx, x2, w):
+        ctx.save_for_backward(x2, w)
+        return mx_quant_dequant(x2) @ mx_quant_dequant(w.to(x2.dtype)).t()
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        wb = w.to(dy.dtype)
+        dx = mx_quant_dequant(dy, torch.float8_e5m2) @ mx_quant_dequant(wb.t().contiguous()).t()
+        dw = mx_quant_dequant(dy.t().contiguous(), torch.float8_e5m2) @ mx_quant_dequant(x2.t().contiguous()).t()
+        return dx, dw.to(w.dtype)
+
+
+class Float8Linear(nn.Linear):
+    """nn.Linear whose matmuls run in FP8; weights (and bias) keep their storage precision."""
+
+    recipe = "tensorwise"
+    fp8_enabled = True
+
+    def forward(self, input):
+        x = input.to(common.COMPUTE_DTYPE)
+        if not self.fp8_enabled:
+            from nanochat_b200 import ops
+            return ops.linear(x, self.weight)
+        x2 = x.reshape(-1, x.shape[-1])
+        if self.recipe == "mxfp8":
+            y = _MxEmulatedMatmul.apply(x2, self.weight)
+        else:
+            y = _TensorwiseMatmul.apply(x2, self.weight)
+        y = y.reshape(*x.shape[:-1], y.shape[-1])
+        if self.bias is not None:
+            y = y + self.bias.to(y.dtype)
+        return y
+
+    @classmethod
+    def from_float(cls, mod, recipe="tensorwise"):
+        with torch.device("meta"):
+            new = cls(mod.in_features, mod.out_features, bias=False)
+        new.weight = mod.weight
+        new.bias = mod.bias
+        new.recipe = recipe
+        return new
+
+
+class Float8LinearConfig:
+    def __init__(self, recipe="tensorwise"):
+        self.recipe = recipe
+
+    @staticmethod
+    def from_recipe_name(recipe_name):
+        if recipe_name not in ("tensorwise", "mxfp8"):
+            raise ValueError(f"Only 'tensorwise' and 'mxfp8' recipes are supported, got '{recipe_name}'.")
+        return Float8LinearConfig(recipe_name)
+
+
+def default_fp8_filter(mod, fqn):
+    """Both dims divisible by 16 and at least 128 (reference: scripts/base_train.py:178-185)."""
+    if not isinstance(mod, nn.Linear):
+        return False
+    if mod.in_features % 16 != 0 or mod.out_features % 16 != 0:
+        return False
+    return min(mod.in_features, mod.out_features) >= 128
+
+
+def convert_to_float8_training(module, *, config=None, module_filter_fn=None):
+    """Swap matching nn.Linear children (post-order) for Float8Linear sharing the same parameters."""
+    recipe = config.recipe if config is not None else "tensorwise"
+
+    def walk(mod, prefix=""):
+        for name, child in mod.named_children():
+            fqn = f"{prefix}.{name}" if prefix else name
+            walk(child, fqn)
+            if isinstance(child, nn.Linear) and not isinstance(child, Float8Linear):
+                if module_filter_fn is None or module_filter_fn(child, fqn):
+                    setattr(mod, name, Float8Linear.from_float(child, recipe))
+    walk(module)
+    return module
+
+
+@contextmanager
+def fp8_disabled(model):
+    """Run every Float8Linear of `model` as a bf16 linear inside the block."""
+    mods = [m for m in model.modules() if isinstance(m, Float8Linear)]
+    for m in mods:
+        m.fp8_enabled = False
+    try:
+        yield
+    finally:
+        for m in mods:
+            m.fp8_enabled = True

@@ -27,6 +27,9 @@ inline PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
 inline bool make_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base,
                       const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                       CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+  // Driver entry points need a current context on the calling thread; autograd's worker threads have
+  // none until their first runtime call, so make the primary context current here.
+  cudaFree(nullptr);
   auto enc = tensor_map_encoder();
   if (!enc) return false;
   cuuint64_t gdim[5];
