@@ -291,7 +291,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
     if (ok) ok = mbar_wait(done, 0, abort_flag, args.status, ST_WAIT_TMEM_FULL, 0x300);
     tc_fence_after();
     const int limit = DKV ? args.Tk : args.Tq;
-    if (ok && xi < limit) {
+    // tcgen05.ld is warp-collective: every lane of the warp runs the loads, only the stores are predicated
+    const bool warp_ok = __all_sync(0xffffffffu, ok);
+    const bool store_row_ok = xi < limit;
+    if (warp_ok) {
       for (int which = 0; which < (DKV ? 2 : 1); ++which) {
         const float mul = (DKV && which == 0) ? 1.f : args.scale;
         __nv_bfloat16* orow =
@@ -317,7 +320,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
             w.y = pack_bf16(__uint_as_float(v[j + 2]) * mul, __uint_as_float(v[j + 3]) * mul);
             w.z = pack_bf16(__uint_as_float(v[j + 4]) * mul, __uint_as_float(v[j + 5]) * mul);
             w.w = pack_bf16(__uint_as_float(v[j + 6]) * mul, __uint_as_float(v[j + 7]) * mul);
-            *reinterpret_cast<uint4*>(orow + c * 32 + j) = w;
+            if (store_row_ok) *reinterpret_cast<uint4*>(orow + c * 32 + j) = w;
           }
         }
       }

@@ -6,6 +6,7 @@
 #include <c10/cuda/CUDAGuard.h>
 
 #include "attention.h"
+#include "comm.h"
 #include "fused.h"
 #include "gemm.h"
 #include "optim.h"
@@ -270,6 +271,58 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   g_launches += 2;   // delta pre-pass + dK/dV kernel + dQ kernel
 }
 
+// ------------------------------------------------------------------ peer-to-peer optimizer
+nc::PeerPtrs peer_ptrs(const std::vector<int64_t>& v) {
+  TORCH_CHECK((int)v.size() <= nc::MAX_RANKS, "too many ranks");
+  nc::PeerPtrs p{};
+  for (size_t i = 0; i < v.size(); ++i) p.p[i] = reinterpret_cast<void*>(v[i]);
+  return p;
+}
+nc::AdamWArgs adamw_args(double lr, double beta1, double beta2, double eps, double wd, int64_t step) {
+  nc::AdamWArgs a;
+  a.lr = (float)lr; a.beta1 = (float)beta1; a.beta2 = (float)beta2; a.eps = (float)eps; a.wd = (float)wd;
+  a.bias1 = (float)(1.0 - std::pow(beta1, (double)step));
+  a.bias2 = (float)(1.0 - std::pow(beta2, (double)step));
+  a.grad_scale = 1.f;
+  return a;
+}
+void p2p_barrier(const std::vector<int64_t>& pads, int64_t rank, int64_t epoch, const Tensor& like) {
+  const c10::cuda::CUDAGuard guard(like.device());
+  NC_CHECK(nc::p2p_barrier(peer_ptrs(pads), (int)rank, (int)pads.size(), (int)epoch, status_ptr(like), cur_stream()));
+}
+void p2p_adamw(const std::vector<int64_t>& grads, int64_t grad_off, int64_t rank, Tensor& p, Tensor& m, Tensor& v,
+               const std::vector<int64_t>& out, int64_t out_off, bool write_local_out, double lr, double beta1,
+               double beta2, double eps, double wd, int64_t step) {
+  const c10::cuda::CUDAGuard guard(p.device());
+  TORCH_CHECK(p.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "p2p_adamw: contiguous slices");
+  NC_CHECK(nc::p2p_adamw(peer_ptrs(grads), (size_t)grad_off, (int)grads.size(), (int)rank, p.data_ptr(),
+                         p.scalar_type() == at::kBFloat16, m.data_ptr(), v.data_ptr(), peer_ptrs(out), (size_t)out_off,
+                         write_local_out, (size_t)p.numel(), adamw_args(lr, beta1, beta2, eps, wd, step), cur_stream()));
+}
+void p2p_muon_momentum(const std::vector<int64_t>& grads, int64_t grad_off, Tensor& buf, Tensor& X, Tensor& rowss,
+                       Tensor& total, double mu) {
+  const c10::cuda::CUDAGuard guard(buf.device());
+  NC_CHECK(nc::p2p_muon_momentum(peer_ptrs(grads), (size_t)grad_off, (int)grads.size(), buf.data_ptr<float>(),
+                                 X.data_ptr(), rowss.data_ptr<float>(), (float)mu, (int)X.size(0), (int)X.size(1),
+                                 (int)X.size(2), cur_stream()));
+  // per-matrix totals of the row sums (same reduction the single-GPU path uses)
+  Tensor t = rowss.view({X.size(0), X.size(1)}).sum(1);
+  total.copy_(t);
+}
+void p2p_bcast_bf16(const Tensor& src, const std::vector<int64_t>& dst, int64_t dst_off, int64_t rank) {
+  const c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.is_contiguous() && src.scalar_type() == at::kBFloat16, "p2p_bcast: contiguous bf16");
+  NC_CHECK(nc::p2p_bcast_bf16(src.data_ptr(), peer_ptrs(dst), (size_t)dst_off, (int)dst.size(), (int)rank,
+                              (size_t)src.numel(), cur_stream()));
+}
+void p2p_small_adamw(const std::vector<int64_t>& grads, int64_t grad_off, Tensor& p, Tensor& m, Tensor& v, double lr,
+                     double beta1, double beta2, double eps, double wd, int64_t step) {
+  const c10::cuda::CUDAGuard guard(p.device());
+  NC_CHECK(nc::p2p_small_adamw(peer_ptrs(grads), (size_t)grad_off, (int)grads.size(), p.data_ptr<float>(),
+                               m.data_ptr<float>(), v.data_ptr<float>(), (int)p.numel(),
+                               adamw_args(lr, beta1, beta2, eps, wd, step), cur_stream()));
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -295,6 +348,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("muon_momentum", &muon_momentum);
   m.def("muon_equilibrate", &muon_equilibrate);
   m.def("muon_finish", &muon_finish);
+  m.def("p2p_barrier", &p2p_barrier);
+  m.def("p2p_adamw", &p2p_adamw);
+  m.def("p2p_muon_momentum", &p2p_muon_momentum);
+  m.def("p2p_bcast_bf16", &p2p_bcast_bf16);
+  m.def("p2p_small_adamw", &p2p_small_adamw);
   m.def("attn_fwd", &attn_fwd);
   m.def("attn_bwd", &attn_bwd);
 }

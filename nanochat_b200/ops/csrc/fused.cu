@@ -233,10 +233,13 @@ backout_norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat1
 // Buffer layout per token: [ q: H heads | k: Hkv heads | v: Hkv heads ] x 128 dims, row pitch `ld`.
 // Eight lanes own one head: lane s holds dims [8s, 8s+8) and [64+8s, 64+8s+8), so the
 // rotation pairs (d, d+64) are lane-local and the norm reduces over 8 lanes.
-__device__ __forceinline__ float group8_sum(float v) {
-  v += __shfl_xor_sync(0xffffffffu, v, 1);
-  v += __shfl_xor_sync(0xffffffffu, v, 2);
-  v += __shfl_xor_sync(0xffffffffu, v, 4);
+// Sum over the 8 lanes of one head group. The four groups of a warp may sit in different branches
+// (rotary head / value head / idle), so the shuffle names only the group's own lanes.
+__device__ __forceinline__ float group8_sum(float v, int grp) {
+  const unsigned mask = 0xffu << (grp * 8);
+  v += __shfl_xor_sync(mask, v, 1);
+  v += __shfl_xor_sync(mask, v, 2);
+  v += __shfl_xor_sync(mask, v, 4);
   return v;
 }
 
@@ -285,7 +288,7 @@ qkv_post_fwd_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, int H, int Hk
           a[j] = y1; b[j] = y2;
           ss += y1 * y1 + y2 * y2;
         }
-        ss = group8_sum(ss);
+        ss = group8_sum(ss, grp);
         const float rstd = rsqrtf(ss * (1.f / 128.f) + RMS_EPS);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -360,7 +363,7 @@ qkv_post_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __res
           ga[j] *= 1.2f; gb[j] *= 1.2f;                     // grad wrt xhat
           dot += ga[j] * ya[j] + gb[j] * yb[j];
         }
-        dot = group8_sum(dot) * (1.f / 128.f);
+        dot = group8_sum(dot, grp) * (1.f / 128.f);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           const float d1 = rstd * (ga[j] - ya[j] * dot);    // grad wrt rotated values
@@ -385,7 +388,7 @@ qkv_post_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __res
         float dg = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) dg += ga[j] * ea[j] + gb[j] * eb[j];
-        dg = group8_sum(dg);
+        dg = group8_sum(dg, grp);
         float* dst = dve + erow;
 #pragma unroll
         for (int j = 0; j < 8; j += 4) {

@@ -139,6 +139,9 @@ def _accumulate_wgrad(w, dy2, x2):
     if w.grad is None:
         w.grad = torch.empty_like(w, dtype=w.dtype)
         gemm(dy2, x2, w.grad, a_mn=True, b_mn=True)
+    elif getattr(w, "_grad_fresh", False):      # persistent arena buffer, first write of this step
+        gemm(dy2, x2, w.grad, a_mn=True, b_mn=True)
+        w._grad_fresh = False
     else:
         gemm(dy2, x2, w.grad, a_mn=True, b_mn=True, aux=w.grad, beta=1.0)
 
@@ -471,9 +474,15 @@ class _LayerFn(Function):
             gemm(dqkv[:, nq + nkv:], sv, dxn, b_mn=True, aux=dxn, beta=1.0)
         fused_g = None
         if all(w.grad is not None for w in (wq, wk, wv)):
-            fused_g = _contiguous_rows([wq.grad, wk.grad, wv.grad])
+            fresh = [getattr(w, "_grad_fresh", False) for w in (wq, wk, wv)]
+            if all(fresh) or not any(fresh):
+                fused_g = _contiguous_rows([wq.grad, wk.grad, wv.grad])
         if fused_g is not None:
-            gemm(dqkv, xn, fused_g, a_mn=True, b_mn=True, aux=fused_g, beta=1.0)
+            if fresh[0]:
+                gemm(dqkv, xn, fused_g, a_mn=True, b_mn=True)
+                wq._grad_fresh = wk._grad_fresh = wv._grad_fresh = False
+            else:
+                gemm(dqkv, xn, fused_g, a_mn=True, b_mn=True, aux=fused_g, beta=1.0)
         else:
             _accumulate_wgrad(wq, dqkv[:, :nq], xn)
             _accumulate_wgrad(wk, dqkv[:, nq:nq + nkv], xn)

@@ -74,7 +74,8 @@ class MuonAdamW(torch.optim.Optimizer):
             grad32 = getattr(p, "grad32", None)   # fp32 accumulator kept by the native embedding kernels
             if grad32 is not None:
                 grad = grad32
-                self._consumed.append(grad32)
+                if getattr(p, "_arena", None) is None:
+                    self._consumed.append(grad32)     # an arena clears its own buffers
             if comm.world == 1:
                 jobs.append((p, shard, grad, None))
             elif shard.replicated:

@@ -1,0 +1,257 @@
+"""
+Fused peer-to-peer optimizer path for one NVSwitch domain (2-8 GPUs).
+
+Replaces the optimizer's NCCL collectives (reference: nanochat/optim.py:274-318 reduces,
+:359,407-417 gathers) by kernels that read and write the other ranks' memory directly:
+
+  * gradients, bf16 weight shadows and bf16 embedding tables live in two symmetric pools
+    (`torch.distributed._symmetric_memory` allocates and exchanges the mappings; every rank
+    has the same layout at the same offsets);
+  * reduce-scatter + update + all-gather of an AdamW tensor is ONE kernel over the rank's row
+    slice (`p2p_adamw`): pull the slice of all N gradients over NVLink, average in rank order,
+    apply AdamW to the local state, store the new bf16 values into all N shadows / tables;
+  * a Muon group pulls and averages the gradients of the matrices this rank owns inside the
+    momentum kernel (`p2p_muon_momentum`), runs the polar iteration locally on the tcgen05
+    GEMM, and broadcasts the updated bf16 shadows to the peers (`p2p_bcast_bf16`);
+  * replicated small parameters average all ranks' gradients themselves (`p2p_small_adamw`);
+  * two device-side barriers per step (bounded waits, status word) bracket the phase.
+
+What crosses NVLink per step is therefore fp32 gradients in (as in the reference) but bf16
+parameters out (half of the reference's fp32 all-gather). The fp32 masters stay with their
+owners; `sync_masters()` makes every replica's masters consistent on demand (checkpointing),
+using NCCL broadcasts since that is rare and off the hot path.
+
+Ownership, optimizer state layout and hyper-parameters are the reference's, so per-rank
+optimizer checkpoints remain interchangeable with the NCCL path.
+"""
+
+import torch
+import torch.distributed as dist
+
+from nanochat_b200.parallel.ownership import adamw_shard, muon_shard
+
+_ALIGN = 256
+
+
+class _Pool:
+    """A symmetric byte pool with a bump allocator; `peer_ptrs` are the N mapped base addresses."""
+
+    def __init__(self, nbytes, device, group):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        self.handle = symm_mem.rendezvous(self.buf, group=group.group_name if hasattr(group, "group_name") else group)
+        self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.used = 0
+
+    def take(self, shape, dtype):
+        n = 1
+        for s in shape:
+            n *= s
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        start = (self.used + _ALIGN - 1) // _ALIGN * _ALIGN
+        assert start + nbytes <= self.buf.numel(), "symmetric pool exhausted"
+        self.used = start + nbytes
+        return self.buf[start:start + nbytes].view(dtype).view(*shape)
+
+    def offset_of(self, t, dtype_size):
+        """Offset of tensor `t` from the pool base, in elements of `dtype_size` bytes."""
+        off = t.data_ptr() - self.buf.data_ptr()
+        assert 0 <= off < self.buf.numel() and off % dtype_size == 0
+        return off // dtype_size
+
+
+def _pool_sizes(model):
+    """Bytes needed in the gradient pool (fp32) and the bf16 pool (shadows + tables + pad)."""
+    grad = bf16 = 0
+    pad = lambda n: (n + _ALIGN - 1) // _ALIGN * _ALIGN + _ALIGN
+    matrix_params = list(model.transformer.h.parameters())
+    for shape in {p.shape for p in matrix_params}:
+        k = sum(1 for p in matrix_params if p.shape == shape)
+        n = k * shape[0] * shape[1]
+        grad += pad(4 * n)
+        bf16 += pad(2 * n)
+    big = [model.lm_head.weight, model.transformer.wte.weight] + [ve.weight for ve in model.value_embeds.values()]
+    for p in big:
+        grad += pad(4 * p.numel())
+        bf16 += pad(2 * p.numel())
+    seen = {id(p) for p in matrix_params} | {id(p) for p in big}
+    for p in model.parameters():
+        if id(p) not in seen:
+            grad += pad(4 * p.numel())
+    return grad + 4096, bf16 + 4096
+
+
+class SymmComm:
+    """Communicator whose `fused_step` runs the whole sharded optimizer step with in-kernel NVLink traffic."""
+
+    fused = True
+
+    def __init__(self, model, group=None):
+        from nanochat_b200 import ops
+        from nanochat_b200.parallel.arena import ParamArena
+        assert dist.is_initialized() and dist.get_world_size(group) > 1
+        self.group = group if group is not None else dist.group.WORLD
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        assert self.world <= 8, "one NVSwitch domain: at most 8 ranks"
+        self.nat = ops.native_module()
+        dev = model.get_device()
+        grad_bytes, bf16_bytes = _pool_sizes(model)
+        self.grad_pool = _Pool(grad_bytes, dev, self.group)
+        self.bf16_pool = _Pool(bf16_bytes, dev, self.group)
+        self.pad_pool = _Pool(4096, dev, self.group)
+        self.pad_pool.buf.zero_()
+        self.epoch = 0
+
+        def alloc(shape, dtype, device, role="master"):
+            if role == "grad":
+                return self.grad_pool.take(shape, dtype)
+            if role in ("shadow", "table"):
+                return self.bf16_pool.take(shape, dtype)
+            return torch.empty(shape, dtype=dtype, device=device)
+
+        self.arena = ParamArena(model, alloc=alloc, with_shadows=True)
+        self._fallback = None
+        torch.cuda.synchronize()
+        dist.barrier(group)
+
+    @classmethod
+    def create(cls, model, group=None):
+        return cls(model, group)
+
+    # TorchDistComm surface for the pieces that stay on NCCL (tiny Muon groups)
+    def _nccl(self):
+        if self._fallback is None:
+            from nanochat_b200.parallel.comm import TorchDistComm
+            self._fallback = TorchDistComm(None if self.group is dist.group.WORLD else self.group)
+        return self._fallback
+
+    def barrier(self):
+        self.epoch += 1
+        self.nat._C.p2p_barrier(self.pad_pool.peer_ptrs, self.rank, self.epoch, self.pad_pool.buf)
+
+    # ------------------------------------------------------------------ the fused step
+    def _entry_of(self, p):
+        for d in self.arena.adamw_big:
+            if d["param"] is p:
+                return d
+        return None
+
+    @torch.no_grad()
+    def fused_step(self, opt):
+        C = self.nat._C
+        gp, bp = self.grad_pool, self.bf16_pool
+        self.barrier()                                   # every rank's gradients are complete
+        for group in opt.param_groups:
+            if group["kind"] == "adamw":
+                self._adamw_group(opt, group, C, gp, bp)
+            else:
+                self._muon_group(opt, group, C, gp, bp)
+        self.barrier()                                   # write-backs landed; peers are done reading my grads
+        for g in self.arena.muon_groups:
+            if g["shadow"] is not None:
+                for p in g["params"]:
+                    self.nat.mark_shadow_fresh(p)
+        for d in self.arena.adamw_big:
+            if d["shadow"] is not None:
+                self.nat.mark_shadow_fresh(d["param"])
+
+    def _adamw_group(self, opt, group, C, gp, bp):
+        b1, b2 = group["betas"]
+        for p in group["params"]:
+            shard = adamw_shard(tuple(p.shape), self.rank, self.world)
+            state = opt.state[p]
+            if shard.replicated:
+                if not state:
+                    state["step"] = 0
+                    state["exp_avg"] = torch.zeros_like(p)
+                    state["exp_avg_sq"] = torch.zeros_like(p)
+                state["step"] += 1
+                C.p2p_small_adamw(gp.peer_ptrs, gp.offset_of(p.grad, 4), p.data, state["exp_avg"], state["exp_avg_sq"],
+                                  group["lr"], b1, b2, group["eps"], group["weight_decay"], state["step"])
+                continue
+            entry = self._entry_of(p)
+            cols = p.shape[1]
+            p_slice = p.data[shard.row_start:shard.row_end]
+            if not state:
+                state["step"] = 0
+                state["exp_avg"] = torch.zeros_like(p_slice)
+                state["exp_avg_sq"] = torch.zeros_like(p_slice)
+            state["step"] += 1
+            grad_off = gp.offset_of(entry["grad"], 4) + shard.row_start * cols
+            if p.dtype == torch.bfloat16:      # the table itself is the bf16 tensor every rank reads
+                out_off = bp.offset_of(p.data, 2) + shard.row_start * cols
+                write_local = False            # the kernel already wrote p_slice in place
+            else:
+                out_off = bp.offset_of(entry["shadow"], 2) + shard.row_start * cols
+                write_local = True
+            C.p2p_adamw(gp.peer_ptrs, grad_off, self.rank, p_slice, state["exp_avg"], state["exp_avg_sq"],
+                        bp.peer_ptrs, out_off, write_local, group["lr"], b1, b2, group["eps"],
+                        group["weight_decay"], state["step"])
+
+    def _muon_group(self, opt, group, C, gp, bp):
+        params = group["params"]
+        p0 = params[0]
+        r, c = p0.shape
+        entry = next(g for g in self.arena.muon_groups if g["params"][0] is p0)
+        if r % 8 or c % 8:
+            # tiny gate matrices (a few KB): average with NCCL and use the generic sharded update
+            info = opt._launch_muon(group, self._nccl())
+            gathers = []
+            opt._finish_muon(group, info, self._nccl(), gathers)
+            for work, stacked, ps in gathers:
+                work.wait()
+                torch._foreach_copy_([p.data for p in ps], list(stacked[:len(ps)].unbind(0)))
+            return
+        shard = muon_shard(len(params), self.rank, self.world)
+        state = opt.state[p0]
+        if "momentum_buffer" not in state:
+            state["momentum_buffer"] = torch.zeros(shard.chunk, r, c, dtype=p0.dtype, device=p0.device)
+            sshape = (shard.chunk, r, 1) if r >= c else (shard.chunk, 1, c)
+            state["second_momentum_buffer"] = torch.zeros(sshape, dtype=p0.dtype, device=p0.device)
+        n = shard.num_owned
+        if n == 0:
+            return
+        nat = self.nat
+        dev = p0.device
+        X = nat._scratch("muon_X", (n, r, c), torch.bfloat16, dev)
+        rowss = nat._scratch("muon_rowss", (n * r,), torch.float32, dev)
+        rowss2 = nat._scratch("muon_rowss2", (n * r,), torch.float32, dev)
+        total = nat._scratch("muon_total", (n,), torch.float32, dev)
+        total2 = nat._scratch("muon_total2", (n,), torch.float32, dev)
+        grad_off = gp.offset_of(entry["grad"], 4) + shard.start * r * c
+        C.p2p_muon_momentum(gp.peer_ptrs, grad_off, state["momentum_buffer"][:n], X, rowss, total, group["momentum"])
+        C.muon_equilibrate(X, rowss, total, rowss2, total2)
+        Xo = nat.polar_express_native(X, group["ns_steps"])
+        m = max(r, c)
+        ss = nat._scratch("muon_ss", (n * m,), torch.float32, dev)
+        scale = nat._scratch("muon_scale", (n * m,), torch.float32, dev)
+        lr = group["lr"] * max(1.0, r / c) ** 0.5
+        master = entry["master"][shard.start:shard.start + n]
+        shadow = entry["shadow"][shard.start:shard.start + n]
+        C.muon_finish(master, Xo, state["second_momentum_buffer"][:n].view(n, -1), ss, scale, shadow, lr,
+                      group["weight_decay"], group["beta2"])
+        out_off = bp.offset_of(entry["shadow"], 2) + shard.start * r * c
+        C.p2p_bcast_bf16(shadow, bp.peer_ptrs, out_off, self.rank)
+
+    # ---------------------------------------------------------------- master consistency
+    @torch.no_grad()
+    def sync_masters(self):
+        """Make every rank's fp32 masters equal to their owners' (before saving a full-model checkpoint)."""
+        for g in self.arena.muon_groups:
+            K = len(g["params"])
+            if g["shape"][0] % 8 or g["shape"][1] % 8:
+                continue                     # tiny groups are gathered by the NCCL path every step
+            chunk = -(-K // self.world)
+            for owner in range(self.world):
+                lo, hi = owner * chunk, min(K, (owner + 1) * chunk)
+                if lo < hi:
+                    dist.broadcast(g["master"][lo:hi], src=dist.get_global_rank(self.group, owner), group=self.group)
+        for d in self.arena.adamw_big:
+            p = d["param"]
+            if p.dtype != torch.float32:
+                continue                     # bf16 tables are written on every rank by the update kernel
+            rows = p.shape[0] // self.world
+            for owner in range(self.world):
+                dist.broadcast(p.data[owner * rows:(owner + 1) * rows],
+                               src=dist.get_global_rank(self.group, owner), group=self.group)

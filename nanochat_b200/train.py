@@ -8,8 +8,13 @@ import torch
 
 
 class TrainStep:
-    def __init__(self, model, grad_accum=1, comm=None, optimizer=None, **optimizer_kwargs):
+    def __init__(self, model, grad_accum=1, comm=None, optimizer=None, use_arena=None, **optimizer_kwargs):
         self.model = model
+        if use_arena is None:
+            use_arena = model.get_device().type == "cuda"
+        if use_arena and getattr(model, "_arena", None) is None:
+            from nanochat_b200.parallel.arena import ParamArena
+            ParamArena(model)
         self.grad_accum = grad_accum
         self.optimizer = optimizer if optimizer is not None else model.setup_optimizer(comm=comm, **optimizer_kwargs)
 
@@ -23,6 +28,10 @@ class TrainStep:
             loss = self.model(x, y)
             (loss * scale).backward()
         self.optimizer.step()
-        # dropping the buffers lets the first wgrad of the next step write instead of read-modify-write
-        self.model.zero_grad(set_to_none=True)
+        arena = getattr(self.model, "_arena", None)
+        if arena is not None:
+            arena.zero_grads()      # persistent gradient buffers: re-arm "first write overwrites"
+        else:
+            # dropping the buffers lets the first wgrad of the next step write instead of read-modify-write
+            self.model.zero_grad(set_to_none=True)
         return loss.detach()
