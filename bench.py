@@ -43,6 +43,8 @@ def parse_args():
     ap.add_argument("--total-batch-size", type=int, default=1048576)
     ap.add_argument("--window-pattern", type=str, default="SSSL")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end region (debugging)")
+    ap.add_argument("--comm", type=str, default="auto", choices=["auto", "fused", "nccl"],
+                    help="optimizer collectives for N>1: fused peer-to-peer kernels or NCCL")
     ap.add_argument("--ref-bf16", action="store_true", help="reference arm without --fp8")
     ap.add_argument("--ref-eager", action="store_true", help="reference arm without torch.compile")
     return ap.parse_args()
@@ -153,7 +155,20 @@ def run_ours(args):
     B, T = args.device_batch_size, args.seq_len
     assert args.total_batch_size % (B * T * world) == 0
     accum = args.total_batch_size // (B * T * world)
-    trainer = TrainStep(model, grad_accum=accum, matrix_lr=0.02, weight_decay=0.1)
+    comm, comm_name = None, "none (1 GPU)"
+    if world > 1:
+        comm_name = "nccl"
+        if args.comm in ("auto", "fused"):
+            try:
+                from nanochat_b200.parallel.symm import SymmComm
+                comm = SymmComm.create(model)
+                comm_name = "fused peer-to-peer kernels (symmetric memory over NVLink)"
+            except Exception as e:
+                if args.comm == "fused":
+                    raise
+                print(f"[bench] fused optimizer path unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+                comm = None
+    trainer = TrainStep(model, grad_accum=accum, comm=comm, matrix_lr=0.02, weight_decay=0.1)
     flops_per_token = model.estimate_flops()
 
     gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
@@ -205,7 +220,7 @@ def run_ours(args):
         "impl": "ours",
         "config": {"model": f"d{args.depth}", "global_batch": args.total_batch_size, "seq_len": T,
                    "device_batch": B, "grad_accum": accum, "window_pattern": args.window_pattern,
-                   "parallelism": f"dp{world}", "optimizer": "MuonAdamW (ZeRO-2 sharded)",
+                   "parallelism": f"dp{world}", "optimizer": "MuonAdamW (ZeRO-2 sharded)", "optimizer_comm": comm_name,
                    "l2": "inputs larger than L2 (activations of one micro-batch exceed 126 MB)",
                    "attention": nat.ATTENTION_IMPL},
         "mfu_bf16_nominal": flops_per_token * tok_s / (world * 2.25e15),

@@ -105,6 +105,9 @@ class MuonAdamW(torch.optim.Optimizer):
                 ref_ops.adamw_update(*args)
             if not shard.replicated:
                 gathers.append((comm.all_gather(p, p_slice), None, None))
+                if _use_native(p) and p.dtype == torch.float32:
+                    # the other ranks' rows arrive behind autograd's back: the bf16 operand copy must be re-cast
+                    self._stale_shadows.append(p)
 
     # ------------------------------------------------------------- Muon
     def _launch_muon(self, group, comm):
@@ -185,6 +188,7 @@ class MuonAdamW(torch.optim.Optimizer):
             return comm.fused_step(self)
         launched = []
         self._consumed = []
+        self._stale_shadows = []
         for group in self.param_groups:
             if group["kind"] == "adamw":
                 launched.append(self._launch_adamw(group, comm))
@@ -205,3 +209,10 @@ class MuonAdamW(torch.optim.Optimizer):
         for g in self._consumed:
             g.zero_()
         self._consumed = []
+        if self._stale_shadows:
+            table = ops.native_module()._shadow
+            for p in self._stale_shadows:
+                ent = table.get(p)
+                if ent is not None:
+                    table.set(p, -1, ent[1])     # keep the buffer, force a refresh on next use
+            self._stale_shadows = []
