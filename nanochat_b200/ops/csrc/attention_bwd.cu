@@ -6,17 +6,31 @@
 //             the inner loop walks 64-query blocks (Y1 = Q, Y2 = dO) of every query head that
 //             shares the kv head. Scores are kept transposed (rows = keys):
 //               S'  = K Q^T,  dP' = V dO^T                      (tcgen05, TMEM 2 x 64 columns, double buffered)
-//               P'  = exp2(S' * c - lse_q),  dS' = P' * (dP' - delta_q)   (one thread per key row)
-//               dV += P' dO,  dK += dS' Q                        (A from the bf16 smem tile, B = Y tile MN-major)
+//               P'  = exp2(S' * c - lse_q),  dS' = P' * (dP' - delta_q)   (two threads per key row, 32 columns each)
+//               dV += P' dO,  dK += dS' Q                        (A = bf16 P'/dS' in TMEM, B = Y tile MN-major)
 //   MODE_DQ   CTA = (128-query block, head, batch). X1 = Q, X2 = dO resident, inner 64-key blocks
 //             (Y1 = K, Y2 = V): S = Q K^T, dP = dO V^T, dS = P (dP - delta),  dQ += dS K.
+//
+// P' and dS' never touch shared memory: the compute threads write them as packed bf16 over the fp32
+// S' / dP' columns they were computed from (tcgen05.st) and the accumulate products read their A
+// operand from tensor memory. That leaves room for a four-deep ring of inner tiles, enough to cover
+// the latency of the TMA loads (a stage is only released when the accumulate products that read it
+// have completed).
 //
 // Recomputing S and dP in both launches costs 7 tile products instead of 5 but keeps every
 // accumulator in TMEM (no atomics, deterministic) and every operand in its natural layout.
 // delta = rowsum(dO * O) comes from a small pre-pass. All waits are bounded.
+//
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer, warps 2..9 =
+// two compute warpgroups. Both warpgroups work on the same 128 x 64 score block, one per 32-column
+// half, so the exp2 / dS arithmetic of a block takes half as long and each scheduler has two
+// resident warps to overlap TMEM loads with math. Blocks that lie entirely inside the causal /
+// window band skip the per-element mask.
 #include "attention.h"
 #include "host_utils.cuh"
 #include "ptx.cuh"
+
+#include <type_traits>
 
 namespace nc {
 
@@ -24,14 +38,15 @@ namespace ab {
 constexpr int BX = 128;                  // outer rows per CTA
 constexpr int BY = 64;                   // inner block
 constexpr int D = 128;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;
+constexpr int COMPUTE_WARPS = 8;
 constexpr int X_HALF = 128 * 64 * 2;     // 16 KB box of an outer tile
 constexpr int X_TILE = 2 * X_HALF;       // 32 KB
 constexpr int Y_HALF = 64 * 64 * 2;      // 8 KB box of an inner tile
 constexpr int Y_TILE = 2 * Y_HALF;       // 16 KB
-constexpr int P_TILE = 128 * 64 * 2;     // 16 KB: 128 rows x 64 bf16 (one swizzle row each)
-// smem: X1, X2 | 2 stages x (Y1, Y2) | 2 x (P, dS)
-constexpr int SMEM_BYTES = 2 * X_TILE + 2 * 2 * Y_TILE + 2 * 2 * P_TILE + 1024 /*col vectors*/ + 1024 + 256;
+constexpr int NS = 4;                    // inner-tile ring depth
+// smem: X1, X2 | NS stages x (Y1, Y2) | column vectors | barriers
+constexpr int SMEM_BYTES = 2 * X_TILE + NS * 2 * Y_TILE + 1024 /*col vectors*/ + 1024 + 256;
 constexpr int TMEM_COLS = 512;
 constexpr int COL_S = 0, COL_DP = 128, COL_ACC1 = 256, COL_ACC2 = 384;
 }  // namespace ab
@@ -59,16 +74,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
   uint8_t* sX1 = smem;
   uint8_t* sX2 = sX1 + X_TILE;
   uint8_t* sY = sX2 + X_TILE;                     // stage s: Y1 at s*2*Y_TILE, Y2 right after
-  uint8_t* sPD = sY + 2 * 2 * Y_TILE;             // buffer b: P at b*2*P_TILE, dS right after
-  float* col_vec = reinterpret_cast<float*>(sPD + 2 * 2 * P_TILE);   // [2 buffers][2 (lse, delta)][64]
+  float* col_vec = reinterpret_cast<float*>(sY + NS * 2 * Y_TILE);   // [2 buffers][2 (lse, delta)][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(col_vec) + 1024);
   uint64_t* out_full = bars;
-  uint64_t* in_full = bars + 1;       // [2]
-  uint64_t* in_empty = bars + 3;      // [2]
-  uint64_t* s_full = bars + 5;        // [2]
-  uint64_t* s_free = bars + 7;        // [2]
-  uint64_t* p_ready = bars + 9;       // [2]
-  uint64_t* p_free = bars + 11;       // [2]
+  uint64_t* in_full = bars + 1;       // [NS]
+  uint64_t* in_empty = bars + 5;      // [NS]
+  uint64_t* s_full = bars + 9;        // [2]
+  uint64_t* p_ready = bars + 11;      // [2]
   uint64_t* done = bars + 13;
   uint64_t* cv_ready = bars + 14;     // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
@@ -98,9 +110,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
 
   if (threadIdx.x == 0) {
     mbar_init(out_full, 1);
+    for (int s = 0; s < NS; ++s) { mbar_init(&in_full[s], 1); mbar_init(&in_empty[s], 1); }
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&in_full[s], 1); mbar_init(&in_empty[s], 1); mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 4);
-      mbar_init(&p_ready[s], 4); mbar_init(&p_free[s], 1); mbar_init(&cv_ready[s], 4);
+      mbar_init(&s_full[s], 1); mbar_init(&p_ready[s], COMPUTE_WARPS); mbar_init(&cv_ready[s], 4);
     }
     mbar_init(done, 1);
     *abort_flag = 0;
@@ -123,7 +135,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
       tma_load_4d(sX2, &tmX2, out_full, 0, x0, head_x, b);
       tma_load_4d(sX2 + X_HALF, &tmX2, out_full, 64, x0, head_x, b);
       for (int it = 0; it < n_items; ++it) {
-        const int s = it & 1; const uint32_t ph = (it >> 1) & 1;
+        const int s = it % NS; const uint32_t ph = (it / NS) & 1;
         const int hi_idx = it / per_head;
         const int y0 = (y_lo + it - hi_idx * per_head) * BY;
         const int head_y = DKV ? hkv * group + hi_idx : hkv;
@@ -146,31 +158,35 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
       bool ok = mbar_wait(out_full, 0, abort_flag, args.status, ST_WAIT_FULL, 0xfff);
       auto accumulate = [&](int i) -> bool {
         const int bfr = i & 1; const uint32_t ph = (i >> 1) & 1;
+        const int st = i % NS;
         if (!mbar_wait(&p_ready[bfr], ph, abort_flag, args.status, ST_WAIT_PEER, i)) return false;
         tc_fence_after();
-        const uint32_t y1 = smem_u32(sY + bfr * 2 * Y_TILE), y2 = y1 + Y_TILE;
-        const uint32_t p = smem_u32(sPD + bfr * 2 * P_TILE), ds = p + P_TILE;
+        const uint32_t y1 = smem_u32(sY + st * 2 * Y_TILE), y2 = y1 + Y_TILE;
 #pragma unroll
         for (int kk = 0; kk < BY / 16; ++kk) {
+          // A: 16 reduction elements = 8 packed columns; each warpgroup wrote its 32 elements at the start of
+          // its own 32-column half of the fp32 block
+          const uint32_t acol = bfr * BY + (kk >> 1) * 32 + (kk & 1) * 8;
           const uint64_t bdesc1 = umma_desc_sw128(y1 + kk * 2048, Y_HALF, 1024);   // Y1 as [red 64][out 128]
           if (DKV) {
             const uint64_t bdesc2 = umma_desc_sw128(y2 + kk * 2048, Y_HALF, 1024);
-            mma_f16(tmem_base + COL_ACC1, umma_desc_sw128(p + kk * 32, 16, 1024), bdesc2, idesc_acc, (i | kk) != 0);
-            mma_f16(tmem_base + COL_ACC2, umma_desc_sw128(ds + kk * 32, 16, 1024), bdesc1, idesc_acc, (i | kk) != 0);
+            mma_f16_ts(tmem_base + COL_ACC1, tmem_base + COL_S + acol, bdesc2, idesc_acc, (i | kk) != 0);
+            mma_f16_ts(tmem_base + COL_ACC2, tmem_base + COL_DP + acol, bdesc1, idesc_acc, (i | kk) != 0);
           } else {
-            mma_f16(tmem_base + COL_ACC1, umma_desc_sw128(ds + kk * 32, 16, 1024), bdesc1, idesc_acc, (i | kk) != 0);
+            mma_f16_ts(tmem_base + COL_ACC1, tmem_base + COL_DP + acol, bdesc1, idesc_acc, (i | kk) != 0);
           }
         }
-        mma_commit(&in_empty[bfr]);
-        mma_commit(&p_free[bfr]);
+        mma_commit(&in_empty[st]);
         return true;
       };
       for (int it = 0; it < n_items && ok; ++it) {
-        const int s = it & 1; const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(&in_full[s], ph, abort_flag, args.status, ST_WAIT_FULL, it)) { ok = false; break; }
-        if (!mbar_wait(&s_free[s], ph ^ 1, abort_flag, args.status, ST_WAIT_TMEM_EMPTY, it)) { ok = false; break; }
+        // S'/dP' buffer it&1 still holds P'/dS' of item it-2: its accumulate products were issued in the
+        // previous iteration and the tensor pipe runs this thread's instructions in order
+        const int s = it & 1;
+        const int st = it % NS; const uint32_t ph = (it / NS) & 1;
+        if (!mbar_wait(&in_full[st], ph, abort_flag, args.status, ST_WAIT_FULL, it)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t y1 = smem_u32(sY + s * 2 * Y_TILE), y2 = y1 + Y_TILE;
+        const uint32_t y1 = smem_u32(sY + st * 2 * Y_TILE), y2 = y1 + Y_TILE;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t xo = (kk >> 2) * X_HALF + (kk & 3) * 32;
@@ -193,9 +209,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------------ compute
-    const int quad = warp & 3;
+    const int quad = warp & 3;                      // TMEM lane quadrant this warp can read
+    const int half = (warp - 2) >> 2;               // which 32-column half of the 64-wide block
     const int r = quad * 32 + lane;
-    const int tid_c = threadIdx.x - 64;             // 0..127 among the compute threads
+    const int tid_c = (quad * 32 + lane);           // 0..127 inside a warpgroup
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
     const int xi = x0 + r;                          // DKV: key index ; DQ: query index
     float row_lse = 0.f, row_delta = 0.f;
@@ -211,7 +228,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
       const int y0 = (y_lo + it - hi_idx * per_head) * BY;
       float* cv = col_vec + s * 128;
       float col_stat = 0.f;
-      if (DKV) {
+      if (DKV && half == 0) {
         // per-query (column) statistics of this inner block: fetched early, published to smem below
         const int hq = hkv * group + hi_idx;
         const int qi = y0 + (tid_c & 63);
@@ -222,68 +239,73 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
       }
       if (!mbar_wait(&s_full[s], ph, abort_flag, args.status, ST_WAIT_TMEM_FULL, it)) { ok = false; break; }
       tc_fence_after();
-      uint32_t sv[64], dv[64];
-      {
-        uint32_t t32[32];
-        tmem_ld32(tmem_base + lane_sel + COL_S + s * BY, t32);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) sv[j] = t32[j];
-        tmem_ld32(tmem_base + lane_sel + COL_S + s * BY + 32, t32);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) sv[32 + j] = t32[j];
-        tmem_ld32(tmem_base + lane_sel + COL_DP + s * BY, t32);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) dv[j] = t32[j];
-        tmem_ld32(tmem_base + lane_sel + COL_DP + s * BY + 32, t32);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) dv[32 + j] = t32[j];
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[s]);
-      // the tiles and column vectors of buffer s were last used by item it-2; its accumulate MMAs are done
-      // (and therefore every compute warp has finished that item) once p_free[s] flips
-      if (!mbar_wait(&p_free[s], ph ^ 1, abort_flag, args.status, ST_WAIT_EMPTY, 0x200 + it)) { ok = false; break; }
+      uint32_t sv[32], dv[32];
+      tmem_ld32(tmem_base + lane_sel + COL_S + s * BY + half * 32, sv);
+      tmem_ld32(tmem_base + lane_sel + COL_DP + s * BY + half * 32, dv);
+      tmem_wait_ld();
+      // column vectors of buffer s were last read for item it-2; every compute warp finished that item before
+      // its accumulate products (and therefore this item's S'/dP') could be issued
       if (DKV) {
-        cv[tid_c] = col_stat;
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&cv_ready[s]);
+        if (half == 0) {
+          cv[tid_c] = col_stat;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&cv_ready[s]);
+        }
         if (!mbar_wait(&cv_ready[s], ph, abort_flag, args.status, ST_WAIT_PEER, 0x400 + it)) { ok = false; break; }
       }
-      uint8_t* prow = sPD + s * 2 * P_TILE + r * 128;
-      uint8_t* dsrow = prow + P_TILE;
+      // a block needs the element mask only if the causal diagonal, the window edge or the end of the
+      // sequence passes through it
+      const bool interior =
+          DKV ? (x0 + BX - 1 <= y0 + off) && (args.window < 0 || y0 + BY - 1 + off - x0 <= args.window) &&
+                    (x0 + BX - 1 < args.Tk) && (y0 + BY - 1 < args.Tq)
+              : (y0 + BY - 1 <= x0 + off) && (args.window < 0 || x0 + BX - 1 + off - y0 <= args.window) &&
+                    (y0 + BY - 1 < args.Tk) && (x0 + BX - 1 < args.Tq);
+      uint32_t pp[16], dd[16];
+      auto block = [&](auto masked_tag) {
+        constexpr bool MASKED = decltype(masked_tag)::value;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        uint32_t pp[4], dd[4];
-#pragma unroll
-        for (int j2 = 0; j2 < 4; ++j2) {
-          float pv[2], dsv[2];
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int c = u * 8 + j2 * 2 + e;
-            const int yi = y0 + c;
-            const int qi = DKV ? yi : xi;
-            const int kj = DKV ? xi : yi;
-            const float lse2 = DKV ? cv[c] : row_lse;
-            const float dl = DKV ? cv[64 + c] : row_delta;
-            const bool valid = (kj <= qi + off) && (args.window < 0 || qi + off - kj <= args.window) &&
-                               (kj < args.Tk) && (qi < args.Tq);
-            const float p = valid ? exp2f(__uint_as_float(sv[c]) * args.scale_log2 - lse2) : 0.f;
-            pv[e] = p;
-            dsv[e] = p * (__uint_as_float(dv[c]) - dl);
+        for (int u = 0; u < 4; ++u) {
+          const int cbase = half * 32 + u * 8;      // first of 8 columns, within the 64-wide block
+          float l8[8], d8[8];
+          if (DKV) {
+            const float4 la = *reinterpret_cast<const float4*>(cv + cbase);
+            const float4 lb = *reinterpret_cast<const float4*>(cv + cbase + 4);
+            const float4 da = *reinterpret_cast<const float4*>(cv + 64 + cbase);
+            const float4 db = *reinterpret_cast<const float4*>(cv + 64 + cbase + 4);
+            l8[0] = la.x; l8[1] = la.y; l8[2] = la.z; l8[3] = la.w; l8[4] = lb.x; l8[5] = lb.y; l8[6] = lb.z; l8[7] = lb.w;
+            d8[0] = da.x; d8[1] = da.y; d8[2] = da.z; d8[3] = da.w; d8[4] = db.x; d8[5] = db.y; d8[6] = db.z; d8[7] = db.w;
           }
-          pp[j2] = pack_bf16(pv[0], pv[1]);
-          dd[j2] = pack_bf16(dsv[0], dsv[1]);
+          float pv[8], dsv[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const int j = u * 8 + e;                // index into this thread's 32 loaded columns
+            const float lse2 = DKV ? l8[e] : row_lse;
+            const float dl = DKV ? d8[e] : row_delta;
+            float pe = exp2f(__uint_as_float(sv[j]) * args.scale_log2 - lse2);
+            if (MASKED) {
+              const int yi = y0 + cbase + e;
+              const int qi = DKV ? yi : xi;
+              const int kj = DKV ? xi : yi;
+              const bool valid = (kj <= qi + off) && (args.window < 0 || qi + off - kj <= args.window) &&
+                                 (kj < args.Tk) && (qi < args.Tq);
+              pe = valid ? pe : 0.f;
+            }
+            pv[e] = pe;
+            dsv[e] = pe * (__uint_as_float(dv[j]) - dl);
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if (DKV) pp[u * 4 + e] = pack_bf16(pv[2 * e], pv[2 * e + 1]);
+            dd[u * 4 + e] = pack_bf16(dsv[2 * e], dsv[2 * e + 1]);
+          }
         }
-        const int unit = u ^ (r & 7);
-        if (DKV) *reinterpret_cast<uint4*>(prow + unit * 16) = make_uint4(pp[0], pp[1], pp[2], pp[3]);
-        *reinterpret_cast<uint4*>(dsrow + unit * 16) = make_uint4(dd[0], dd[1], dd[2], dd[3]);
-      }
-      fence_proxy_async_smem();
+      };
+      if (interior) block(std::false_type{}); else block(std::true_type{});
+      // packed bf16 over the first 16 of this warp's own 32 fp32 columns (already in registers)
+      if (DKV) tmem_st16(tmem_base + lane_sel + COL_S + s * BY + half * 32, pp);
+      tmem_st16(tmem_base + lane_sel + COL_DP + s * BY + half * 32, dd);
+      tmem_wait_st();
+      tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[s]);
     }
@@ -295,7 +317,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
     const bool warp_ok = __all_sync(0xffffffffu, ok);
     const bool store_row_ok = xi < limit;
     if (warp_ok) {
-      for (int which = 0; which < (DKV ? 2 : 1); ++which) {
+      // DKV: warpgroup 0 writes dV, warpgroup 1 writes dK. DQ: each warpgroup writes half of the head dim.
+      {
+        const int which = DKV ? half : 0;
+        const int c_lo = DKV ? 0 : half * (D / 64), c_hi = DKV ? D / 32 : c_lo + D / 64;
         const float mul = (DKV && which == 0) ? 1.f : args.scale;
         __nv_bfloat16* orow =
             which == 0 ? reinterpret_cast<__nv_bfloat16*>(args.out1) + (long long)b * args.o1_bat +
@@ -304,7 +329,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
                              (long long)xi * args.o2_tok + (long long)hx * args.o2_head;
         const uint32_t col0 = which == 0 ? COL_ACC1 : COL_ACC2;
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
+        for (int c = c_lo; c < c_hi; ++c) {
           uint32_t v[32];
           if (n_items > 0) {
             tmem_ld32(tmem_base + lane_sel + col0 + c * 32, v);

@@ -25,10 +25,8 @@
 namespace nc {
 
 constexpr int BM = 128;
-constexpr int BK = 64;          // 64 bf16 = one 128-byte swizzle row
-constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
-constexpr int CHUNK_BYTES = 64 * BK * 2;   // one MN-major TMA box: 64 k-rows x 128 B
+constexpr int ROW_BYTES = 128;   // one swizzle row: 64 bf16 or 128 fp8 values along the contiguous dim
 
 struct GemmKernelArgs {
   int M, N, K, batch;
@@ -37,26 +35,40 @@ struct GemmKernelArgs {
   const void* aux;
   long long ldaux, bsaux;
   float alpha, beta;
+  const float* scale_a;     // optional device scalars multiplied into alpha (fp8 de-quantisation)
+  const float* scale_b;
+  float* amax_out;          // optional: max |C| over everything this launch stores (atomic, fp32 bits)
   int epi;
   int c_f32;
   int m_blocks, n_blocks, group_m;
+  uint32_t idesc;
   int* status;
 };
 
 constexpr int next_pow2_cols(int n) { return n <= 32 ? 32 : n <= 64 ? 64 : n <= 128 ? 128 : 256; }
 
-template <int BN, bool A_MN, bool B_MN>
+// FP8 = operands are 1-byte (e4m3 / e5m2, kind::f8f6f4), else bf16 (kind::f16). A k-block is always one
+// 128-byte swizzle row deep along K for K-major operands, and BK rows of 128 bytes for MN-major ones.
+template <int BN, bool A_MN, bool B_MN, bool FP8>
 struct Cfg {
-  static constexpr int BN_SMEM = (BN + 63) / 64 * 64;
-  static constexpr int A_BYTES = BM * BK * 2;
-  static constexpr int B_BYTES = BN_SMEM * BK * 2;
-  static constexpr int B_TX = B_MN ? B_BYTES : BN * BK * 2;
+  static constexpr int ELT = FP8 ? 1 : 2;
+  static constexpr int BK = ROW_BYTES / ELT;            // elements of K per k-block (64 bf16 / 128 fp8)
+  static constexpr int UMMA_K = 32 / ELT;               // K per tcgen05.mma (16 bf16 / 32 fp8)
+  static constexpr int MN_CHUNK = ROW_BYTES / ELT;      // MN elements per MN-major TMA box
+  static constexpr int CHUNK_BYTES = BK * ROW_BYTES;    // one MN-major box: BK k-rows x 128 B
+  static constexpr int A_CHUNKS = BM / MN_CHUNK;        // 2 (bf16) / 1 (fp8)
+  static constexpr int B_CHUNKS = (BN + MN_CHUNK - 1) / MN_CHUNK;
+  static constexpr int A_BYTES = BM * ROW_BYTES;        // 16 KB either way
+  static constexpr int B_ROWS_ALLOC = (BN + 127) / 128 * 128;
+  static constexpr int B_BYTES = B_ROWS_ALLOC * ROW_BYTES;
+  static constexpr int B_TX = B_MN ? B_CHUNKS * CHUNK_BYTES : BN * ROW_BYTES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int MAX_STAGES = (227 * 1024 - 2048) / STAGE_BYTES;
   static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
   static constexpr int ACC_STRIDE = next_pow2_cols(BN);
   static constexpr int TMEM_COLS = 2 * ACC_STRIDE;
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+  static_assert(!B_MN || B_CHUNKS * CHUNK_BYTES <= B_BYTES, "MN-major B boxes must fit the stage");
 };
 
 __device__ __forceinline__ void tile_coords(int t, const GemmKernelArgs& a, int& b, int& mb, int& nb) {
@@ -72,11 +84,12 @@ __device__ __forceinline__ void tile_coords(int t, const GemmKernelArgs& a, int&
   nb = in_g / gm;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool FP8>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmKernelArgs args) {
-  using C = Cfg<BN, A_MN, B_MN>;
+  using C = Cfg<BN, A_MN, B_MN, FP8>;
+  constexpr int BK = C::BK;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
@@ -119,15 +132,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           mbar_arrive_expect_tx(&full[stage], C::A_BYTES + C::B_TX);
           const int k0 = kb * BK;
           if constexpr (A_MN) {
-            tma_load_3d(sA, &tmA, &full[stage], m0, k0, b);
-            tma_load_3d(sA + CHUNK_BYTES, &tmA, &full[stage], m0 + 64, k0, b);
+#pragma unroll
+            for (int j = 0; j < C::A_CHUNKS; ++j)
+              tma_load_3d(sA + j * C::CHUNK_BYTES, &tmA, &full[stage], m0 + C::MN_CHUNK * j, k0, b);
           } else {
             tma_load_3d(sA, &tmA, &full[stage], k0, m0, b);
           }
           if constexpr (B_MN) {
 #pragma unroll
-            for (int j = 0; j < C::BN_SMEM / 64; ++j)
-              tma_load_3d(sB + j * CHUNK_BYTES, &tmB, &full[stage], n0 + 64 * j, k0, b);
+            for (int j = 0; j < C::B_CHUNKS; ++j)
+              tma_load_3d(sB + j * C::CHUNK_BYTES, &tmB, &full[stage], n0 + C::MN_CHUNK * j, k0, b);
           } else {
             tma_load_3d(sB, &tmB, &full[stage], k0, n0, b);
           }
@@ -138,7 +152,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN, B_MN);
+      const uint32_t idesc = args.idesc;
       int stage = 0; uint32_t phase = 0; bool ok = true;
       int acc = 0; uint32_t acc_phase = 0;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
@@ -151,12 +165,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint32_t a_addr = smem_u32(tiles + stage * C::STAGE_BYTES);
           const uint32_t b_addr = a_addr + C::A_BYTES;
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t a_desc = A_MN ? umma_desc_sw128(a_addr + k * (UMMA_K * 128), CHUNK_BYTES, 1024)
-                                         : umma_desc_sw128(a_addr + k * (UMMA_K * 2), 16, 1024);
-            const uint64_t b_desc = B_MN ? umma_desc_sw128(b_addr + k * (UMMA_K * 128), CHUNK_BYTES, 1024)
-                                         : umma_desc_sw128(b_addr + k * (UMMA_K * 2), 16, 1024);
-            mma_f16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0);
+          for (int k = 0; k < BK / C::UMMA_K; ++k) {
+            // one instruction consumes 32 bytes of K: 32 B along a K-major row, or UMMA_K rows of 128 B
+            const uint64_t a_desc = A_MN ? umma_desc_sw128(a_addr + k * (C::UMMA_K * ROW_BYTES), C::CHUNK_BYTES, 1024)
+                                         : umma_desc_sw128(a_addr + k * 32, 16, 1024);
+            const uint64_t b_desc = B_MN ? umma_desc_sw128(b_addr + k * (C::UMMA_K * ROW_BYTES), C::CHUNK_BYTES, 1024)
+                                         : umma_desc_sw128(b_addr + k * 32, 16, 1024);
+            if (FP8) mma_f8(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0);
+            else     mma_f16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0);
           }
           mma_commit(&empty[stage]);   // frees the smem stage once these MMAs have read it
           if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
@@ -170,6 +186,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ---------------------------------------------------------------- epilogue
     const int quad = warp & 3;
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
+    float amax = 0.f;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int b, mb, nb; tile_coords(t, args, b, mb, nb);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, args.status, ST_WAIT_TMEM_FULL, t)) { ok = false; break; }
@@ -178,7 +195,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int n0 = nb * BN;
       const bool row_ok = row < args.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC_STRIDE;
-      const float alpha = args.alpha, beta = args.beta;
+      float alpha = args.alpha;
+      if (args.scale_a) alpha *= __ldg(args.scale_a);
+      if (args.scale_b) alpha *= __ldg(args.scale_b);
+      const float beta = args.beta;
 #pragma unroll 1
       for (int c = 0; c < BN / 16; ++c) {
         uint32_t r[16];
@@ -202,6 +222,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                   float4 x = *reinterpret_cast<const float4*>(xrow + q4 * 4);
                   o.x += beta * x.x; o.y += beta * x.y; o.z += beta * x.z; o.w += beta * x.w;
                 }
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
                 *reinterpret_cast<float4*>(crow + q4 * 4) = o;
               }
             }
@@ -233,6 +254,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                     }
                   }
                 }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(vv[j]));
                 uint4 o;
                 o.x = pack_bf16(vv[0], vv[1]); o.y = pack_bf16(vv[2], vv[3]);
                 o.z = pack_bf16(vv[4], vv[5]); o.w = pack_bf16(vv[6], vv[7]);
@@ -246,6 +269,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (args.amax_out) {
+      // non-negative floats order like their bit patterns
+#pragma unroll
+      for (int w = 16; w > 0; w >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, w));
+      if (lane == 0 && amax > 0.f) atomicMax(reinterpret_cast<unsigned int*>(args.amax_out), __float_as_uint(amax));
     }
   }
 
@@ -264,44 +293,49 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 // ----------------------------------------------------------------------------- host
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool FP8>
 static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t stream) {
-  using C = Cfg<BN, A_MN, B_MN>;
+  using C = Cfg<BN, A_MN, B_MN, FP8>;
+  constexpr int BK = C::BK;
+  constexpr int ELT = C::ELT;
   static bool configured = false;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, FP8>;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     configured = true;
   }
+  const CUtensorMapDataType dt = FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tmA, tmB;
   const uint64_t batch = static_cast<uint64_t>(d.batch);
   {
     uint64_t dims[3], str[2]; uint32_t box[3];
-    if (A_MN) { dims[0] = d.M; dims[1] = d.K; box[0] = 64; box[1] = BK; }
+    if (A_MN) { dims[0] = d.M; dims[1] = d.K; box[0] = C::MN_CHUNK; box[1] = BK; }
     else      { dims[0] = d.K; dims[1] = d.M; box[0] = BK; box[1] = BM; }
     dims[2] = batch; box[2] = 1;
-    str[0] = static_cast<uint64_t>(d.lda) * 2;
-    str[1] = d.batch > 1 ? static_cast<uint64_t>(d.bsa) * 2 : str[0] * dims[1];
-    if (!make_tmap(&tmA, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d.A, dims, str, box)) return cudaErrorInvalidValue;
+    str[0] = static_cast<uint64_t>(d.lda) * ELT;
+    str[1] = d.batch > 1 ? static_cast<uint64_t>(d.bsa) * ELT : str[0] * dims[1];
+    if (!make_tmap(&tmA, dt, 3, d.A, dims, str, box)) return cudaErrorInvalidValue;
   }
   {
     uint64_t dims[3], str[2]; uint32_t box[3];
-    if (B_MN) { dims[0] = d.N; dims[1] = d.K; box[0] = 64; box[1] = BK; }
+    if (B_MN) { dims[0] = d.N; dims[1] = d.K; box[0] = C::MN_CHUNK; box[1] = BK; }
     else      { dims[0] = d.K; dims[1] = d.N; box[0] = BK; box[1] = BN; }
     dims[2] = batch; box[2] = 1;
-    str[0] = static_cast<uint64_t>(d.ldb) * 2;
-    str[1] = d.batch > 1 ? static_cast<uint64_t>(d.bsb) * 2 : str[0] * dims[1];
-    if (!make_tmap(&tmB, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d.B, dims, str, box)) return cudaErrorInvalidValue;
+    str[0] = static_cast<uint64_t>(d.ldb) * ELT;
+    str[1] = d.batch > 1 ? static_cast<uint64_t>(d.bsb) * ELT : str[0] * dims[1];
+    if (!make_tmap(&tmB, dt, 3, d.B, dims, str, box)) return cudaErrorInvalidValue;
   }
   GemmKernelArgs a;
   a.M = d.M; a.N = d.N; a.K = d.K; a.batch = d.batch;
   a.C = d.C; a.ldc = d.ldc; a.bsc = d.bsc;
   a.aux = d.aux; a.ldaux = d.ldaux; a.bsaux = d.bsaux;
   a.alpha = d.alpha; a.beta = d.beta; a.epi = d.epi; a.c_f32 = d.c_f32;
+  a.scale_a = d.scale_a; a.scale_b = d.scale_b; a.amax_out = d.amax_out;
   a.m_blocks = (d.M + BM - 1) / BM;
   a.n_blocks = (d.N + BN - 1) / BN;
   a.group_m = 16;
+  a.idesc = FP8 ? umma_idesc_f8(BM, BN, A_MN, B_MN, d.a_e5m2, d.b_e5m2) : umma_idesc_bf16(BM, BN, A_MN, B_MN);
   a.status = status;
   const long long tiles = 1ll * a.m_blocks * a.n_blocks * d.batch;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
@@ -309,16 +343,24 @@ static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t strea
   return cudaGetLastError();
 }
 
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool FP8>
 static cudaError_t launch_bn(int bn, const GemmDesc& d, int* status, cudaStream_t s) {
   switch (bn) {
-    case 256: return launch_cfg<256, A_MN, B_MN>(d, status, s);
-    case 208: return launch_cfg<208, A_MN, B_MN>(d, status, s);
-    case 128: return launch_cfg<128, A_MN, B_MN>(d, status, s);
-    case 64:  return launch_cfg<64, A_MN, B_MN>(d, status, s);
-    case 32:  return launch_cfg<32, A_MN, B_MN>(d, status, s);
+    case 256: return launch_cfg<256, A_MN, B_MN, FP8>(d, status, s);
+    case 208: return launch_cfg<208, A_MN, B_MN, FP8>(d, status, s);
+    case 128: return launch_cfg<128, A_MN, B_MN, FP8>(d, status, s);
+    case 64:  return launch_cfg<64, A_MN, B_MN, FP8>(d, status, s);
+    case 32:  return launch_cfg<32, A_MN, B_MN, FP8>(d, status, s);
     default:  return cudaErrorInvalidValue;
   }
+}
+
+template <bool FP8>
+static cudaError_t launch_major(int bn, const GemmDesc& d, int* status, cudaStream_t stream) {
+  if (d.a_mn && d.b_mn) return launch_bn<true, true, FP8>(bn, d, status, stream);
+  if (!d.a_mn && d.b_mn) return launch_bn<false, true, FP8>(bn, d, status, stream);
+  if (!d.a_mn && !d.b_mn) return launch_bn<false, false, FP8>(bn, d, status, stream);
+  return launch_bn<true, false, FP8>(bn, d, status, stream);
 }
 
 int gemm_pick_bn(int M, int N, int batch) {
@@ -343,10 +385,15 @@ cudaError_t gemm_bf16(const GemmDesc& d, int* status, cudaStream_t stream) {
   if (d.M <= 0 || d.N <= 0 || d.K <= 0 || d.batch <= 0) return cudaErrorInvalidValue;
   if ((d.N & 7) || (d.lda & 7) || (d.ldb & 7) || (d.ldc & 3)) return cudaErrorInvalidValue;
   const int bn = d.bn > 0 ? d.bn : gemm_pick_bn(d.M, d.N, d.batch);
-  if (d.a_mn && d.b_mn) return launch_bn<true, true>(bn, d, status, stream);
-  if (!d.a_mn && d.b_mn) return launch_bn<false, true>(bn, d, status, stream);
-  if (!d.a_mn && !d.b_mn) return launch_bn<false, false>(bn, d, status, stream);
-  return launch_bn<true, false>(bn, d, status, stream);
+  return launch_major<false>(bn, d, status, stream);
+}
+
+cudaError_t gemm_fp8(const GemmDesc& d, int* status, cudaStream_t stream) {
+  if (d.M <= 0 || d.N <= 0 || d.K <= 0 || d.batch <= 0) return cudaErrorInvalidValue;
+  // TMA strides are multiples of 16 bytes; output rows as for the bf16 kernel
+  if ((d.N & 7) || (d.lda & 15) || (d.ldb & 15) || (d.ldc & 3)) return cudaErrorInvalidValue;
+  const int bn = d.bn > 0 ? d.bn : gemm_pick_bn(d.M, d.N, d.batch);
+  return launch_major<true>(bn, d, status, stream);
 }
 
 }  // namespace nc

@@ -1,4 +1,5 @@
-// Host interface of the sm_100a tcgen05 bf16 GEMM (gemm.cu).
+// Host interface of the sm_100a tcgen05 GEMMs (gemm.cu): bf16 operands, or 8-bit float operands with
+// per-tensor scales.
 #pragma once
 
 #include <cuda_runtime.h>
@@ -25,9 +26,19 @@ struct GemmDesc {
   float alpha, beta;
   int epi;
   int bn;   // N tile override (256/208/128/64/32); 0 = pick automatically
+  // Optional, any operand type: device scalars multiplied into alpha when the kernel runs (the
+  // de-quantisation scales of per-tensor-scaled fp8 operands), and a device word that receives
+  // max |C| over the stored values (atomic max on the fp32 bit pattern; zero it beforehand).
+  const float* scale_a = nullptr;
+  const float* scale_b = nullptr;
+  float* amax_out = nullptr;
+  // gemm_fp8 only: operand element formats (0 = e4m3, 1 = e5m2)
+  int a_e5m2 = 0, b_e5m2 = 0;
 };
 
 cudaError_t gemm_bf16(const GemmDesc& d, int* status, cudaStream_t stream);
+// Same contract with 1-byte A and B (lda/ldb/bs* in elements = bytes, multiples of 16).
+cudaError_t gemm_fp8(const GemmDesc& d, int* status, cudaStream_t stream);
 int gemm_pick_bn(int M, int N, int batch);
 
 }  // namespace nc

@@ -38,8 +38,13 @@ def main():
     fused_model, cfg = build(device)
     nccl_model, _ = build(device)
     comm = SymmComm.create(fused_model)
-    a = TrainStep(fused_model, grad_accum=2, comm=comm, weight_decay=0.1)
-    b = TrainStep(nccl_model, grad_accum=2, weight_decay=0.1)      # default comm: torch.distributed (NCCL)
+    # Small learning rates keep three steps in the regime where two implementations that differ by
+    # rounding stay comparable element by element (at the training rates a +-lr sign flip of a
+    # near-zero gradient is amplified by the following steps).
+    hp = dict(weight_decay=0.1, embedding_lr=2e-3, unembedding_lr=4e-4, matrix_lr=2e-3, scalar_lr=5e-3)
+    initial = {n: p.detach().float().clone() for n, p in fused_model.named_parameters()}
+    a = TrainStep(fused_model, grad_accum=2, comm=comm, **hp)
+    b = TrainStep(nccl_model, grad_accum=2, **hp)      # default comm: torch.distributed (NCCL)
     gen = torch.Generator(device="cpu").manual_seed(100 + rank)
     losses, history = [], []
     for step in range(3):
@@ -55,21 +60,30 @@ def main():
     # oracle: the PyTorch reference bodies with NCCL collectives on the same data
     ops.set_kernel_mode("torch")
     oracle, _ = build(device)
-    c = TrainStep(oracle, grad_accum=2, weight_decay=0.1, use_arena=False)
+    c = TrainStep(oracle, grad_accum=2, use_arena=False, **hp)
     for data in history:
         c.step(lambda i: data[i])
     ops.set_kernel_mode("native")
 
-    def compare(model):
+    def compare(model, other, rel, min_numel):
+        """Parameters whose update (value - initial value) disagrees with `other` on more than 2% of
+        the elements; an element disagrees when it is off by more than rel x the mean |update|."""
         bad = {}
-        for (n, p), (_, q) in zip(model.named_parameters(), oracle.named_parameters()):
-            d = (p.float() - q.float()).abs()
-            tol = 3e-2 * q.float().abs().mean().item() + 2e-3
-            frac = (d > tol).float().mean().item()
-            if frac > 5e-3:
-                bad[n] = (round(d.max().item(), 4), round(frac, 4))
-        return dict(sorted(bad.items(), key=lambda kv: -kv[1][1])[:6])
-    bad_fused, bad_nccl = compare(fused_model), compare(nccl_model)
+        for (n, p), (_, q) in zip(model.named_parameters(), other.named_parameters()):
+            if p.numel() < min_numel:
+                continue
+            dp, dq = p.float() - initial[n], q.float() - initial[n]
+            tol = rel * dq.abs().mean().item() + 1e-7
+            frac = ((dp - dq).abs() > tol).float().mean().item()
+            if frac > 2e-2:
+                bad[n] = (round((dp - dq).abs().max().item(), 5), round(frac, 4), round(dq.abs().mean().item(), 5))
+        return dict(sorted(bad.items(), key=lambda kv: -kv[1][1])[:8])
+    # same kernels, different collectives: only the summation order differs
+    bad_pair = compare(fused_model, nccl_model, 0.1, 1)
+    # against the PyTorch bodies: bf16 rounding differs everywhere, scalars (sums with heavy
+    # cancellation) are left to the pairwise check
+    bad_fused = compare(fused_model, oracle, 0.5, 64)
+    bad_nccl = compare(nccl_model, oracle, 0.5, 64)
     oracle_params = dict(oracle.named_parameters())
     shadow_err = 0.0
     for g in comm.arena.muon_groups:
@@ -85,7 +99,7 @@ def main():
             shadow_err = max(shadow_err, ((d["shadow"].float() - ref).norm() / ref.norm()).item())
     gathered = [None] * world
     dist.all_gather_object(gathered, {"rank": rank, "losses": losses, "shadow_err": shadow_err,
-                                      "bad": bad_fused, "bad_nccl": bad_nccl})
+                                      "bad": bad_fused, "bad_nccl": bad_nccl, "bad_pair": bad_pair})
     if rank == 0:
         with open(out_path, "w") as f:
             json.dump(gathered, f)

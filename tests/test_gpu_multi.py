@@ -38,5 +38,6 @@ def test_fused_p2p_optimizer_matches_nccl(world, tmp_path):
         for la, lb in rec["losses"]:
             assert abs(la - lb) < 3e-2, rec
         assert rec["shadow_err"] < 2e-2, rec
+        assert not rec["bad_pair"], rec     # fused peer-to-peer path vs native kernels with NCCL collectives
         assert not rec["bad"], rec          # fused peer-to-peer path vs the PyTorch/NCCL oracle
         assert not rec["bad_nccl"], rec     # native kernels with NCCL collectives vs the same oracle
