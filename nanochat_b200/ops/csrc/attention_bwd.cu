@@ -154,22 +154,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(BX, BY, false, false);
       constexpr uint32_t idesc_acc = umma_idesc_bf16(BX, D, false, true);
-      const uint32_t x1 = smem_u32(sX1), x2 = smem_u32(sX2);
+      // Descriptors are built once per tile; a byte offset inside a tile adds offset/16 to the address field
+      // (shared memory is smaller than the field's range, so the add never carries out of it).
+      const uint64_t dx1 = umma_desc_sw128(smem_u32(sX1), 16, 1024), dx2 = umma_desc_sw128(smem_u32(sX2), 16, 1024);
+      // inner tiles of ring stage 0 viewed K-major (scores) and MN-major (accumulate); stage st adds st * stride
+      const uint64_t dyk0 = umma_desc_sw128(smem_u32(sY), 16, 1024), dym0 = umma_desc_sw128(smem_u32(sY), Y_HALF, 1024);
+      constexpr uint64_t STAGE_STEP = (2 * Y_TILE) >> 4, Y2_STEP = Y_TILE >> 4;
       bool ok = mbar_wait(out_full, 0, abort_flag, args.status, ST_WAIT_FULL, 0xfff);
       auto accumulate = [&](int i) -> bool {
         const int bfr = i & 1; const uint32_t ph = (i >> 1) & 1;
         const int st = i % NS;
         if (!mbar_wait(&p_ready[bfr], ph, abort_flag, args.status, ST_WAIT_PEER, i)) return false;
         tc_fence_after();
-        const uint32_t y1 = smem_u32(sY + st * 2 * Y_TILE), y2 = y1 + Y_TILE;
+        const uint64_t m1 = dym0 + st * STAGE_STEP, m2 = m1 + Y2_STEP;
 #pragma unroll
         for (int kk = 0; kk < BY / 16; ++kk) {
           // A: 16 reduction elements = 8 packed columns; each warpgroup wrote its 32 elements at the start of
           // its own 32-column half of the fp32 block
           const uint32_t acol = bfr * BY + (kk >> 1) * 32 + (kk & 1) * 8;
-          const uint64_t bdesc1 = umma_desc_sw128(y1 + kk * 2048, Y_HALF, 1024);   // Y1 as [red 64][out 128]
+          const uint64_t bdesc1 = m1 + static_cast<uint64_t>((kk * 2048) >> 4);   // Y1 as [red 64][out 128]
           if (DKV) {
-            const uint64_t bdesc2 = umma_desc_sw128(y2 + kk * 2048, Y_HALF, 1024);
+            const uint64_t bdesc2 = m2 + static_cast<uint64_t>((kk * 2048) >> 4);
             mma_f16_ts(tmem_base + COL_ACC1, tmem_base + COL_S + acol, bdesc2, idesc_acc, (i | kk) != 0);
             mma_f16_ts(tmem_base + COL_ACC2, tmem_base + COL_DP + acol, bdesc1, idesc_acc, (i | kk) != 0);
           } else {
@@ -186,20 +191,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         const int st = it % NS; const uint32_t ph = (it / NS) & 1;
         if (!mbar_wait(&in_full[st], ph, abort_flag, args.status, ST_WAIT_FULL, it)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t y1 = smem_u32(sY + st * 2 * Y_TILE), y2 = y1 + Y_TILE;
+        const uint64_t k1 = dyk0 + st * STAGE_STEP, k2 = k1 + Y2_STEP;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t xo = (kk >> 2) * X_HALF + (kk & 3) * 32;
-          const uint32_t yo = (kk >> 2) * Y_HALF + (kk & 3) * 32;
-          mma_f16(tmem_base + COL_S + s * BY, umma_desc_sw128(x1 + xo, 16, 1024), umma_desc_sw128(y1 + yo, 16, 1024),
-                  idesc_s, kk != 0);
+          const uint64_t xo = static_cast<uint64_t>(((kk >> 2) * X_HALF + (kk & 3) * 32) >> 4);
+          const uint64_t yo = static_cast<uint64_t>(((kk >> 2) * Y_HALF + (kk & 3) * 32) >> 4);
+          mma_f16(tmem_base + COL_S + s * BY, dx1 + xo, k1 + yo, idesc_s, kk != 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t xo = (kk >> 2) * X_HALF + (kk & 3) * 32;
-          const uint32_t yo = (kk >> 2) * Y_HALF + (kk & 3) * 32;
-          mma_f16(tmem_base + COL_DP + s * BY, umma_desc_sw128(x2 + xo, 16, 1024), umma_desc_sw128(y2 + yo, 16, 1024),
-                  idesc_s, kk != 0);
+          const uint64_t xo = static_cast<uint64_t>(((kk >> 2) * X_HALF + (kk & 3) * 32) >> 4);
+          const uint64_t yo = static_cast<uint64_t>(((kk >> 2) * Y_HALF + (kk & 3) * 32) >> 4);
+          mma_f16(tmem_base + COL_DP + s * BY, dx2 + xo, k2 + yo, idesc_s, kk != 0);
         }
         mma_commit(&s_full[s]);
         if (it > 0 && !accumulate(it - 1)) { ok = false; break; }

@@ -84,6 +84,80 @@ __device__ __forceinline__ void tile_coords(int t, const GemmKernelArgs& a, int&
   nb = in_g / gm;
 }
 
+// Epilogue of one accumulator tile for one thread: its row of 128 x BN fp32 values comes out of tensor memory
+// 16 columns at a time, goes through the fused epilogue and is stored as bf16 or fp32.
+template <int BN>
+__device__ __forceinline__ void store_tile_row(const GemmKernelArgs& args, uint32_t taddr, int b, int row, int n0,
+                                               float alpha, float beta, float& amax) {
+  const bool row_ok = row < args.M;
+#pragma unroll 1
+  for (int c = 0; c < BN / 16; ++c) {
+    uint32_t r[16];
+    tmem_ld16(taddr + c * 16, r);
+    tmem_wait_ld();
+    const int col = n0 + c * 16;
+    if (row_ok && col < args.N) {
+      float v[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) * alpha;
+      if (args.c_f32) {
+        float* crow = reinterpret_cast<float*>(args.C) + b * args.bsc + static_cast<long long>(row) * args.ldc + col;
+        const float* xrow = args.aux ? reinterpret_cast<const float*>(args.aux) + b * args.bsaux +
+                                           static_cast<long long>(row) * args.ldaux + col
+                                     : nullptr;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          if (col + q4 * 4 + 4 <= args.N) {
+            float4 o = make_float4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
+            if (xrow) {
+              float4 x = *reinterpret_cast<const float4*>(xrow + q4 * 4);
+              o.x += beta * x.x; o.y += beta * x.y; o.z += beta * x.z; o.w += beta * x.w;
+            }
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
+            *reinterpret_cast<float4*>(crow + q4 * 4) = o;
+          }
+        }
+      } else {
+        __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(args.C) + b * args.bsc +
+                              static_cast<long long>(row) * args.ldc + col;
+        const __nv_bfloat16* xrow = args.aux ? reinterpret_cast<const __nv_bfloat16*>(args.aux) + b * args.bsaux +
+                                                   static_cast<long long>(row) * args.ldaux + col
+                                             : nullptr;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (col + h * 8 + 8 <= args.N) {
+            float* vv = v + h * 8;
+            if (args.epi == EPI_RELU2) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { float tpos = fmaxf(vv[j], 0.f); vv[j] = tpos * tpos; }
+            } else if (xrow) {
+              uint4 xa = *reinterpret_cast<const uint4*>(xrow + h * 8);
+              const uint32_t xs[4] = {xa.x, xa.y, xa.z, xa.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                float2 f = unpack_bf16(xs[j]);
+                if (args.epi == EPI_MUL2SQRT) {
+                  vv[2 * j] *= 2.f * sqrtf(f.x);
+                  vv[2 * j + 1] *= 2.f * sqrtf(f.y);
+                } else {
+                  vv[2 * j] += beta * f.x;
+                  vv[2 * j + 1] += beta * f.y;
+                }
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(vv[j]));
+            uint4 o;
+            o.x = pack_bf16(vv[0], vv[1]); o.y = pack_bf16(vv[2], vv[3]);
+            o.z = pack_bf16(vv[4], vv[5]); o.w = pack_bf16(vv[6], vv[7]);
+            *reinterpret_cast<uint4*>(crow + h * 8) = o;
+          }
+        }
+      }
+    }
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN, bool FP8>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -187,84 +261,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int quad = warp & 3;
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
     float amax = 0.f;
+    float alpha = args.alpha;
+    if (args.scale_a) alpha *= __ldg(args.scale_a);
+    if (args.scale_b) alpha *= __ldg(args.scale_b);
+    const float beta = args.beta;
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int b, mb, nb; tile_coords(t, args, b, mb, nb);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, args.status, ST_WAIT_TMEM_FULL, t)) { ok = false; break; }
       tc_fence_after();
       const int row = mb * BM + quad * 32 + lane;
       const int n0 = nb * BN;
-      const bool row_ok = row < args.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC_STRIDE;
-      float alpha = args.alpha;
-      if (args.scale_a) alpha *= __ldg(args.scale_a);
-      if (args.scale_b) alpha *= __ldg(args.scale_b);
-      const float beta = args.beta;
-#pragma unroll 1
-      for (int c = 0; c < BN / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld16(taddr + c * 16, r);
-        tmem_wait_ld();
-        const int col = n0 + c * 16;
-        if (row_ok && col < args.N) {
-          float v[16];
-#pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]) * alpha;
-          if (args.c_f32) {
-            float* crow = reinterpret_cast<float*>(args.C) + b * args.bsc + static_cast<long long>(row) * args.ldc + col;
-            const float* xrow = args.aux ? reinterpret_cast<const float*>(args.aux) + b * args.bsaux +
-                                               static_cast<long long>(row) * args.ldaux + col
-                                         : nullptr;
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              if (col + q4 * 4 + 4 <= args.N) {
-                float4 o = make_float4(v[q4 * 4], v[q4 * 4 + 1], v[q4 * 4 + 2], v[q4 * 4 + 3]);
-                if (xrow) {
-                  float4 x = *reinterpret_cast<const float4*>(xrow + q4 * 4);
-                  o.x += beta * x.x; o.y += beta * x.y; o.z += beta * x.z; o.w += beta * x.w;
-                }
-                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
-                *reinterpret_cast<float4*>(crow + q4 * 4) = o;
-              }
-            }
-          } else {
-            __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(args.C) + b * args.bsc +
-                                  static_cast<long long>(row) * args.ldc + col;
-            const __nv_bfloat16* xrow = args.aux ? reinterpret_cast<const __nv_bfloat16*>(args.aux) + b * args.bsaux +
-                                                       static_cast<long long>(row) * args.ldaux + col
-                                                 : nullptr;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              if (col + h * 8 + 8 <= args.N) {
-                float* vv = v + h * 8;
-                if (args.epi == EPI_RELU2) {
-#pragma unroll
-                  for (int j = 0; j < 8; ++j) { float tpos = fmaxf(vv[j], 0.f); vv[j] = tpos * tpos; }
-                } else if (xrow) {
-                  uint4 xa = *reinterpret_cast<const uint4*>(xrow + h * 8);
-                  const uint32_t xs[4] = {xa.x, xa.y, xa.z, xa.w};
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    float2 f = unpack_bf16(xs[j]);
-                    if (args.epi == EPI_MUL2SQRT) {
-                      vv[2 * j] *= 2.f * sqrtf(f.x);
-                      vv[2 * j + 1] *= 2.f * sqrtf(f.y);
-                    } else {
-                      vv[2 * j] += beta * f.x;
-                      vv[2 * j + 1] += beta * f.y;
-                    }
-                  }
-                }
-#pragma unroll
-                for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(vv[j]));
-                uint4 o;
-                o.x = pack_bf16(vv[0], vv[1]); o.y = pack_bf16(vv[2], vv[3]);
-                o.z = pack_bf16(vv[4], vv[5]); o.w = pack_bf16(vv[6], vv[7]);
-                *reinterpret_cast<uint4*>(crow + h * 8) = o;
-              }
-            }
-          }
-        }
-      }
+      store_tile_row<BN>(args, taddr, b, row, n0, alpha, beta, amax);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
