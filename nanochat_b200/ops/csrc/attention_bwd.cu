@@ -51,6 +51,15 @@ constexpr int TMEM_COLS = 512;
 constexpr int COL_S = 0, COL_DP = 128, COL_ACC1 = 256, COL_ACC2 = 384;
 }  // namespace ab
 
+// Optional timeline of one CTA (build with -DNC_ATTN_TRACE): SM clock at pipeline events of the first 32
+// inner items, read back with nc_attn_trace_read(). Used to see which role the others wait for.
+#ifdef NC_ATTN_TRACE
+__device__ long long g_attn_trace[16 * 32];
+#define NC_TRACE(ev, it) do { if (trace_on && (it) < 32) g_attn_trace[(ev) * 32 + (it)] = clock64(); } while (0)
+#else
+#define NC_TRACE(ev, it) do { } while (0)
+#endif
+
 struct AttnBwdArgs {
   const float* lse;      // (B, H, Tq)
   const float* delta;    // (B, H, Tq)
@@ -87,6 +96,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef NC_ATTN_TRACE
+  const bool trace_on = DKV && blockIdx.x == 2 && blockIdx.y == 0 && blockIdx.z == 0 && (lane == 0) && (warp < 3);
+#endif
   const int xb = DKV ? blockIdx.x : (gridDim.x - 1 - blockIdx.x);
   const int hx = blockIdx.y, b = blockIdx.z;       // DKV: kv head ; DQ: q head
   const int group = args.H / args.Hkv;
@@ -142,6 +154,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         if (!mbar_wait(&in_empty[s], ph ^ 1, abort_flag, args.status, ST_WAIT_EMPTY, it)) break;
         uint8_t* y1 = sY + s * 2 * Y_TILE;
         uint8_t* y2 = y1 + Y_TILE;
+        NC_TRACE(7, it);
         mbar_arrive_expect_tx(&in_full[s], 2 * Y_TILE);
         tma_load_4d(y1, &tmY1, &in_full[s], 0, y0, head_y, b);
         tma_load_4d(y1 + Y_HALF, &tmY1, &in_full[s], 64, y0, head_y, b);
@@ -165,6 +178,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         const int bfr = i & 1; const uint32_t ph = (i >> 1) & 1;
         const int st = i % NS;
         if (!mbar_wait(&p_ready[bfr], ph, abort_flag, args.status, ST_WAIT_PEER, i)) return false;
+        NC_TRACE(1, i);
         tc_fence_after();
         const uint64_t m1 = dym0 + st * STAGE_STEP, m2 = m1 + Y2_STEP;
 #pragma unroll
@@ -190,6 +204,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         const int s = it & 1;
         const int st = it % NS; const uint32_t ph = (it / NS) & 1;
         if (!mbar_wait(&in_full[st], ph, abort_flag, args.status, ST_WAIT_FULL, it)) { ok = false; break; }
+        NC_TRACE(8, it);
         tc_fence_after();
         const uint64_t k1 = dyk0 + st * STAGE_STEP, k2 = k1 + Y2_STEP;
 #pragma unroll
@@ -205,6 +220,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
           mma_f16(tmem_base + COL_DP + s * BY, dx2 + xo, k2 + yo, idesc_s, kk != 0);
         }
         mma_commit(&s_full[s]);
+        NC_TRACE(0, it);
         if (it > 0 && !accumulate(it - 1)) { ok = false; break; }
       }
       if (ok && n_items > 0) ok = accumulate(n_items - 1);
@@ -241,11 +257,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         }
       }
       if (!mbar_wait(&s_full[s], ph, abort_flag, args.status, ST_WAIT_TMEM_FULL, it)) { ok = false; break; }
+      NC_TRACE(2, it);
       tc_fence_after();
       uint32_t sv[32], dv[32];
       tmem_ld32(tmem_base + lane_sel + COL_S + s * BY + half * 32, sv);
       tmem_ld32(tmem_base + lane_sel + COL_DP + s * BY + half * 32, dv);
       tmem_wait_ld();
+      NC_TRACE(3, it);
       // column vectors of buffer s were last read for item it-2; every compute warp finished that item before
       // its accumulate products (and therefore this item's S'/dP') could be issued
       if (DKV) {
@@ -256,6 +274,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         }
         if (!mbar_wait(&cv_ready[s], ph, abort_flag, args.status, ST_WAIT_PEER, 0x400 + it)) { ok = false; break; }
       }
+      NC_TRACE(4, it);
       // a block needs the element mask only if the causal diagonal, the window edge or the end of the
       // sequence passes through it
       const bool interior =
@@ -304,10 +323,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         }
       };
       if (interior) block(std::false_type{}); else block(std::true_type{});
+      NC_TRACE(5, it);
       // packed bf16 over the first 16 of this warp's own 32 fp32 columns (already in registers)
       if (DKV) tmem_st16(tmem_base + lane_sel + COL_S + s * BY + half * 32, pp);
       tmem_st16(tmem_base + lane_sel + COL_DP + s * BY + half * 32, dd);
       tmem_wait_st();
+      NC_TRACE(6, it);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_ready[s]);
@@ -444,3 +465,9 @@ cudaError_t attention_bwd(const AttnBwdDesc& d, int* status, cudaStream_t stream
 }
 
 }  // namespace nc
+
+#ifdef NC_ATTN_TRACE
+extern "C" int nc_attn_trace_read(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, nc::g_attn_trace, sizeof(long long) * 16 * 32);
+}
+#endif

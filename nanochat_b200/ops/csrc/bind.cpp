@@ -42,10 +42,18 @@ void check_bf16(const Tensor& t, const char* name) {
 const void* optptr(const optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
 
 // ------------------------------------------------------------------------------ GEMM
+// Operands are bf16, or 8-bit floats (e4m3 / e5m2, both operands) with optional per-tensor scales.
 void gemm(const Tensor& A, const Tensor& B, Tensor& C, const optional<Tensor>& aux, bool a_mn, bool b_mn,
-          double alpha, double beta, int64_t epi, int64_t bn) {
-  check_bf16(A, "A");
-  check_bf16(B, "B");
+          double alpha, double beta, int64_t epi, int64_t bn, int64_t pair, const optional<Tensor>& scale_a,
+          const optional<Tensor>& scale_b, const optional<Tensor>& amax_out) {
+  const bool fp8 = A.scalar_type() == at::kFloat8_e4m3fn || A.scalar_type() == at::kFloat8_e5m2;
+  if (fp8) {
+    TORCH_CHECK(A.is_cuda() && B.is_cuda(), "fp8 operands must be CUDA tensors");
+    TORCH_CHECK(B.scalar_type() == at::kFloat8_e4m3fn || B.scalar_type() == at::kFloat8_e5m2, "B must be fp8 like A");
+  } else {
+    check_bf16(A, "A");
+    check_bf16(B, "B");
+  }
   TORCH_CHECK(C.is_cuda() && (C.scalar_type() == at::kBFloat16 || C.scalar_type() == at::kFloat), "C dtype");
   TORCH_CHECK(A.dim() == B.dim() && A.dim() == C.dim() && (A.dim() == 2 || A.dim() == 3), "gemm rank");
   const c10::cuda::CUDAGuard guard(A.device());
@@ -70,8 +78,22 @@ void gemm(const Tensor& A, const Tensor& B, Tensor& C, const optional<Tensor>& a
     TORCH_CHECK(aux->scalar_type() == C.scalar_type() && aux->stride(nd - 1) == 1, "aux must match C");
     d.aux = aux->data_ptr(); d.ldaux = aux->stride(nd - 2); d.bsaux = nd == 3 ? aux->stride(0) : 0;
   }
-  d.alpha = (float)alpha; d.beta = (float)beta; d.epi = (int)epi; d.bn = (int)bn;
-  NC_CHECK(nc::gemm_bf16(d, status_ptr(A), cur_stream()));
+  d.alpha = (float)alpha; d.beta = (float)beta; d.epi = (int)epi; d.bn = (int)bn; d.pair = (int)pair;
+  auto scalar = [&](const optional<Tensor>& t, const char* n) -> float* {
+    if (!t.has_value() || !t->defined()) return nullptr;
+    TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->numel() == 1, n, " must be a CUDA fp32 scalar");
+    return t->data_ptr<float>();
+  };
+  d.scale_a = scalar(scale_a, "scale_a");
+  d.scale_b = scalar(scale_b, "scale_b");
+  d.amax_out = scalar(amax_out, "amax_out");
+  if (fp8) {
+    d.a_e5m2 = A.scalar_type() == at::kFloat8_e5m2;
+    d.b_e5m2 = B.scalar_type() == at::kFloat8_e5m2;
+    NC_CHECK(nc::gemm_fp8(d, status_ptr(A), cur_stream()));
+  } else {
+    NC_CHECK(nc::gemm_bf16(d, status_ptr(A), cur_stream()));
+  }
 }
 
 int64_t gemm_pick_bn(int64_t M, int64_t N, int64_t batch) { return nc::gemm_pick_bn((int)M, (int)N, (int)batch); }

@@ -22,6 +22,8 @@
 #include "host_utils.cuh"
 #include "ptx.cuh"
 
+#include <stdlib.h>
+
 namespace nc {
 
 constexpr int BM = 128;
@@ -299,6 +301,186 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
 }
 
+// ------------------------------------------------------------------ CTA-pair kernel
+// Same pipeline with cta_group::2: a cluster of two CTAs computes one 256 x BN tile. Each CTA loads its
+// own 128 rows of A and its own half (BN/2 columns) of B, so a k-block costs each SM 16 KB + BN/2 * 128 B
+// of shared-memory fill instead of 16 KB + BN * 128 B, and each tensor core reads half of B from its
+// partner. With one CTA per tile the fill plus the operand reads exceed what shared memory can deliver
+// while the tensor core runs; the pair brings the two into balance.
+//
+// Only the even CTA ("leader") issues MMAs. Barriers: full[s] lives in the leader and counts the bytes of
+// all four copies (the partner's TMA signals it through its cluster address); empty[s] and acc_full[a]
+// exist in both CTAs and the leader's MMA thread commits to each of them; acc_empty[a] lives in the
+// leader and collects the arrivals of the eight epilogue warps of the pair.
+template <int BN, bool A_MN, bool B_MN, bool FP8>
+struct PairCfg {
+  using Base = Cfg<BN, A_MN, B_MN, FP8>;
+  static constexpr int BK = Base::BK;
+  static constexpr int UMMA_K = Base::UMMA_K;
+  static constexpr int MN_CHUNK = Base::MN_CHUNK;
+  static constexpr int CHUNK_BYTES = Base::CHUNK_BYTES;
+  static constexpr int A_CHUNKS = Base::A_CHUNKS;
+  static constexpr int BNH = BN / 2;                                   // B columns held by one CTA
+  static constexpr int B_CHUNKS = (BNH + MN_CHUNK - 1) / MN_CHUNK;
+  static constexpr int A_BYTES = BM * ROW_BYTES;
+  static constexpr int B_TX = B_MN ? B_CHUNKS * CHUNK_BYTES : BNH * ROW_BYTES;
+  static constexpr int B_BYTES = (B_TX + 1023) / 1024 * 1024;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int MAX_STAGES = (227 * 1024 - 2048) / STAGE_BYTES;
+  static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
+  static constexpr int ACC_STRIDE = next_pow2_cols(BN);
+  static constexpr int TMEM_COLS = 2 * ACC_STRIDE;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+  static_assert(BN % 32 == 0 || BN == 208, "pair tiles: N/2 must stay a multiple of 8");
+};
+
+template <int BN, bool A_MN, bool B_MN, bool FP8>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmKernelArgs args) {
+  using C = PairCfg<BN, A_MN, B_MN, FP8>;
+  constexpr int BK = C::BK;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* acc_full = empty + C::STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader, 1 = partner
+  const int pair = blockIdx.x >> 1;
+  const int n_pairs = gridDim.x >> 1;
+  const int num_kb = (args.K + BK - 1) / BK;
+  const int total_tiles = args.m_blocks * args.n_blocks * args.batch;   // m_blocks counts 256-row blocks
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 8); }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
+  if (warp == 1) { tmem_alloc_pair(tmem_slot, C::TMEM_COLS); tmem_relinquish_pair(); }
+  tc_fence_before();
+  cluster_sync_all();                               // both CTAs' barriers exist before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
+        int b, mb, nb; tile_coords(t, args, b, mb, nb);
+        const int m0 = mb * (2 * BM) + rank * BM;
+        const int n0 = nb * BN + rank * C::BNH;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, args.status, ST_WAIT_EMPTY, t)) { ok = false; break; }
+          uint8_t* sA = tiles + stage * C::STAGE_BYTES;
+          uint8_t* sB = sA + C::A_BYTES;
+          const uint32_t bar = map_to_cta(smem_u32(&full[stage]), 0);
+          if (rank == 0) mbar_arrive_expect_tx(&full[stage], 2 * (C::A_BYTES + C::B_TX));
+          const int k0 = kb * BK;
+          if constexpr (A_MN) {
+#pragma unroll
+            for (int j = 0; j < C::A_CHUNKS; ++j)
+              tma_load_3d_pair(sA + j * C::CHUNK_BYTES, &tmA, bar, m0 + C::MN_CHUNK * j, k0, b);
+          } else {
+            tma_load_3d_pair(sA, &tmA, bar, k0, m0, b);
+          }
+          if constexpr (B_MN) {
+#pragma unroll
+            for (int j = 0; j < C::B_CHUNKS; ++j)
+              tma_load_3d_pair(sB + j * C::CHUNK_BYTES, &tmB, bar, n0 + C::MN_CHUNK * j, k0, b);
+          } else {
+            tma_load_3d_pair(sB, &tmB, bar, k0, n0, b);
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer (leader only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = args.idesc;
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      int acc = 0; uint32_t acc_phase = 0;
+      for (int t = pair; t < total_tiles && ok; t += n_pairs) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, args.status, ST_WAIT_TMEM_EMPTY, t)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * C::ACC_STRIDE;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, args.status, ST_WAIT_FULL, t)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + stage * C::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + C::A_BYTES;
+          const uint64_t a0 = A_MN ? umma_desc_sw128(a_addr, C::CHUNK_BYTES, 1024) : umma_desc_sw128(a_addr, 16, 1024);
+          const uint64_t b0 = B_MN ? umma_desc_sw128(b_addr, C::CHUNK_BYTES, 1024) : umma_desc_sw128(b_addr, 16, 1024);
+#pragma unroll
+          for (int k = 0; k < BK / C::UMMA_K; ++k) {
+            // one instruction consumes 32 bytes of K: 32 B along a K-major row, or UMMA_K rows of 128 B
+            const uint64_t ao = static_cast<uint64_t>((A_MN ? k * (C::UMMA_K * ROW_BYTES) : k * 32) >> 4);
+            const uint64_t bo = static_cast<uint64_t>((B_MN ? k * (C::UMMA_K * ROW_BYTES) : k * 32) >> 4);
+            mma_pair<FP8>(d_tmem, a0 + ao, b0 + bo, idesc, (kb | k) != 0);
+          }
+          // frees the stage in both CTAs once these MMAs have read it
+          mma_commit_pair(smem_u32(&empty[stage]));
+          mma_commit_pair(map_to_cta(smem_u32(&empty[stage]), 1));
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit_pair(smem_u32(&acc_full[acc]));
+        mma_commit_pair(map_to_cta(smem_u32(&acc_full[acc]), 1));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
+    const int quad = warp & 3;
+    int acc = 0; uint32_t acc_phase = 0; bool ok = true;
+    float amax = 0.f;
+    float alpha = args.alpha;
+    if (args.scale_a) alpha *= __ldg(args.scale_a);
+    if (args.scale_b) alpha *= __ldg(args.scale_b);
+    const float beta = args.beta;
+    for (int t = pair; t < total_tiles && ok; t += n_pairs) {
+      int b, mb, nb; tile_coords(t, args, b, mb, nb);
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, args.status, ST_WAIT_TMEM_FULL, t)) { ok = false; break; }
+      tc_fence_after();
+      const int row = mb * (2 * BM) + rank * BM + quad * 32 + lane;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC_STRIDE;
+      store_tile_row<BN>(args, taddr, b, row, nb * BN, alpha, beta, amax);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (args.amax_out) {
+#pragma unroll
+      for (int w = 16; w > 0; w >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, w));
+      if (lane == 0 && amax > 0.f) atomicMax(reinterpret_cast<unsigned int*>(args.amax_out), __float_as_uint(amax));
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncthreads();
+  if (*abort_flag) {
+    unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  cluster_sync_all();       // the partner may still signal this CTA's barriers or read its operands until here
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, C::TMEM_COLS);
+  }
+}
+
 // ----------------------------------------------------------------------------- host
 
 template <int BN, bool A_MN, bool B_MN, bool FP8>
@@ -363,8 +545,84 @@ static cudaError_t launch_bn(int bn, const GemmDesc& d, int* status, cudaStream_
   }
 }
 
+template <int BN, bool A_MN, bool B_MN, bool FP8>
+static cudaError_t launch_pair_cfg(const GemmDesc& d, int* status, cudaStream_t stream) {
+  using C = PairCfg<BN, A_MN, B_MN, FP8>;
+  constexpr int BK = C::BK;
+  constexpr int ELT = Cfg<BN, A_MN, B_MN, FP8>::ELT;
+  static bool configured = false;
+  auto kern = gemm_pair_kernel<BN, A_MN, B_MN, FP8>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  const CUtensorMapDataType dt = FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap tmA, tmB;
+  const uint64_t batch = static_cast<uint64_t>(d.batch);
+  {
+    uint64_t dims[3], str[2]; uint32_t box[3];
+    if (A_MN) { dims[0] = d.M; dims[1] = d.K; box[0] = C::MN_CHUNK; box[1] = BK; }
+    else      { dims[0] = d.K; dims[1] = d.M; box[0] = BK; box[1] = BM; }
+    dims[2] = batch; box[2] = 1;
+    str[0] = static_cast<uint64_t>(d.lda) * ELT;
+    str[1] = d.batch > 1 ? static_cast<uint64_t>(d.bsa) * ELT : str[0] * dims[1];
+    if (!make_tmap(&tmA, dt, 3, d.A, dims, str, box)) return cudaErrorInvalidValue;
+  }
+  {
+    uint64_t dims[3], str[2]; uint32_t box[3];
+    if (B_MN) { dims[0] = d.N; dims[1] = d.K; box[0] = C::MN_CHUNK; box[1] = BK; }
+    else      { dims[0] = d.K; dims[1] = d.N; box[0] = BK; box[1] = C::BNH; }      // each CTA loads half of the columns
+    dims[2] = batch; box[2] = 1;
+    str[0] = static_cast<uint64_t>(d.ldb) * ELT;
+    str[1] = d.batch > 1 ? static_cast<uint64_t>(d.bsb) * ELT : str[0] * dims[1];
+    if (!make_tmap(&tmB, dt, 3, d.B, dims, str, box)) return cudaErrorInvalidValue;
+  }
+  GemmKernelArgs a;
+  a.M = d.M; a.N = d.N; a.K = d.K; a.batch = d.batch;
+  a.C = d.C; a.ldc = d.ldc; a.bsc = d.bsc;
+  a.aux = d.aux; a.ldaux = d.ldaux; a.bsaux = d.bsaux;
+  a.alpha = d.alpha; a.beta = d.beta; a.epi = d.epi; a.c_f32 = d.c_f32;
+  a.scale_a = d.scale_a; a.scale_b = d.scale_b; a.amax_out = d.amax_out;
+  a.m_blocks = (d.M + 2 * BM - 1) / (2 * BM);
+  a.n_blocks = (d.N + BN - 1) / BN;
+  a.group_m = 8;
+  a.idesc = FP8 ? umma_idesc_f8(2 * BM, BN, A_MN, B_MN, d.a_e5m2, d.b_e5m2) : umma_idesc_bf16(2 * BM, BN, A_MN, B_MN);
+  a.status = status;
+  const long long tiles = 1ll * a.m_blocks * a.n_blocks * d.batch;
+  const int max_pairs = sm_count() / 2;
+  const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(GEMM_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, a);
+}
+
+template <bool A_MN, bool B_MN, bool FP8>
+static cudaError_t launch_pair_bn(int bn, const GemmDesc& d, int* status, cudaStream_t s) {
+  switch (bn) {
+    case 256: return launch_pair_cfg<256, A_MN, B_MN, FP8>(d, status, s);
+    case 208: return launch_pair_cfg<208, A_MN, B_MN, FP8>(d, status, s);
+    case 128: return launch_pair_cfg<128, A_MN, B_MN, FP8>(d, status, s);
+    default:  return cudaErrorInvalidValue;
+  }
+}
+
 template <bool FP8>
-static cudaError_t launch_major(int bn, const GemmDesc& d, int* status, cudaStream_t stream) {
+static cudaError_t launch_major(int bn, bool pair, const GemmDesc& d, int* status, cudaStream_t stream) {
+  if (pair) {
+    if (d.a_mn && d.b_mn) return launch_pair_bn<true, true, FP8>(bn, d, status, stream);
+    if (!d.a_mn && d.b_mn) return launch_pair_bn<false, true, FP8>(bn, d, status, stream);
+    if (!d.a_mn && !d.b_mn) return launch_pair_bn<false, false, FP8>(bn, d, status, stream);
+    return launch_pair_bn<true, false, FP8>(bn, d, status, stream);
+  }
   if (d.a_mn && d.b_mn) return launch_bn<true, true, FP8>(bn, d, status, stream);
   if (!d.a_mn && d.b_mn) return launch_bn<false, true, FP8>(bn, d, status, stream);
   if (!d.a_mn && !d.b_mn) return launch_bn<false, false, FP8>(bn, d, status, stream);
@@ -389,19 +647,64 @@ int gemm_pick_bn(int M, int N, int batch) {
   return pick;
 }
 
+// Tile plan: N tile and kernel flavour. Scores are (relative tile efficiency) x (useful fraction of the padded
+// tile grid) x (fill of the last wave); the efficiencies are measured rates of the d26 layer shapes relative to
+// the single-CTA 128 x 256 tile. The CTA-pair kernel needs at least two 256-row blocks to be worth a cluster.
+struct GemmPlan { int bn; bool pair; };
+static bool best_is_invalid(const GemmPlan& p, const GemmDesc& d) {
+  if (d.bn > 0 && p.bn != d.bn) return true;                  // the requested tile has no kernel of the requested flavour
+  return p.pair && p.bn != 256 && p.bn != 208 && p.bn != 128;
+}
+static GemmPlan gemm_plan(const GemmDesc& d, bool fp8) {
+  static const int env_pair = [] { const char* e = getenv("NANOCHAT_GEMM_PAIR"); return e ? atoi(e) : 1; }();
+  const int sms = sm_count();
+  auto score = [&](int bn, bool pair, double eff) {
+    const long long rows = pair ? 2 * BM : BM;
+    const long long mb = (d.M + rows - 1) / rows, nb = (d.N + bn - 1) / bn;
+    const long long tiles = mb * nb * d.batch;
+    const long long slots = pair ? sms / 2 : sms;
+    const long long waves = (tiles + slots - 1) / slots;
+    return eff * (double(d.N) / double(nb * bn)) * (double(d.M) / double(mb * rows)) *
+           (double(tiles) / double(waves * slots));
+  };
+  GemmPlan best{128, false};
+  double best_score = -1;
+  const bool pair_ok = d.pair > 0 || (d.pair < 0 && env_pair > 0 && d.M > 2 * BM);
+  const bool single_ok = d.pair <= 0;
+  static const int cand[5] = {256, 208, 128, 64, 32};
+  static const double eff1[5] = {1.0, 0.98, 0.86, 0.62, 0.36};
+  static const double eff2[3] = {1.14, 1.08, 0.95};
+  for (int i = 0; i < 5; ++i) {
+    if (d.bn > 0 && cand[i] != d.bn) continue;
+    if (single_ok) {
+      const double sc = score(cand[i], false, eff1[i]);
+      if (sc > best_score + 1e-9) { best_score = sc; best = {cand[i], false}; }
+    }
+    if (pair_ok && i < 3) {
+      // fp8, MN-major B: the partner's half of a 208-wide tile would start a TMA copy off a 16-byte boundary
+      if (fp8 && d.b_mn && cand[i] == 208) continue;
+      const double sc = score(cand[i], true, eff2[i]);
+      if (sc > best_score + 1e-9) { best_score = sc; best = {cand[i], true}; }
+    }
+  }
+  return best;
+}
+
 cudaError_t gemm_bf16(const GemmDesc& d, int* status, cudaStream_t stream) {
   if (d.M <= 0 || d.N <= 0 || d.K <= 0 || d.batch <= 0) return cudaErrorInvalidValue;
   if ((d.N & 7) || (d.lda & 7) || (d.ldb & 7) || (d.ldc & 3)) return cudaErrorInvalidValue;
-  const int bn = d.bn > 0 ? d.bn : gemm_pick_bn(d.M, d.N, d.batch);
-  return launch_major<false>(bn, d, status, stream);
+  const GemmPlan p = gemm_plan(d, false);
+  if (best_is_invalid(p, d)) return cudaErrorInvalidValue;
+  return launch_major<false>(p.bn, p.pair, d, status, stream);
 }
 
 cudaError_t gemm_fp8(const GemmDesc& d, int* status, cudaStream_t stream) {
   if (d.M <= 0 || d.N <= 0 || d.K <= 0 || d.batch <= 0) return cudaErrorInvalidValue;
   // TMA strides are multiples of 16 bytes; output rows as for the bf16 kernel
   if ((d.N & 7) || (d.lda & 15) || (d.ldb & 15) || (d.ldc & 3)) return cudaErrorInvalidValue;
-  const int bn = d.bn > 0 ? d.bn : gemm_pick_bn(d.M, d.N, d.batch);
-  return launch_major<true>(bn, d, status, stream);
+  const GemmPlan p = gemm_plan(d, true);
+  if (best_is_invalid(p, d)) return cudaErrorInvalidValue;
+  return launch_major<true>(p.bn, p.pair, d, status, stream);
 }
 
 }  // namespace nc

@@ -34,6 +34,8 @@ struct GemmDesc {
   float* amax_out = nullptr;
   // gemm_fp8 only: operand element formats (0 = e4m3, 1 = e5m2)
   int a_e5m2 = 0, b_e5m2 = 0;
+  // CTA-pair kernel (256 x BN tiles on two SMs): 1 = use it, 0 = never, -1 = let the library decide
+  int pair = -1;
 };
 
 cudaError_t gemm_bf16(const GemmDesc& d, int* status, cudaStream_t stream);

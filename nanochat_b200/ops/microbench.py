@@ -45,10 +45,31 @@ def _attn_pairs(T, window):
     return sum(min(i, window) + 1 for i in range(T))
 
 
+def _operand(shape, dtype):
+    """Random operand; 8-bit floats come with the de-quantisation scale of a per-tensor scaling."""
+    x = torch.randn(shape, device="cuda")
+    if dtype == "bf16":
+        return x.to(torch.bfloat16), None
+    t = torch.float8_e4m3fn
+    scale = x.abs().max() / torch.finfo(t).max
+    return (x / scale).to(t), scale.reshape(1).float()
+
+
 def bench_gemm(args, nat):
     m, n, k = args.m, args.n, args.k
     bf16 = torch.bfloat16
     dev = "cuda"
+    if args.dtype == "fp8" or args.pair >= 0:
+        shapes = {"fwd": ((m, k), (n, k)), "dgrad": ((m, k), (k, n)), "wgrad": ((k, m), (k, n))}[args.layout]
+        (A, sa), (B, sb) = _operand(shapes[0], args.dtype), _operand(shapes[1], args.dtype)
+        wg = args.layout == "wgrad"
+        C = torch.zeros(m, n, device=dev, dtype=torch.float32 if wg else bf16)
+        kw = dict(a_mn=wg, b_mn=args.layout != "fwd", bn=args.bn, pair=args.pair, scale_a=sa, scale_b=sb)
+        if wg:
+            kw.update(aux=C, beta=1.0)
+        ms = _time(lambda: nat.gemm(A, B, C, **kw), args.iters, args.warmup)
+        return dict(op=f"gemm/{args.layout}", dtype=args.dtype, pair=args.pair, m=m, n=n, k=k, bn=args.bn, ms=ms,
+                    tflops=2.0 * m * n * k / ms / 1e9)
     if args.layout == "fwd":        # y[m,n] = x[m,k] W[n,k]^T
         A = torch.randn(m, k, device=dev).to(bf16)
         B = torch.randn(n, k, device=dev).to(bf16)
@@ -108,6 +129,8 @@ def main():
     ap.add_argument("--k", type=int, default=1664)
     ap.add_argument("--bn", type=int, default=0, help="N tile (0 = heuristic)")
     ap.add_argument("--layout", default="fwd", choices=["fwd", "dgrad", "wgrad"])
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"], help="GEMM operand type")
+    ap.add_argument("--pair", type=int, default=-1, help="GEMM: 1 = CTA-pair kernel, 0 = single-CTA kernel, -1 = library choice")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=13)

@@ -123,9 +123,12 @@ def mark_shadow_fresh(w):
 
 # -------------------------------------------------------------------------------- GEMM
 
-def gemm(A, B, out, *, a_mn=False, b_mn=False, aux=None, alpha=1.0, beta=0.0, epi=EPI_LINEAR, bn=0):
-    """out = epilogue(alpha * A @ B^T, aux); see csrc/gemm.h for the operand conventions."""
-    _C.gemm(A, B, out, aux, a_mn, b_mn, alpha, beta, epi, bn)
+def gemm(A, B, out, *, a_mn=False, b_mn=False, aux=None, alpha=1.0, beta=0.0, epi=EPI_LINEAR, bn=0, pair=-1,
+         scale_a=None, scale_b=None, amax_out=None):
+    """out = epilogue(alpha * A @ B^T, aux); see csrc/gemm.h for the operand conventions. A and B are bf16, or
+    both 8-bit floats with optional device-scalar scales (multiplied into alpha by the kernel). `pair` selects
+    the CTA-pair kernel (1), the single-CTA kernel (0) or the library's choice (-1)."""
+    _C.gemm(A, B, out, aux, a_mn, b_mn, alpha, beta, epi, bn, pair, scale_a, scale_b, amax_out)
     return out
 
 

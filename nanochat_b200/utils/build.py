@@ -80,7 +80,8 @@ def build_cuda_extension(verbose=False, force=False):
     so_path = os.path.join(PKG_DIR, name + EXT_SUFFIX)
     cus, cpps = cuda_sources()
     headers = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh"))
-    digest = _hash_files(cus + cpps + headers, extra=torch.__version__)
+    extra_flags = os.environ.get("NANOCHAT_NVCC_FLAGS", "").split()     # e.g. -DNC_ATTN_TRACE for kernel timelines
+    digest = _hash_files(cus + cpps + headers, extra=torch.__version__ + " ".join(extra_flags))
     if not force and not _stale(so_path, digest):
         return so_path
     os.makedirs(BUILD_DIR, exist_ok=True)
@@ -96,7 +97,7 @@ def build_cuda_extension(verbose=False, force=False):
     for src in cus:
         obj = os.path.join(BUILD_DIR, os.path.basename(src) + ".o")
         cmd = [nvcc, *NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", "--use_fast_math", "-Xcompiler", "-fPIC",
-               "-Xptxas", "-v" if verbose else "-O3", "-I", CSRC, "-c", src, "-o", obj]
+               "-Xptxas", "-v" if verbose else "-O3", *extra_flags, "-I", CSRC, "-c", src, "-o", obj]
         jobs.append((cmd, obj))
     for src in cpps:
         obj = os.path.join(BUILD_DIR, os.path.basename(src) + ".o")

@@ -1,0 +1,112 @@
+"""
+GPU numerics of the GEMM variants against plain PyTorch fp32 references:
+the CTA-pair (cta_group::2, 256 x BN tiles) kernel in every operand layout, and the 8-bit float
+(e4m3 / e5m2, per-tensor scaled) kernels in the three layouts a linear layer needs.
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+BF16 = torch.bfloat16
+
+
+@pytest.fixture(scope="module")
+def nat():
+    from nanochat_b200.ops import native
+    return native
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+def _mk(shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return torch.randn(shape, device="cuda", generator=g) * scale
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K,bn", [
+    (256, 256, 64, 256), (512, 256, 192, 256), (512, 416, 128, 208), (768, 128, 320, 128),
+    (304, 520, 136, 256), (1280, 1664, 1664, 208), (4992, 1664, 2048, 256),
+])
+def test_pair_gemm_layouts(nat, M, N, K, bn, a_mn, b_mn):
+    A = _mk((K, M) if a_mn else (M, K), seed=1).to(BF16)
+    B = _mk((K, N) if b_mn else (N, K), seed=2).to(BF16)
+    C = torch.empty(M, N, dtype=BF16, device="cuda")
+    nat.gemm(A, B, C, a_mn=a_mn, b_mn=b_mn, bn=bn, pair=1)
+    nat.check_status(C)
+    ref = (A.float().t() if a_mn else A.float()) @ (B.float() if b_mn else B.float().t())
+    assert _rel_err(C, ref) < 1e-2, (M, N, K, bn, a_mn, b_mn)
+
+
+def test_pair_gemm_epilogues_batched_and_accumulate(nat):
+    M, N, K = 512, 512, 256
+    A, B = _mk((M, K), seed=3).to(BF16), _mk((N, K), seed=4).to(BF16)
+    ref = A.float() @ B.float().t()
+    out = torch.empty(M, N, dtype=BF16, device="cuda")
+    nat.gemm(A, B, out, epi=nat.EPI_RELU2, pair=1)
+    assert _rel_err(out, torch.relu(ref) ** 2) < 1e-2
+    aux = _mk((M, N), seed=5).to(BF16)
+    nat.gemm(A, B, out, aux=aux, alpha=0.5, beta=2.0, pair=1)
+    assert _rel_err(out, 0.5 * ref + 2.0 * aux.float()) < 1e-2
+    # wgrad form: fp32 C += A^T B, both operands MN-major, twice into the same buffer
+    dy, x = _mk((1024, M), seed=6).to(BF16), _mk((1024, N), seed=7).to(BF16)
+    acc = torch.zeros(M, N, device="cuda")
+    nat.gemm(dy, x, acc, a_mn=True, b_mn=True, pair=1)
+    nat.gemm(dy, x, acc, a_mn=True, b_mn=True, aux=acc, beta=1.0, pair=1)
+    assert _rel_err(acc, 2 * (dy.float().t() @ x.float())) < 1e-2
+    # batched
+    Ab, Bb = _mk((3, M, K), seed=8).to(BF16), _mk((3, N, K), seed=9).to(BF16)
+    Cb = torch.empty(3, M, N, dtype=BF16, device="cuda")
+    nat.gemm(Ab, Bb, Cb, pair=1)
+    assert _rel_err(Cb, Ab.float() @ Bb.float().transpose(1, 2)) < 1e-2
+    nat.check_status(Cb)
+
+
+def _quant(x, dtype):
+    """Per-tensor scaling to the format's range; returns (fp8 tensor, de-quantisation scale as a CUDA scalar)."""
+    fmax = torch.finfo(dtype).max
+    scale = x.abs().max().float().clamp(min=1e-12) / fmax
+    return (x.float() / scale).clamp(-fmax, fmax).to(dtype), scale.reshape(1)
+
+
+@pytest.mark.parametrize("pair", [0, 1])
+@pytest.mark.parametrize("M,N,K,bn", [(256, 256, 128, 256), (512, 416, 384, 208), (384, 128, 256, 128), (1024, 1664, 1664, 0)])
+def test_fp8_gemm_three_layouts(nat, M, N, K, bn, pair):
+    e4, e5 = torch.float8_e4m3fn, torch.float8_e5m2
+    if pair and bn == 0:
+        bn = 256
+    # forward: y = x W^T, both e4m3, K-major
+    x, w = _mk((M, K), seed=1), _mk((N, K), seed=2, scale=0.05)
+    xq, sx = _quant(x, e4)
+    wq, sw = _quant(w, e4)
+    y = torch.empty(M, N, dtype=BF16, device="cuda")
+    nat.gemm(xq, wq, y, scale_a=sx, scale_b=sw, bn=bn, pair=pair)
+    ref = (xq.float() * sx) @ (wq.float() * sw).t()
+    assert _rel_err(y, ref) < 1e-2
+    assert _rel_err(y, x @ w.t()) < 8e-2          # quantisation error of e4m3 x e4m3
+    # dgrad: dx = dy W, dy e5m2 (K-major, reduction over N), W e4m3 read MN-major
+    dy = _mk((M, N), seed=3, scale=1e-3)
+    dyq, sdy = _quant(dy, e5)
+    dx = torch.empty(M, K, dtype=BF16, device="cuda")
+    nat.gemm(dyq, wq, dx, b_mn=True, scale_a=sdy, scale_b=sw, pair=pair)
+    ref = (dyq.float() * sdy) @ (wq.float() * sw)
+    assert _rel_err(dx, ref) < 1e-2
+    # wgrad: dW = dy^T x, both MN-major, fp32 accumulate
+    dw = torch.zeros(N, K, device="cuda")
+    nat.gemm(dyq, xq, dw, a_mn=True, b_mn=True, scale_a=sdy, scale_b=sx, pair=pair)
+    ref = (dyq.float() * sdy).t() @ (xq.float() * sx)
+    assert _rel_err(dw, ref) < 1e-2
+    nat.check_status(y)
+
+
+def test_gemm_amax_output(nat):
+    M, N, K = 512, 384, 256
+    A, B = _mk((M, K), seed=3).to(BF16), _mk((N, K), seed=4).to(BF16)
+    out = torch.empty(M, N, dtype=BF16, device="cuda")
+    amax = torch.zeros(1, device="cuda")
+    nat.gemm(A, B, out, amax_out=amax)
+    assert abs(amax.item() - out.float().abs().max().item()) <= 1e-2 * amax.item()
