@@ -45,6 +45,8 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end region (debugging)")
     ap.add_argument("--comm", type=str, default="auto", choices=["auto", "fused", "nccl"],
                     help="optimizer collectives for N>1: fused peer-to-peer kernels or NCCL")
+    ap.add_argument("--precision", type=str, default="fp8", choices=["fp8", "bf16"],
+                    help="our arm: fp8 = tensorwise e4m3/e5m2 linear layers (the reference's headline recipe)")
     ap.add_argument("--ref-bf16", action="store_true", help="reference arm without --fp8")
     ap.add_argument("--ref-eager", action="store_true", help="reference arm without torch.compile")
     return ap.parse_args()
@@ -151,6 +153,12 @@ def run_ours(args):
     _, _, _, _, device = common.compute_init("cuda")
     assert common.COMPUTE_DTYPE == torch.bfloat16
     model, cfg = build_ours(args, device)
+    dtype = "bf16"
+    if args.precision == "fp8":
+        from nanochat_b200.fp8 import Float8LinearConfig, convert_to_float8_training, default_fp8_filter
+        convert_to_float8_training(model, config=Float8LinearConfig.from_recipe_name("tensorwise"),
+                                   module_filter_fn=default_fp8_filter)
+        dtype = "fp8 (tensorwise e4m3/e5m2 linears, bf16 elsewhere)"
     from nanochat_b200.train import TrainStep
     B, T = args.device_batch_size, args.seq_len
     assert args.total_batch_size % (B * T * world) == 0
@@ -216,7 +224,7 @@ def run_ours(args):
     out = {
         "metric": "d26 pretrain tokens/sec (whole job)", "value": tok_s, "unit": "tokens/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": tok_s / PUBLISHED_TOK_PER_SEC, "dtype": "bf16", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": tok_s / PUBLISHED_TOK_PER_SEC, "dtype": dtype, "data": "synthetic",
         "impl": "ours",
         "config": {"model": f"d{args.depth}", "global_batch": args.total_batch_size, "seq_len": T,
                    "device_batch": B, "grad_accum": accum, "window_pattern": args.window_pattern,

@@ -154,7 +154,21 @@ def convert_to_float8_training(module, *, config=None, module_filter_fn=None):
                 if module_filter_fn is None or module_filter_fn(child, fqn):
                     setattr(mod, name, Float8Linear.from_float(child, recipe))
     walk(module)
+    if recipe == "tensorwise":
+        _set_native_fp8(True)
     return module
+
+
+def _set_native_fp8(enabled):
+    """The fused sm_100a layer path does not go through the nn.Linear modules: it has its own switch."""
+    from nanochat_b200 import ops
+    if _native_active():
+        ops.native_module().set_fp8(enabled)
+
+
+def _native_active():
+    from nanochat_b200 import ops
+    return ops.get_kernel_mode() == "native" and torch.cuda.is_available()
 
 
 @contextmanager
@@ -163,8 +177,14 @@ def fp8_disabled(model):
     mods = [m for m in model.modules() if isinstance(m, Float8Linear)]
     for m in mods:
         m.fp8_enabled = False
+    from nanochat_b200 import ops
+    native_was_on = _native_active() and ops.native_module().fp8_enabled()
+    if native_was_on:
+        _set_native_fp8(False)
     try:
         yield
     finally:
         for m in mods:
             m.fp8_enabled = True
+        if native_was_on:
+            _set_native_fp8(True)

@@ -367,6 +367,8 @@ class GPT(nn.Module):
         """Whole-sequence forward on the sm_100a kernels: one fused autograd node per layer."""
         nat = ops.native_module()
         assert idx.size(1) > 1, "Training forward pass should have T > 1"
+        if nat.fp8_enabled():
+            nat.begin_microstep(idx.device)
         x, _ = nat.embed_norm_smear(idx, self.transformer.wte.weight, self.smear_gate.weight, self.smear_lambda)
         x0 = x
         backout_layer = self.config.n_layer // 2

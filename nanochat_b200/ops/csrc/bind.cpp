@@ -188,6 +188,28 @@ void embed_bwd(const Tensor& dx, const Tensor& idx, const Tensor& wte, const Ten
                          gate_w.data_ptr<float>(), lam.data_ptr<float>(), dwte.data_ptr<float>(),
                          dgate_w.data_ptr<float>(), dlam.data_ptr<float>(), M, T, C, cur_stream()));
 }
+// x: bf16 (rows, cols), rows may be strided. amax: fp32 scalar (accumulates a max; zero it first).
+void amax_bf16(const Tensor& x, Tensor& amax) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "amax: 2-D, innermost contiguous");
+  TORCH_CHECK(amax.is_cuda() && amax.scalar_type() == at::kFloat && amax.numel() == 1, "amax scalar");
+  const c10::cuda::CUDAGuard guard(x.device());
+  NC_CHECK(nc::amax_bf16(x.data_ptr(), x.stride(0), (int)x.size(0), (int)x.size(1), amax.data_ptr<float>(), cur_stream()));
+}
+// q: fp8 (e4m3fn or e5m2) dense (rows, cols); inv_scale: fp32 scalar that receives the de-quantisation factor.
+void quantize_bf16(const Tensor& x, const Tensor& amax, Tensor& q, Tensor& inv_scale) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "quantize: 2-D, innermost contiguous");
+  const bool e5 = q.scalar_type() == at::kFloat8_e5m2;
+  TORCH_CHECK(q.is_cuda() && (e5 || q.scalar_type() == at::kFloat8_e4m3fn) && q.is_contiguous() &&
+              q.numel() == x.numel(), "q must be a dense fp8 tensor of x's size");
+  TORCH_CHECK(amax.scalar_type() == at::kFloat && inv_scale.scalar_type() == at::kFloat && amax.numel() == 1 &&
+              inv_scale.numel() == 1, "scalars");
+  const c10::cuda::CUDAGuard guard(x.device());
+  NC_CHECK(nc::quantize_bf16(x.data_ptr(), x.stride(0), (int)x.size(0), (int)x.size(1), amax.data_ptr<float>(),
+                             q.data_ptr(), inv_scale.data_ptr<float>(), e5 ? 1 : 0, cur_stream()));
+}
+
 void cast_f32_bf16(const Tensor& src, Tensor& dst) {
   const c10::cuda::CUDAGuard guard(src.device());
   TORCH_CHECK(src.is_contiguous() && dst.is_contiguous() && src.numel() == dst.numel(), "cast shapes");
@@ -350,6 +372,8 @@ void p2p_small_adamw(const std::vector<int64_t>& grads, int64_t grad_off, Tensor
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_pick_bn", &gemm_pick_bn);
+  m.def("amax_bf16", &amax_bf16);
+  m.def("quantize_bf16", &quantize_bf16);
   m.def("read_status", &read_status);
   m.def("launch_count", &launch_count);
   m.def("mixnorm_fwd", &mixnorm_fwd);

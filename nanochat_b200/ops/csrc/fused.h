@@ -32,6 +32,13 @@ cudaError_t embed_bwd(const void* dx, const long long* idx, const void* wte, con
                       float* dwte, float* dgate_w, float* dlam, int M, int T, int C, cudaStream_t s);
 cudaError_t cast_f32_bf16(const float* src, void* dst, size_t n, cudaStream_t s);
 
+// ---- per-tensor scaling to 8-bit floats (quant.cu); x is bf16 [rows][cols] with row pitch ld (elements)
+// amax: atomic max of |x| into *amax (zero it first). quantize: q = sat(x * FMAX/amax) dense [rows][cols],
+// *inv_scale = amax/FMAX; e5m2 selects the 5-bit-exponent format (FMAX 57344) instead of e4m3 (448).
+cudaError_t amax_bf16(const void* x, long long ld, int rows, int cols, float* amax, cudaStream_t s);
+cudaError_t quantize_bf16(const void* x, long long ld, int rows, int cols, const float* amax, void* q,
+                          float* inv_scale, int e5m2, cudaStream_t s);
+
 // ---- soft-capped cross entropy over bf16 logits (loss.cu)
 // loss[row] = logsumexp(cap*tanh(l/cap)) - cap*tanh(l[target]/cap); 0 for target < 0. lse is saved.
 cudaError_t softcap_ce_fwd(const void* logits, long long ld, const long long* targets, float* loss, float* lse,

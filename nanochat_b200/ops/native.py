@@ -104,6 +104,7 @@ def shadow_of(w):
     else:
         buf.copy_(src)
     _shadow.set(w, ver, buf)
+    bump_weights_epoch()
     return buf
 
 
@@ -119,6 +120,7 @@ def mark_shadow_fresh(w):
     ent = _shadow.get(w)
     if ent is not None:
         _shadow.set(w, w._version, ent[1])
+    bump_weights_epoch()
 
 
 # -------------------------------------------------------------------------------- GEMM
@@ -132,21 +134,101 @@ def gemm(A, B, out, *, a_mn=False, b_mn=False, aux=None, alpha=1.0, beta=0.0, ep
     return out
 
 
+# ------------------------------------------------------------------------- fp8 matmuls
+# Tensorwise dynamic scaling as in the reference's Float8Linear (nanochat/fp8.py:125-193): activations and
+# weights go to e4m3, output gradients to e5m2, every operand with one scale = FMAX / amax; all three GEMMs
+# of a linear layer (forward, dgrad, wgrad) then run on 8-bit operands with fp32 accumulation. Differences:
+# the fused QKV weight carries one scale (the reference has three modules), a weight is quantised once per
+# optimizer step instead of once per forward, and tensors produced by a GEMM get their amax from its epilogue.
+E4M3, E5M2 = torch.float8_e4m3fn, torch.float8_e5m2
+_fp8_enabled = False
+_weights_epoch = 0
+_fp8_weights = {}
+_amax_pool = None
+_amax_next = 0
+
+
+def set_fp8(enabled):
+    """Run the linear layers of the transformer blocks (and lm_head) on fp8 tensor-core GEMMs."""
+    global _fp8_enabled
+    _fp8_enabled = bool(enabled)
+
+
+def fp8_enabled():
+    return _fp8_enabled
+
+
+def bump_weights_epoch():
+    """Called whenever parameters changed (optimizer step, checkpoint load): cached fp8 weights are stale."""
+    global _weights_epoch
+    _weights_epoch += 1
+
+
+def begin_microstep(device):
+    """Re-arm the pool of zeroed amax scalars; one fill kernel per micro-batch instead of one per tensor."""
+    global _amax_pool, _amax_next
+    if _amax_pool is None or _amax_pool.device != device:
+        _amax_pool = torch.zeros(2048, dtype=torch.float32, device=device)
+    else:
+        _amax_pool.zero_()
+    _amax_next = 0
+
+
+def _zeroed_scalar(device):
+    global _amax_next
+    if _amax_pool is None or _amax_pool.device != device or _amax_next >= _amax_pool.numel():
+        return torch.zeros(1, dtype=torch.float32, device=device)
+    s = _amax_pool[_amax_next:_amax_next + 1]
+    _amax_next += 1
+    return s
+
+
+def quantize(x2, dtype=E4M3, amax=None):
+    """(fp8 copy, de-quantisation scale) of a bf16 matrix; `amax` = device scalar holding max|x| if already known."""
+    if amax is None:
+        amax = _zeroed_scalar(x2.device)
+        _C.amax_bf16(x2, amax)
+    q = torch.empty(x2.shape, dtype=dtype, device=x2.device)
+    inv = torch.empty(1, dtype=torch.float32, device=x2.device)
+    _C.quantize_bf16(x2, amax, q, inv)
+    return q, inv
+
+
+def fp8_weight(w_bf16):
+    """e4m3 copy + scale of a bf16 weight matrix (or fused stack), cached until the next optimizer step."""
+    key = (w_bf16.data_ptr(), tuple(w_bf16.shape))
+    ent = _fp8_weights.get(key)
+    if ent is not None and ent[0] == _weights_epoch:
+        return ent[1], ent[2]
+    amax = torch.zeros(1, dtype=torch.float32, device=w_bf16.device)
+    _C.amax_bf16(w_bf16, amax)
+    q = ent[1] if ent is not None else torch.empty(w_bf16.shape, dtype=E4M3, device=w_bf16.device)
+    inv = ent[2] if ent is not None else torch.empty(1, dtype=torch.float32, device=w_bf16.device)
+    _C.quantize_bf16(w_bf16, amax, q, inv)
+    _fp8_weights[key] = (_weights_epoch, q, inv)
+    return q, inv
+
+
+def _fp8_ok(*dims):
+    return _fp8_enabled and all(d % 16 == 0 for d in dims)
+
+
 def _rows(x):
     x2 = x.reshape(-1, x.shape[-1])
     return x2 if x2.stride(-1) == 1 else x2.contiguous()
 
 
-def _accumulate_wgrad(w, dy2, x2):
-    """w.grad (fp32) += dy2^T @ x2, fused in the GEMM epilogue."""
+def _accumulate_wgrad(w, dy2, x2, scale_a=None, scale_b=None):
+    """w.grad (fp32) += dy2^T @ x2, fused in the GEMM epilogue (bf16 operands, or fp8 with their scales)."""
+    kw = dict(a_mn=True, b_mn=True, scale_a=scale_a, scale_b=scale_b)
     if w.grad is None:
         w.grad = torch.empty_like(w, dtype=w.dtype)
-        gemm(dy2, x2, w.grad, a_mn=True, b_mn=True)
+        gemm(dy2, x2, w.grad, **kw)
     elif getattr(w, "_grad_fresh", False):      # persistent arena buffer, first write of this step
-        gemm(dy2, x2, w.grad, a_mn=True, b_mn=True)
+        gemm(dy2, x2, w.grad, **kw)
         w._grad_fresh = False
     else:
-        gemm(dy2, x2, w.grad, a_mn=True, b_mn=True, aux=w.grad, beta=1.0)
+        gemm(dy2, x2, w.grad, aux=w.grad, beta=1.0, **kw)
 
 
 def _grad_buffer(p, dtype=torch.float32):
@@ -386,7 +468,13 @@ class _LayerFn(Function):
         qkv = torch.empty(M, nq + 2 * nkv, dtype=BF16, device=dev)
         sq, sk, sv = shadow_of(wq), shadow_of(wk), shadow_of(wv)
         fused_w = _contiguous_rows([sq, sk, sv])
-        if fused_w is not None:
+        fp8 = fused_w is not None and _fp8_ok(C, nq, nkv, wfc.shape[0])
+        f8 = None          # fp8 copies of the GEMM inputs, kept for the weight-gradient GEMMs
+        if fp8:
+            xq8, sx = quantize(xn)
+            w8, sw = fp8_weight(fused_w)
+            gemm(xq8, w8, qkv, scale_a=sx, scale_b=sw)
+        elif fused_w is not None:
             gemm(xn, fused_w, qkv)
         else:
             gemm(xn, sq, qkv[:, :nq])
@@ -406,14 +494,29 @@ class _LayerFn(Function):
         y2 = y.reshape(M, nq)
 
         xa = torch.empty(M, C, dtype=BF16, device=dev)
-        gemm(y2, shadow_of(wo), xa, aux=xm, beta=1.0)
         xn2 = torch.empty(M, C, dtype=BF16, device=dev)
-        _C.norm_fwd(xa, xn2)
         h = torch.empty(M, wfc.shape[0], dtype=BF16, device=dev)
-        gemm(xn2, shadow_of(wfc), h, epi=EPI_RELU2)
         xo = torch.empty(M, C, dtype=BF16, device=dev)
-        gemm(h, shadow_of(wpr), xo, aux=xa, beta=1.0)
+        if fp8:
+            yq8, sy = quantize(y2)
+            w8, sw = fp8_weight(shadow_of(wo))
+            gemm(yq8, w8, xa, aux=xm, beta=1.0, scale_a=sy, scale_b=sw)
+            _C.norm_fwd(xa, xn2)
+            x2q8, s2 = quantize(xn2)
+            w8, sw = fp8_weight(shadow_of(wfc))
+            amax_h = _zeroed_scalar(dev)
+            gemm(x2q8, w8, h, epi=EPI_RELU2, scale_a=s2, scale_b=sw, amax_out=amax_h)
+            hq8, sh = quantize(h, amax=amax_h)
+            w8, sw = fp8_weight(shadow_of(wpr))
+            gemm(hq8, w8, xo, aux=xa, beta=1.0, scale_a=sh, scale_b=sw)
+            f8 = (xq8, sx, yq8, sy, x2q8, s2, hq8, sh)
+        else:
+            gemm(y2, shadow_of(wo), xa, aux=xm, beta=1.0)
+            _C.norm_fwd(xa, xn2)
+            gemm(xn2, shadow_of(wfc), h, epi=EPI_RELU2)
+            gemm(h, shadow_of(wpr), xo, aux=xa, beta=1.0)
 
+        ctx.f8 = f8
         ctx.meta = (B, T, C, D, n_head, n_kv_head, layer, window, has_ve)
         ctx.save_for_backward(x2, x02, idx_c, cos2, sin2, resid_lambdas, x0_lambdas, wq, wk, wv, wo, wfc, wpr,
                               wgate, ve_w, xm, xn, qkv, rstd, y2, lse, xa, xn2, h)
@@ -429,21 +532,44 @@ class _LayerFn(Function):
         nq, nkv = n_head * D, n_kv_head * D
         dxo2 = _rows(dxo)
 
+        f8 = ctx.f8
+        if f8 is not None:
+            xq8, sx, yq8, sy, x2q8, s2, hq8, sh = f8
         # ---- MLP
         dh = torch.empty_like(h)
-        gemm(dxo2, shadow_of(wpr), dh, b_mn=True, aux=h, epi=EPI_MUL2SQRT)
-        _accumulate_wgrad(wpr, dxo2, h)
         dxn2 = torch.empty(M, C, dtype=BF16, device=dev)
-        gemm(dh, shadow_of(wfc), dxn2, b_mn=True)
-        _accumulate_wgrad(wfc, dh, xn2)
+        if f8 is not None:
+            g8, sg = quantize(dxo2, E5M2)
+            w8, sw = fp8_weight(shadow_of(wpr))
+            amax_dh = _zeroed_scalar(dev)
+            gemm(g8, w8, dh, b_mn=True, aux=h, epi=EPI_MUL2SQRT, scale_a=sg, scale_b=sw, amax_out=amax_dh)
+            _accumulate_wgrad(wpr, g8, hq8, sg, sh)
+            del g8, hq8
+            dh8, sdh = quantize(dh, E5M2, amax=amax_dh)
+            w8, sw = fp8_weight(shadow_of(wfc))
+            gemm(dh8, w8, dxn2, b_mn=True, scale_a=sdh, scale_b=sw)
+            _accumulate_wgrad(wfc, dh8, x2q8, sdh, s2)
+            del dh8, x2q8
+        else:
+            gemm(dxo2, shadow_of(wpr), dh, b_mn=True, aux=h, epi=EPI_MUL2SQRT)
+            _accumulate_wgrad(wpr, dxo2, h)
+            gemm(dh, shadow_of(wfc), dxn2, b_mn=True)
+            _accumulate_wgrad(wfc, dh, xn2)
         del dh
         dxa = torch.empty(M, C, dtype=BF16, device=dev)
         _C.normadd_bwd(dxn2, xa, dxo2, dxa)
 
         # ---- attention output projection
         dy = dxn2  # reuse
-        gemm(dxa, shadow_of(wo), dy, b_mn=True)
-        _accumulate_wgrad(wo, dxa, y2)
+        if f8 is not None:
+            a8, sa = quantize(dxa, E5M2)
+            w8, sw = fp8_weight(shadow_of(wo))
+            gemm(a8, w8, dy, b_mn=True, scale_a=sa, scale_b=sw)
+            _accumulate_wgrad(wo, a8, yq8, sa, sy)
+            del a8, yq8
+        else:
+            gemm(dxa, shadow_of(wo), dy, b_mn=True)
+            _accumulate_wgrad(wo, dxa, y2)
 
         # ---- attention core
         dqkv = torch.empty_like(qkv)
@@ -469,7 +595,12 @@ class _LayerFn(Function):
         dxn = dy  # reuse again
         sq, sk, sv = shadow_of(wq), shadow_of(wk), shadow_of(wv)
         fused_w = _contiguous_rows([sq, sk, sv])
-        if fused_w is not None:
+        d8 = None
+        if f8 is not None:
+            d8, sd = quantize(dqkv, E5M2)
+            w8, sw = fp8_weight(fused_w)
+            gemm(d8, w8, dxn, b_mn=True, scale_a=sd, scale_b=sw)
+        elif fused_w is not None:
             gemm(dqkv, fused_w, dxn, b_mn=True)
         else:
             gemm(dqkv[:, :nq], sq, dxn, b_mn=True)
@@ -481,11 +612,13 @@ class _LayerFn(Function):
             if all(fresh) or not any(fresh):
                 fused_g = _contiguous_rows([wq.grad, wk.grad, wv.grad])
         if fused_g is not None:
+            wa, wb = (d8, xq8) if d8 is not None else (dqkv, xn)
+            kw = dict(a_mn=True, b_mn=True, scale_a=sd, scale_b=sx) if d8 is not None else dict(a_mn=True, b_mn=True)
             if fresh[0]:
-                gemm(dqkv, xn, fused_g, a_mn=True, b_mn=True)
+                gemm(wa, wb, fused_g, **kw)
                 wq._grad_fresh = wk._grad_fresh = wv._grad_fresh = False
             else:
-                gemm(dqkv, xn, fused_g, a_mn=True, b_mn=True, aux=fused_g, beta=1.0)
+                gemm(wa, wb, fused_g, aux=fused_g, beta=1.0, **kw)
         else:
             _accumulate_wgrad(wq, dqkv[:, :nq], xn)
             _accumulate_wgrad(wk, dqkv[:, nq:nq + nkv], xn)
@@ -525,7 +658,15 @@ class _HeadFn(Function):
         xn = torch.empty(M, C, dtype=BF16, device=dev)
         _C.backout_norm_fwd(x2, xb2, lam32, xn)
         logits = torch.empty(M, w.shape[0], dtype=BF16, device=dev)
-        gemm(xn, shadow_of(w), logits)
+        f8 = None
+        if _fp8_ok(C, w.shape[0]) and M % 16 == 0:
+            xq8, sx = quantize(xn)
+            w8, sw = fp8_weight(shadow_of(w))
+            gemm(xq8, w8, logits, scale_a=sx, scale_b=sw)
+            f8 = (xq8, sx)
+        else:
+            gemm(xn, shadow_of(w), logits)
+        ctx.f8 = f8
         tgt = targets.reshape(-1).contiguous()
         loss_rows = torch.empty(M, dtype=torch.float32, device=dev)
         lse = torch.empty(M, dtype=torch.float32, device=dev)
@@ -552,8 +693,18 @@ class _HeadFn(Function):
             gscale = dout.float().contiguous().view(-1)
         _C.softcap_ce_bwd(logits, tgt, lse, gscale, vocab_size, softcap)     # logits <- dlogits
         dxn = torch.empty(M, C, dtype=BF16, device=dev)
-        gemm(logits, shadow_of(w), dxn, b_mn=True)
-        _accumulate_wgrad(w, logits, xn)
+        if ctx.f8 is not None:
+            xq8, sx = ctx.f8
+            # |d loss / d logit| <= the row's gradient scale, which bounds amax without a pass over the matrix
+            amax = gscale.abs().max().reshape(1)
+            g8, sg = quantize(logits, E5M2, amax=amax)
+            w8, sw = fp8_weight(shadow_of(w))
+            gemm(g8, w8, dxn, b_mn=True, scale_a=sg, scale_b=sw)
+            _accumulate_wgrad(w, g8, xq8, sg, sx)
+            del g8
+        else:
+            gemm(logits, shadow_of(w), dxn, b_mn=True)
+            _accumulate_wgrad(w, logits, xn)
         dx = torch.empty(M, C, dtype=BF16, device=dev)
         dxb = torch.empty(M, C, dtype=BF16, device=dev) if xb2 is not None else None
         _C.backout_norm_bwd(dxn, x2, xb2, lam.detach().float(), dx, dxb, _grad_buffer(lam))

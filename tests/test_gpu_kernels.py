@@ -210,6 +210,57 @@ def test_model_loss_and_grads_match_torch_path(nat):
     assert logits.shape == (B, T, 2048) and logits.dtype == torch.float32
 
 
+def test_quantize_kernels_match_torch(nat):
+    x = (_mk((384, 512), seed=11).float() * 3).to(BF16)
+    for dt in (torch.float8_e4m3fn, torch.float8_e5m2):
+        q, inv = nat.quantize(x[:, :256], dt)          # strided rows
+        fmax = torch.finfo(dt).max
+        amax = x[:, :256].float().abs().max()
+        ref = (x[:, :256].float() * (fmax / amax)).clamp(-fmax, fmax).to(dt)
+        assert abs(inv.item() - (amax / fmax).item()) <= 1e-6 * inv.item()
+        assert torch.equal(q.view(torch.uint8), ref.view(torch.uint8))
+
+
+def test_fp8_layer_path_close_to_bf16_path(nat):
+    """Loss and gradients of the tiny model with the fp8 linear layers stay within fp8 noise of the bf16 run."""
+    m = _tiny_model(n_layer=4, window="SSSL")
+    B, T = 2, 256
+    idx = torch.randint(0, 2048, (B, T), device="cuda")
+    tgt = torch.randint(0, 2048, (B, T), device="cuda")
+
+    from nanochat_b200.parallel.arena import ParamArena
+    ParamArena(m)            # contiguous QKV shadows: the fused (and therefore fp8) projection path
+
+    def run():
+        m._arena.zero_grads()
+        loss = m(idx, tgt)
+        loss.backward()
+        nat.check_status(loss)
+        return loss.item(), {n: (getattr(p, "grad32", None) if p.grad is None else p.grad).float().clone()
+                             for n, p in m.named_parameters()}
+    ref_loss, ref = run()
+    nat.set_fp8(True)
+    try:
+        loss, got = run()
+        # a second run after a weight change must pick the new weights up
+        with torch.no_grad():
+            m.lm_head.weight.mul_(0.5)
+        nat.bump_weights_epoch()
+        loss_half, _ = run()
+    finally:
+        nat.set_fp8(False)
+    assert abs(loss - ref_loss) < 3e-2, (loss, ref_loss)
+    assert abs(loss_half - loss) > 1e-3
+    bad = []
+    for n in ref:
+        if n == "backout_lambda" or ref[n].numel() < 64:
+            continue
+        err = _rel_err(got[n], ref[n])
+        if err > 0.25:
+            bad.append((n, err))
+    assert not bad, bad
+
+
 def test_adamw_kernel_matches_reference(nat):
     from nanochat_b200.ops import reference as R
     for dtype in (torch.float32, BF16):
