@@ -79,7 +79,7 @@ def main():
                 bad[n] = (round((dp - dq).abs().max().item(), 5), round(frac, 4), round(dq.abs().mean().item(), 5))
         return dict(sorted(bad.items(), key=lambda kv: -kv[1][1])[:8])
     # same kernels, different collectives: only the summation order differs
-    bad_pair = compare(fused_model, nccl_model, 0.1, 1)
+    bad_pair = compare(fused_model, nccl_model, 0.25, 1)
     # against the PyTorch bodies: bf16 rounding differs everywhere, scalars (sums with heavy
     # cancellation) are left to the pairwise check
     bad_fused = compare(fused_model, oracle, 0.5, 64)
@@ -89,7 +89,8 @@ def main():
     for g in comm.arena.muon_groups:
         if g["shadow"] is None:
             continue
-        names = [n for n, p in fused_model.named_parameters() if any(p is gp for gp in g["params"])]
+        name_of = {id(p): n for n, p in fused_model.named_parameters()}
+        names = [name_of[id(gp)] for gp in g["params"]]          # the stack follows the group's order
         ref = torch.stack([oracle_params[n] for n in names]).float()
         shadow_err = max(shadow_err, ((g["shadow"].float() - ref).norm() / ref.norm()).item())
     for d in comm.arena.adamw_big:
