@@ -153,11 +153,16 @@ class RowState:
         self.completed = False
 
 
+def ids_on_cuda(device):
+    return torch.device(device).type == "cuda"
+
+
 class Engine:
     def __init__(self, model, tokenizer):
         self.model = model
         self.tokenizer = tokenizer
         self._decode_graphs = {}
+        self._cache_pool = {}      # rows -> full-length KVCache reused across generations (keeps its decode graph)
 
     def _decode_step(self, ids, kv_cache):
         """One lock-step decode forward; returns (B, V) logits for the new position."""
@@ -194,9 +199,48 @@ class Engine:
         logits = logits[:, -1, :].expand(num_samples, -1)
         # 2) fork the cache for every sample row
         capacity = (len(tokens) + max_tokens) if max_tokens is not None else cfg.sequence_len
-        cache = KVCache(batch_size=num_samples, seq_len=capacity, **geometry)
+        cache = self._pooled_cache(num_samples, capacity, geometry)
+        pooled = cache is not None
+        if not pooled:
+            cache = KVCache(batch_size=num_samples, seq_len=capacity, **geometry)
         cache.prefill(prompt_cache)
         del prompt_cache
+        try:
+            yield from self._decode_loop(tokens, num_samples, max_tokens, temperature, top_k, rng, logits, cache,
+                                         (python_start, python_end, output_start, output_end, assistant_end, bos))
+        finally:
+            if pooled:
+                cache.in_use = False
+
+    def _pooled_cache(self, rows, capacity, geometry):
+        """A full-length cache that lives as long as the engine, so its captured decode graph is reused.
+        None when the graph path does not apply or the pooled cache is busy (nested generations)."""
+        cfg = self.model.config
+        device = geometry["device"]
+        if (device.type != "cuda" or ops.get_kernel_mode() != "native" or rows > 8
+                or capacity > cfg.sequence_len or geometry["head_dim"] != 128):
+            return None
+        cache = self._cache_pool.get(rows)
+        if cache is None:
+            cache = KVCache(batch_size=rows, seq_len=cfg.sequence_len, **geometry)
+            cache.pooled = True
+            cache.in_use = False
+            self._cache_pool[rows] = cache
+        if cache.in_use:
+            return None
+        cache.in_use = True
+        cache.reset()
+        return cache
+
+    def _decode_loop(self, tokens, num_samples, max_tokens, temperature, top_k, rng, logits, cache, specials):
+        python_start, python_end, output_start, output_end, assistant_end, bos = specials
+        tok = self.tokenizer
+        device = self.model.get_device()
+        if ids_on_cuda(device) and ops.get_kernel_mode() == "native":
+            from nanochat_b200.runtime import decode_graph_for
+            runner = decode_graph_for(self, cache)
+            if runner is not None:
+                runner.begin()
         # 3) lock-step decode with the per-row state machine
         rows = [RowState(tokens.copy()) for _ in range(num_samples)]
         produced = 0

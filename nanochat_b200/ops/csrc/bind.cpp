@@ -8,6 +8,7 @@
 #include "attention.h"
 #include "comm.h"
 #include "fused.h"
+#include "decode.h"
 #include "gemm.h"
 #include "optim.h"
 
@@ -236,6 +237,62 @@ void softcap_logits(const Tensor& logits, Tensor& out, int64_t V, double cap) {
                               (float)cap, cur_stream()));
 }
 
+// ---------------------------------------------------------------------------- decode
+void gemv_rows(const Tensor& x, const Tensor& W, Tensor& out, const optional<Tensor>& aux, int64_t epi) {
+  check_bf16(x, "x"); check_bf16(W, "W"); check_bf16(out, "out");
+  TORCH_CHECK(x.dim() == 2 && W.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && W.stride(1) == 1 &&
+              out.stride(1) == 1, "gemv: 2-D row-major tensors");
+  TORCH_CHECK(x.size(1) == W.size(1) && out.size(0) == x.size(0) && out.size(1) == W.size(0), "gemv shapes");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const void* ap = nullptr; long long lda = 0;
+  if (aux.has_value() && aux->defined()) {
+    check_bf16(*aux, "aux");
+    TORCH_CHECK(aux->sizes() == out.sizes() && aux->stride(1) == 1, "aux must match out");
+    ap = aux->data_ptr(); lda = aux->stride(0);
+  }
+  NC_CHECK(nc::gemv_rows(x.data_ptr(), x.stride(0), W.data_ptr(), W.stride(0), out.data_ptr(), out.stride(0), ap, lda,
+                         (int)x.size(0), (int)W.size(0), (int)x.size(1), (int)epi, cur_stream()));
+}
+
+// qkv: (B, (H+2Hkv)*128); cos/sin: (Tmax, 64); seqlens: int32 (B); k_cache/v_cache: (B, Tmax, Hkv, 128) of one layer.
+void decode_qkv_post(Tensor& qkv, int64_t H, int64_t Hkv, const Tensor& cos_t, const Tensor& sin_t, const Tensor& seqlens,
+                     const optional<Tensor>& xn, const optional<Tensor>& wg, const optional<Tensor>& ve,
+                     const optional<Tensor>& idx, Tensor& k_cache, Tensor& v_cache) {
+  check_bf16(qkv, "qkv"); check_bf16(cos_t, "cos"); check_bf16(sin_t, "sin"); check_bf16(k_cache, "k_cache");
+  check_bf16(v_cache, "v_cache");
+  TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == (H + 2 * Hkv) * 128, "qkv shape");
+  TORCH_CHECK(cos_t.is_contiguous() && sin_t.is_contiguous() && cos_t.size(-1) == 64, "rotary tables (T, 64)");
+  TORCH_CHECK(seqlens.scalar_type() == at::kInt && seqlens.numel() == qkv.size(0), "seqlens int32 (B)");
+  TORCH_CHECK(k_cache.dim() == 4 && k_cache.size(0) == qkv.size(0) && k_cache.size(2) == Hkv && k_cache.size(3) == 128 &&
+              k_cache.stride(3) == 1 && k_cache.stride(2) == 128 && v_cache.strides() == k_cache.strides(), "cache layout");
+  const bool has_ve = ve.has_value() && ve->defined();
+  if (has_ve) {
+    check_bf16(*ve, "ve"); check_bf16(*xn, "xn");
+    TORCH_CHECK(wg->scalar_type() == at::kFloat && wg->is_contiguous() && idx->scalar_type() == at::kLong, "ve gate args");
+  }
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  NC_CHECK(nc::decode_qkv_post(qkv.data_ptr(), qkv.stride(0), (int)H, (int)Hkv, cos_t.data_ptr(), sin_t.data_ptr(),
+                               seqlens.data_ptr<int>(), has_ve ? xn->data_ptr() : nullptr, has_ve ? xn->stride(0) : 0,
+                               has_ve ? wg->data_ptr<float>() : nullptr, has_ve ? ve->data_ptr() : nullptr,
+                               has_ve ? ve->stride(0) : 0, has_ve ? reinterpret_cast<const long long*>(idx->data_ptr<int64_t>()) : nullptr,
+                               k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1),
+                               (int)k_cache.size(1), (int)qkv.size(0), status_ptr(qkv), cur_stream()));
+}
+
+// q: (B, H*128) view (row pitch free); y: (B, H*128); scratch fp32 with at least decode_attn_scratch(B, H) elements.
+void decode_attn(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& seqlens, int64_t H,
+                 int64_t Hkv, int64_t window, double scale, Tensor& scratch, Tensor& y) {
+  check_bf16(q, "q"); check_bf16(y, "y");
+  TORCH_CHECK(scratch.scalar_type() == at::kFloat &&
+              (size_t)scratch.numel() >= nc::decode_attn_scratch_floats((int)q.size(0), (int)H), "scratch too small");
+  const c10::cuda::CUDAGuard guard(q.device());
+  g_launches += 1;
+  NC_CHECK(nc::decode_attn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0),
+                           k_cache.stride(1), seqlens.data_ptr<int>(), (int)q.size(0), (int)H, (int)Hkv, (int)window,
+                           (float)scale, scratch.data_ptr<float>(), y.data_ptr(), y.stride(0), cur_stream()));
+}
+int64_t decode_attn_scratch(int64_t B, int64_t H) { return (int64_t)nc::decode_attn_scratch_floats((int)B, (int)H); }
+
 // ------------------------------------------------------------------------- optimizer
 void adamw_step(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const optional<Tensor>& shadow, double lr,
                 double beta1, double beta2, double eps, double wd, int64_t step, double grad_scale) {
@@ -372,6 +429,10 @@ void p2p_small_adamw(const std::vector<int64_t>& grads, int64_t grad_off, Tensor
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_pick_bn", &gemm_pick_bn);
+  m.def("gemv_rows", &gemv_rows);
+  m.def("decode_qkv_post", &decode_qkv_post);
+  m.def("decode_attn", &decode_attn);
+  m.def("decode_attn_scratch", &decode_attn_scratch);
   m.def("amax_bf16", &amax_bf16);
   m.def("quantize_bf16", &quantize_bf16);
   m.def("read_status", &read_status);

@@ -1,0 +1,31 @@
+// Host interface of the single-token decode kernels (decode.cu). All tensors bf16 unless noted; D = 128.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+namespace nc {
+
+enum DecodeEpilogue : int { DEC_EPI_NONE = 0, DEC_EPI_RELU2 = 1 };
+
+// out[b, n] = epi(sum_k x[b, k] * W[n, k]) + aux[b, n]   for b < B <= 8 (aux optional). K, ldx, ldw multiples of 8.
+cudaError_t gemv_rows(const void* x, long long ldx, const void* W, long long ldw, void* out, long long ldo,
+                      const void* aux, long long ldaux, int B, int N, int K, int epi, cudaStream_t s);
+
+// In place on qkv (B rows of [q heads | k heads | v heads]): rotary at position seqlens[b] + RMS norm + 1.2 on
+// q and k; v += 3*sigmoid(xn[:12] . wg[hkv]) * ve[idx[b]] when ve != nullptr; k and v are appended to the
+// caches at (b, seqlens[b]) (cache strides c_bat / c_tok in elements, heads contiguous). A row whose position
+// is outside [0, t_max) is left alone and `status` records it.
+cudaError_t decode_qkv_post(void* qkv, long long ld, int H, int Hkv, const void* cos_t, const void* sin_t,
+                            const int* seqlens, const void* xn, long long ld_xn, const float* wg, const void* ve,
+                            long long ld_ve, const long long* idx, void* k_cache, void* v_cache, long long c_bat,
+                            long long c_tok, int t_max, int B, int* status, cudaStream_t s);
+
+// y[b, h, :] = softmax(q[b, h] . K[b, lo..pos, hkv] * scale) V, pos = seqlens[b], lo = max(0, pos - window)
+// (window < 0: 0). scratch: decode_attn_scratch_floats(B, H) floats.
+size_t decode_attn_scratch_floats(int B, int H);
+cudaError_t decode_attn(const void* q, long long ldq, const void* k_cache, const void* v_cache, long long c_bat,
+                        long long c_tok, const int* seqlens, int B, int H, int Hkv, int window, float scale,
+                        float* scratch, void* y, long long ldy, cudaStream_t s);
+
+}  // namespace nc

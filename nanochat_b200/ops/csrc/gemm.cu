@@ -14,9 +14,9 @@
 //   wgrad    dW = dy^T x : A = dy (MN-major),  B = x  (MN-major), fp32 accumulate
 // and the Newton-Schulz products of the Muon optimizer (X X^T, A A, B X, X^T X).
 //
-// Warp roles (192 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer
-// (one elected lane), warps 2..5 = epilogue (each owns the TMEM lane quadrant
-// warp_id % 4). All waits are bounded (ptx.cuh); a failed wait raises the CTA abort
+// Warp roles (320 threads): warp 0 = TMA producer, warp 1 = TMEM owner + MMA issuer
+// (one elected lane), warps 2..9 = epilogue (a warp may read the TMEM lane quadrant
+// warp_id % 4; the two warps of a quadrant take one half of the tile's columns each). All waits are bounded (ptx.cuh); a failed wait raises the CTA abort
 // flag, records a status word and the kernel drains and exits normally.
 #include "gemm.h"
 #include "host_utils.cuh"
@@ -27,7 +27,8 @@
 namespace nc {
 
 constexpr int BM = 128;
-constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS = 320;        // producer warp, MMA warp, 8 epilogue warps
+constexpr int EPI_WARPS = 8;
 constexpr int ROW_BYTES = 128;   // one swizzle row: 64 bf16 or 128 fp8 values along the contiguous dim
 
 struct GemmKernelArgs {
@@ -90,10 +91,10 @@ __device__ __forceinline__ void tile_coords(int t, const GemmKernelArgs& a, int&
 // 16 columns at a time, goes through the fused epilogue and is stored as bf16 or fp32.
 template <int BN>
 __device__ __forceinline__ void store_tile_row(const GemmKernelArgs& args, uint32_t taddr, int b, int row, int n0,
-                                               float alpha, float beta, float& amax) {
+                                               float alpha, float beta, float& amax, int c_begin, int c_end) {
   const bool row_ok = row < args.M;
 #pragma unroll 1
-  for (int c = 0; c < BN / 16; ++c) {
+  for (int c = c_begin; c < c_end; ++c) {
     uint32_t r[16];
     tmem_ld16(taddr + c * 16, r);
     tmem_wait_ld();
@@ -183,7 +184,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 4); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], EPI_WARPS); }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -261,6 +262,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else {
     // ---------------------------------------------------------------- epilogue
     const int quad = warp & 3;
+    constexpr int CHUNKS = BN / 16, SPLIT = (CHUNKS + 1) / 2;
+    const int c_begin = (warp - 2) < 4 ? 0 : SPLIT, c_end = (warp - 2) < 4 ? SPLIT : CHUNKS;
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
     float amax = 0.f;
     float alpha = args.alpha;
@@ -274,7 +277,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int row = mb * BM + quad * 32 + lane;
       const int n0 = nb * BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC_STRIDE;
-      store_tile_row<BN>(args, taddr, b, row, n0, alpha, beta, amax);
+      store_tile_row<BN>(args, taddr, b, row, n0, alpha, beta, amax, c_begin, c_end);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -311,7 +314,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 // Only the even CTA ("leader") issues MMAs. Barriers: full[s] lives in the leader and counts the bytes of
 // all four copies (the partner's TMA signals it through its cluster address); empty[s] and acc_full[a]
 // exist in both CTAs and the leader's MMA thread commits to each of them; acc_empty[a] lives in the
-// leader and collects the arrivals of the eight epilogue warps of the pair.
+// leader and collects the arrivals of the sixteen epilogue warps of the pair.
 template <int BN, bool A_MN, bool B_MN, bool FP8>
 struct PairCfg {
   using Base = Cfg<BN, A_MN, B_MN, FP8>;
@@ -360,7 +363,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 8); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], 2 * EPI_WARPS); }
     *abort_flag = 0;
     fence_mbar_init();
   }
@@ -442,6 +445,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   } else {
     // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
     const int quad = warp & 3;
+    constexpr int CHUNKS = BN / 16, SPLIT = (CHUNKS + 1) / 2;
+    const int c_begin = (warp - 2) < 4 ? 0 : SPLIT, c_end = (warp - 2) < 4 ? SPLIT : CHUNKS;
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
     float amax = 0.f;
     float alpha = args.alpha;
@@ -454,7 +459,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int row = mb * (2 * BM) + rank * BM + quad * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC_STRIDE;
-      store_tile_row<BN>(args, taddr, b, row, nb * BN, alpha, beta, amax);
+      store_tile_row<BN>(args, taddr, b, row, nb * BN, alpha, beta, amax, c_begin, c_end);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
@@ -683,7 +688,9 @@ static GemmPlan gemm_plan(const GemmDesc& d, bool fp8) {
     if (pair_ok && i < 3) {
       // fp8, MN-major B: the partner's half of a 208-wide tile would start a TMA copy off a 16-byte boundary
       if (fp8 && d.b_mn && cand[i] == 208) continue;
-      const double sc = score(cand[i], true, eff2[i]);
+      // 8-bit operands halve the math time per byte fetched, which is where the pair's smaller shared-memory
+      // traffic counts most (measured on the wgrad shapes: 2.3-2.5 vs 1.8 PFLOP/s)
+      const double sc = score(cand[i], true, eff2[i] * (fp8 ? 1.2 : 1.0));
       if (sc > best_score + 1e-9) { best_score = sc; best = {cand[i], true}; }
     }
   }

@@ -43,7 +43,8 @@ ATTENTION_IMPL = _os.environ.get("NANOCHAT_ATTENTION", "native")
 def check_status(like=None):
     """Raise if any kernel recorded a failed (timed-out) wait since the last check. Synchronises."""
     dev = like if like is not None else torch.empty(0, device="cuda")
-    st = _C.read_status(dev)
+    with torch.inference_mode():      # the status word may have been created by a kernel launched in inference mode
+        st = _C.read_status(dev)
     if st[0] != 0:
         code, detail = st[0] >> 24, st[0] & 0xFFFFFF
         raise RuntimeError(f"nanochat_b200 kernel reported a failed wait: code={code} detail={detail}")

@@ -1,18 +1,173 @@
 """
-Execution runtime: CUDA-graph capture of shape-static inner loops and device-side timers.
+Execution runtime: CUDA-graph replay of the single-token decode step.
 
-`decode_graph_for(engine, kv_cache)` returns a `DecodeGraph` that replays one
-captured decode step of a `GPT` (positions live in device memory, so replays need
-no host-side position), or None when capture does not apply (CPU, non-GPT model,
-kernels disabled).
+A decode step of the reference engine is one `model.forward` on a (B, 1) batch: a few hundred
+small library kernels whose launch cost, not their work, sets the token rate
+(reference: nanochat/engine.py:186-190). Here the step is a fixed sequence of purpose-built
+kernels (`ops/csrc/decode.cu`: weight-streaming GEMV with fused residual / relu^2, rotary +
+QK-norm + value-embedding gate + cache append, split-key attention) over static buffers. Every
+position-dependent quantity is read from device memory (`KVCache.cache_seqlens`), so the whole
+step is captured once per (engine, cache) and replayed with a single launch per token.
+
+`decode_graph_for(engine, kv_cache)` returns the `DecodeGraph` of a cache, or None when the
+fast path does not apply (CPU, kernels disabled, more than 8 rows, head dim != 128).
 """
 
 import torch
+import torch.nn.functional as F
+
+from nanochat_b200 import common, ops
+from nanochat_b200.ops import reference as ref_ops
+
+MAX_ROWS = 8
+
+
+class DecodeGraph:
+    def __init__(self, model, kv_cache):
+        nat = ops.native_module()
+        self.nat, self.C_ = nat, nat._C
+        self.model, self.cache = model, kv_cache
+        cfg = model.config
+        dev = kv_cache.k_cache.device
+        B, C = kv_cache.batch_size, cfg.n_embd
+        self.B, self.C = B, C
+        self.H, self.Hkv = cfg.n_head, cfg.n_kv_head
+        nq, nkv = self.H * 128, self.Hkv * 128
+        bf16 = torch.bfloat16
+        e = lambda *shape, dtype=bf16: torch.empty(*shape, dtype=dtype, device=dev)
+        self.ids = torch.zeros(B, 1, dtype=torch.long, device=dev)
+        self.prev = torch.zeros(B, C, dtype=bf16, device=dev)
+        self.xm, self.xn, self.xa, self.xn2 = e(B, C), e(B, C), e(B, C), e(B, C)
+        self.xs = [e(B, C), e(B, C)]                       # residual stream ping-pong
+        self.x_backout = e(B, C)
+        self.qkv, self.y, self.h = e(B, nq + 2 * nkv), e(B, nq), e(B, 4 * C)
+        self.logits_bf16 = e(B, model.lm_head.weight.shape[0])
+        self.logits = e(B, cfg.vocab_size, dtype=torch.float32)
+        self.scratch = e(self.C_.decode_attn_scratch(B, self.H), dtype=torch.float32)
+        self.cos = model.cos.reshape(-1, 64).contiguous()
+        self.sin = model.sin.reshape(-1, 64).contiguous()
+        self.weights_epoch = None
+        self.w = None
+        self.graph = None
+        self.warm = False
+
+    # ------------------------------------------------------------------ weights
+    def _refresh_weights(self):
+        """bf16 operand copies laid out for the step (fused QKV); re-copied in place when the parameters moved,
+        so a captured graph keeps pointing at valid buffers."""
+        nat = self.nat
+        m = self.model
+        fresh = []
+        for blk in m.transformer.h:
+            a = blk.attn
+            fresh.append(dict(
+                qkv=[nat.shadow_of(a.c_q.weight), nat.shadow_of(a.c_k.weight), nat.shadow_of(a.c_v.weight)],
+                o=nat.shadow_of(a.c_proj.weight), fc=nat.shadow_of(blk.mlp.c_fc.weight),
+                pr=nat.shadow_of(blk.mlp.c_proj.weight),
+                wg=a.ve_gate.weight if a.ve_gate is not None else None))
+        lm_head = nat.shadow_of(m.lm_head.weight)
+        epoch = nat._weights_epoch            # read after the shadows: a re-cast above moves it
+        if self.w is not None and self.weights_epoch == epoch:
+            return
+        first = self.w is None
+        if first:
+            self.w = []
+        for i, f in enumerate(fresh):
+            if first:
+                self.w.append(dict(qkv=torch.cat(f["qkv"]).contiguous(),
+                                   wg=f["wg"].detach().float().contiguous() if f["wg"] is not None else None))
+            else:
+                torch.cat(f["qkv"], out=self.w[i]["qkv"])
+                if f["wg"] is not None:
+                    self.w[i]["wg"].copy_(f["wg"].detach().float())
+            # the other matrices are used where they live (bf16 parameters or their persistent shadows)
+            self.w[i].update(o=f["o"], fc=f["fc"], pr=f["pr"])
+        self.lm_head = lm_head
+        self.weights_epoch = epoch
+
+    # --------------------------------------------------------------------- step
+    def _forward(self):
+        m, C_ = self.model, self.C_
+        B, H, Hkv = self.B, self.H, self.Hkv
+        nq = H * 128
+        cache = self.cache
+        idx = self.ids[:, 0]
+        x = ref_ops.rms_norm(F.embedding(idx, m.transformer.wte.weight).to(torch.bfloat16))
+        gate = m.smear_lambda.to(x.dtype) * torch.sigmoid(
+            F.linear(x[:, :ref_ops.SMEAR_CHANNELS], m.smear_gate.weight.to(x.dtype)))
+        x_in = x + gate * self.prev
+        self.prev.copy_(x)
+        x0 = x_in
+        x = x_in
+        backout_layer = m.config.n_layer // 2
+        scale = 1.0 / (128 ** 0.5)
+        for i, w in enumerate(self.w):
+            C_.mixnorm_fwd(x, x0, m.resid_lambdas, m.x0_lambdas, i, self.xm, self.xn)
+            C_.gemv_rows(self.xn, w["qkv"], self.qkv, None, 0)
+            ve = m.value_embeds[str(i)].weight if str(i) in m.value_embeds else None
+            kc, vc = cache.get_layer_cache(i)
+            C_.decode_qkv_post(self.qkv, H, Hkv, self.cos, self.sin, cache.cache_seqlens,
+                               self.xn if ve is not None else None, w["wg"] if ve is not None else None, ve,
+                               idx if ve is not None else None, kc, vc)
+            window = m.window_sizes[i][0]
+            window = window if 0 <= window < cache.max_seq_len else -1
+            C_.decode_attn(self.qkv[:, :nq], kc, vc, cache.cache_seqlens, H, Hkv, window, scale, self.scratch, self.y)
+            C_.gemv_rows(self.y, w["o"], self.xa, self.xm, 0)
+            C_.norm_fwd(self.xa, self.xn2)
+            C_.gemv_rows(self.xn2, w["fc"], self.h, None, 1)
+            out = self.x_backout if i == backout_layer else self.xs[i & 1]
+            C_.gemv_rows(self.h, w["pr"], out, self.xa, 0)
+            x = out
+        C_.backout_norm_fwd(x, self.x_backout, m.backout_lambda.detach().float(), self.xn)
+        C_.gemv_rows(self.xn, self.lm_head, self.logits_bf16, None, 0)
+        C_.softcap_logits(self.logits_bf16, self.logits, m.config.vocab_size, ref_ops.SOFTCAP)
+        cache.cache_seqlens.add_(1)
+
+    def begin(self):
+        """Start of a generation: take over the smear state the prefill left in the cache."""
+        prev = self.cache.prev_embedding
+        if prev is None:
+            self.prev.zero_()
+        else:
+            self.prev.copy_(prev.reshape(self.B, self.C))
+        self._refresh_weights()
+
+    @torch.inference_mode()
+    def step(self, ids):
+        """ids: (B, 1) token ids of the new position; returns (B, V) fp32 logits (a static buffer, valid until
+        the next step)."""
+        self.ids.copy_(ids)
+        if self.weights_epoch != self.nat._weights_epoch or self.w is None:
+            self._refresh_weights()
+        if self.graph is not None:
+            self.graph.replay()
+        elif not self.warm:
+            self._forward()                      # first step runs eagerly: kernels get configured outside capture
+            self.warm = True
+        else:
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._forward()
+            self.graph = g
+            g.replay()
+        self.cache._pos += 1
+        return self.logits
 
 
 def decode_graph_for(engine, kv_cache):
+    """The DecodeGraph bound to `kv_cache` (created on first use), or None when the fast path does not apply."""
     from nanochat_b200.models.gpt import GPT
     model = engine.model
-    if not isinstance(model, GPT) or not kv_cache.k_cache.is_cuda:
+    if not isinstance(model, GPT) or not kv_cache.k_cache.is_cuda or ops.get_kernel_mode() != "native":
         return None
-    return None  # graph capture is wired in by runtime_graph once the decode kernels are loaded
+    cfg = model.config
+    if (cfg.n_embd // cfg.n_head != 128 or kv_cache.batch_size > MAX_ROWS or common.COMPUTE_DTYPE != torch.bfloat16
+            or not getattr(kv_cache, "pooled", False)):
+        return None
+    graphs = engine._decode_graphs
+    g = graphs.get(id(kv_cache))
+    if g is None or g.cache is not kv_cache:
+        g = DecodeGraph(model, kv_cache)
+        graphs[id(kv_cache)] = g
+    return g

@@ -25,6 +25,10 @@ from nanochat_b200.engine import Engine
 def weight_bytes(model):
     """Bytes a decode step has to read for the parameters, as they are consumed (bf16 shadows of the
     fp32 masters on the native path, the stored dtype otherwise)."""
+    if hasattr(model, "transformer") and next(model.parameters()).is_cuda:
+        # bf16 operand copies of the block matrices and lm_head; embedding tables are only touched by row
+        dense = list(model.transformer.h.parameters()) + [model.lm_head.weight]
+        return sum(p.numel() * 2 for p in dense)
     return sum(p.numel() * p.element_size() for p in model.parameters())
 
 
@@ -82,8 +86,59 @@ class _SyntheticTokenizer:
         return ""
 
 
+def run_reference(args):
+    """Decode rate of the UNMODIFIED reference (baseline/_ref: its GPT, its Engine, stock code path) on random-init
+    weights of --depth, with the same prompt length, batch sizes and timing as the sweep below."""
+    import os
+    import sys
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "baseline", "_ref")
+    if not os.path.isdir(os.path.join(root, "nanochat")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/nanochat not present on this box"}))
+        return
+    sys.path.insert(0, root)
+    for name in [m for m in sys.modules if m == "nanochat" or m.startswith("nanochat.")]:
+        del sys.modules[name]
+    try:
+        import rustbpe  # noqa: F401
+    except ImportError:
+        # the reference's tokenizer module imports its BPE trainer at import time; decode never calls it
+        import types
+        sys.modules["rustbpe"] = types.ModuleType("rustbpe")
+    from nanochat.common import compute_init as ref_init, compute_cleanup as ref_cleanup
+    from nanochat.gpt import GPT, GPTConfig
+    from nanochat.engine import Engine as RefEngine
+    _, _, _, _, device = ref_init("cuda")
+    dim = -(-args.depth * 64 // 128) * 128
+    cfg = GPTConfig(sequence_len=2048, vocab_size=32768, n_layer=args.depth, n_head=dim // 128, n_kv_head=dim // 128,
+                    n_embd=dim)
+    with torch.device("meta"):
+        model = GPT(cfg)
+    model.to_empty(device=device)
+    model.init_weights()
+    model.eval()
+    engine = RefEngine(model, _SyntheticTokenizer(cfg.vocab_size))
+    g = torch.Generator().manual_seed(0)
+    prompt_len = min(args.prompt_tokens, cfg.sequence_len - args.decode_tokens)
+    prompt = torch.randint(0, cfg.vocab_size - 9, (prompt_len,), generator=g).tolist()
+    payload = {"impl": "reference", "prompt_tokens": prompt_len, "decode_tokens": args.decode_tokens, "sweep": []}
+    for bs in [int(b) for b in args.batch_sizes.split(",")]:
+        bench_generate(engine, prompt, bs, 8, args.temperature, args.top_k)
+        res = bench_generate(engine, prompt, bs, args.decode_tokens, args.temperature, args.top_k)
+        st = res["step_times"]
+        if not st:
+            continue
+        tpot = sorted(st)[len(st) // 2]
+        payload["sweep"].append({"batch_size": bs, "ttft_sec": round(res["ttft"], 6), "tpot_sec": round(tpot, 6),
+                                 "tok_per_sec": round(bs * len(st) / sum(st), 1), "decode_steps": len(st)})
+        print(f"reference batch {bs}: TPOT {tpot*1e3:.2f} ms, {payload['sweep'][-1]['tok_per_sec']:,.0f} tok/s")
+    print(json.dumps(payload))
+    ref_cleanup()
+
+
 def main():
     ap = argparse.ArgumentParser(description="Inference benchmark")
+    ap.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"],
+                    help="reference = the unmodified reference engine from baseline/_ref (random-init only)")
     ap.add_argument("-i", "--source", type=str, default="base")
     ap.add_argument("-g", "--model-tag", type=str, default=None)
     ap.add_argument("-s", "--step", type=int, default=None)
@@ -95,6 +150,8 @@ def main():
     ap.add_argument("--random-init", action="store_true", help="random weights of --depth instead of a checkpoint")
     ap.add_argument("--depth", type=int, default=26)
     args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
 
     device_type = autodetect_device_type()
     assert device_type == "cuda", "infer_bench needs a CUDA GPU"
