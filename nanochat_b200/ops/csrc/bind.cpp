@@ -41,6 +41,11 @@ void check_bf16(const Tensor& t, const char* name) {
   TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kBFloat16, name, " must be a CUDA bf16 tensor");
 }
 const void* optptr(const optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+float* opt_scalar(const optional<Tensor>& t) {
+  if (!t.has_value() || !t->defined()) return nullptr;
+  TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->numel() == 1, "expected a CUDA fp32 scalar");
+  return t->data_ptr<float>();
+}
 
 // ------------------------------------------------------------------------------ GEMM
 // Operands are bf16, or 8-bit floats (e4m3 / e5m2, both operands) with optional per-tensor scales.
@@ -108,31 +113,34 @@ std::vector<int64_t> read_status(const Tensor& like) {
 
 // --------------------------------------------------------------------- layer kernels
 void mixnorm_fwd(const Tensor& x, const Tensor& x0, const Tensor& lam_r, const Tensor& lam_0, int64_t layer,
-                 Tensor& xm, Tensor& xn) {
+                 Tensor& xm, Tensor& xn, const optional<Tensor>& amax) {
   const c10::cuda::CUDAGuard guard(x.device());
   const int C = (int)x.size(-1), M = (int)(x.numel() / C);
   NC_CHECK(nc::mixnorm_fwd(x.data_ptr(), x0.data_ptr(), lam_r.data_ptr<float>(), lam_0.data_ptr<float>(), (int)layer,
-                           xm.data_ptr(), xn.data_ptr(), M, C, cur_stream()));
+                           xm.data_ptr(), xn.data_ptr(), opt_scalar(amax), M, C, cur_stream()));
 }
-void norm_fwd(const Tensor& x, Tensor& y) {
+void norm_fwd(const Tensor& x, Tensor& y, const optional<Tensor>& amax) {
   const c10::cuda::CUDAGuard guard(x.device());
   const int C = (int)x.size(-1), M = (int)(x.numel() / C);
-  NC_CHECK(nc::norm_fwd(x.data_ptr(), y.data_ptr(), M, C, cur_stream()));
+  NC_CHECK(nc::norm_fwd(x.data_ptr(), y.data_ptr(), opt_scalar(amax), M, C, cur_stream()));
 }
-void normadd_bwd(const Tensor& dy, const Tensor& x, const optional<Tensor>& dres, Tensor& dx) {
+void normadd_bwd(const Tensor& dy, const Tensor& x, const optional<Tensor>& dres, Tensor& dx,
+                 const optional<Tensor>& amax) {
   const c10::cuda::CUDAGuard guard(x.device());
   const int C = (int)x.size(-1), M = (int)(x.numel() / C);
-  NC_CHECK(nc::normadd_bwd(dy.data_ptr(), x.data_ptr(), optptr(dres), dx.data_ptr(), M, C, cur_stream()));
+  NC_CHECK(nc::normadd_bwd(dy.data_ptr(), x.data_ptr(), optptr(dres), dx.data_ptr(), opt_scalar(amax), M, C,
+                           cur_stream()));
 }
 void mixnorm_bwd(const Tensor& dxn, const Tensor& dres, const optional<Tensor>& dgate, const Tensor& xm,
                  const Tensor& x, const Tensor& x0, const Tensor& lam_r, const Tensor& lam_0, int64_t layer,
-                 Tensor& dx, Tensor& dx0, bool accumulate_dx0, Tensor& dlam_r, Tensor& dlam_0) {
+                 Tensor& dx, Tensor& dx0, bool accumulate_dx0, Tensor& dlam_r, Tensor& dlam_0,
+                 const optional<Tensor>& amax) {
   const c10::cuda::CUDAGuard guard(x.device());
   const int C = (int)x.size(-1), M = (int)(x.numel() / C);
   NC_CHECK(nc::mixnorm_bwd(dxn.data_ptr(), dres.data_ptr(), (const float*)optptr(dgate), xm.data_ptr(), x.data_ptr(),
                            x0.data_ptr(), lam_r.data_ptr<float>(), lam_0.data_ptr<float>(), (int)layer, dx.data_ptr(),
-                           dx0.data_ptr(), accumulate_dx0, dlam_r.data_ptr<float>(), dlam_0.data_ptr<float>(), M, C,
-                           cur_stream()));
+                           dx0.data_ptr(), accumulate_dx0, dlam_r.data_ptr<float>(), dlam_0.data_ptr<float>(),
+                           opt_scalar(amax), M, C, cur_stream()));
 }
 void backout_norm_fwd(const Tensor& x, const optional<Tensor>& xb, const Tensor& lam, Tensor& y) {
   const c10::cuda::CUDAGuard guard(x.device());

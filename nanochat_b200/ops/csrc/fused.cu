@@ -22,10 +22,12 @@ template <int NV>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 mixnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ x0,
                    const float* __restrict__ lam_r, const float* __restrict__ lam_0, int layer,
-                   __nv_bfloat16* __restrict__ xm, __nv_bfloat16* __restrict__ xn, int M, int C) {
+                   __nv_bfloat16* __restrict__ xm, __nv_bfloat16* __restrict__ xn, float* __restrict__ amax_xn,
+                   int M, int C) {
   const int lane = threadIdx.x & 31;
   const int nvec = C >> 3;
   const float lr = lam_r[layer], l0 = lam_0[layer];
+  float mx = 0.f;
   for (int row = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5); row < M; row += gridDim.x * ROW_WARPS) {
     RowF<NV> a, b;
     load_row(a, x + (size_t)row * C, nvec, lane);
@@ -41,14 +43,18 @@ mixnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 #pragma unroll
       for (int j = 0; j < 8; ++j) a.v[i][j] *= rstd;
     store_row(a, xn + (size_t)row * C, nvec, lane);
+    if (amax_xn) mx = lane_absmax_bf16(a, mx);
   }
+  if (amax_xn) publish_absmax(mx, amax_xn, lane);
 }
 
 template <int NV>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
-norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int M, int C) {
+norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, float* __restrict__ amax_y, int M,
+                int C) {
   const int lane = threadIdx.x & 31;
   const int nvec = C >> 3;
+  float mx = 0.f;
   for (int row = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5); row < M; row += gridDim.x * ROW_WARPS) {
     RowF<NV> a;
     load_row(a, x + (size_t)row * C, nvec, lane);
@@ -58,7 +64,9 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__
 #pragma unroll
       for (int j = 0; j < 8; ++j) a.v[i][j] *= rstd;
     store_row(a, y + (size_t)row * C, nvec, lane);
+    if (amax_y) mx = lane_absmax_bf16(a, mx);
   }
+  if (amax_y) publish_absmax(mx, amax_y, lane);
 }
 
 // g <- grad wrt the norm input, given g = grad wrt the norm output and the norm input xin.
@@ -75,9 +83,11 @@ __device__ __forceinline__ void rmsnorm_bwd_inplace(RowF<NV>& g, const RowF<NV>&
 template <int NV>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
 normadd_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
-                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, int M, int C) {
+                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, float* __restrict__ amax_dx,
+                   int M, int C) {
   const int lane = threadIdx.x & 31;
   const int nvec = C >> 3;
+  float mx = 0.f;
   for (int row = blockIdx.x * ROW_WARPS + (threadIdx.x >> 5); row < M; row += gridDim.x * ROW_WARPS) {
     RowF<NV> g, xin;
     load_row(g, dy + (size_t)row * C, nvec, lane);
@@ -92,7 +102,9 @@ normadd_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __
         for (int j = 0; j < 8; ++j) g.v[i][j] += r.v[i][j];
     }
     store_row(g, dx + (size_t)row * C, nvec, lane);
+    if (amax_dx) mx = lane_absmax_bf16(g, mx);
   }
+  if (amax_dx) publish_absmax(mx, amax_dx, lane);
 }
 
 template <int NV>
@@ -103,12 +115,12 @@ mixnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dxn, const __nv_bfloat16* _
                    const __nv_bfloat16* __restrict__ x0, const float* __restrict__ lam_r,
                    const float* __restrict__ lam_0, int layer, __nv_bfloat16* __restrict__ dx,
                    __nv_bfloat16* __restrict__ dx0, int accumulate_dx0, float* __restrict__ dlam_r,
-                   float* __restrict__ dlam_0, int M, int C) {
+                   float* __restrict__ dlam_0, float* __restrict__ amax_dx, int M, int C) {
   __shared__ float red[2][ROW_WARPS];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nvec = C >> 3;
   const float lr = lam_r[layer], l0 = lam_0[layer];
-  float acc_r = 0.f, acc_0 = 0.f;
+  float acc_r = 0.f, acc_0 = 0.f, mx = 0.f;
   for (int row = blockIdx.x * ROW_WARPS + warp; row < M; row += gridDim.x * ROW_WARPS) {
     RowF<NV> g, t;
     load_row(g, dxn + (size_t)row * C, nvec, lane);
@@ -149,7 +161,9 @@ mixnorm_bwd_kernel(const __nv_bfloat16* __restrict__ dxn, const __nv_bfloat16* _
 #pragma unroll
       for (int j = 0; j < 8; ++j) g.v[i][j] *= lr;
     store_row(g, dx + (size_t)row * C, nvec, lane);
+    if (amax_dx) mx = lane_absmax_bf16(g, mx);
   }
+  if (amax_dx) publish_absmax(mx, amax_dx, lane);
   if (lane == 0) { red[0][warp] = acc_r; red[1][warp] = acc_0; }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -573,36 +587,39 @@ static inline int row_grid(int M) {
   } while (0)
 
 cudaError_t mixnorm_fwd(const void* x, const void* x0, const float* lam_r, const float* lam_0, int layer,
-                        void* xm, void* xn, int M, int C, cudaStream_t s) {
+                        void* xm, void* xn, float* amax_xn, int M, int C, cudaStream_t s) {
   if (C & 7) return cudaErrorInvalidValue;
   NC_DISPATCH_NV(C, (mixnorm_fwd_kernel<NV><<<row_grid(M), ROW_WARPS * 32, 0, s>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)x0, lam_r, lam_0, layer,
-      (__nv_bfloat16*)xm, (__nv_bfloat16*)xn, M, C)));
+      (__nv_bfloat16*)xm, (__nv_bfloat16*)xn, amax_xn, M, C)));
   return cudaGetLastError();
 }
 
-cudaError_t norm_fwd(const void* x, void* y, int M, int C, cudaStream_t s) {
+cudaError_t norm_fwd(const void* x, void* y, float* amax_y, int M, int C, cudaStream_t s) {
   if (C & 7) return cudaErrorInvalidValue;
   NC_DISPATCH_NV(C, (norm_fwd_kernel<NV><<<row_grid(M), ROW_WARPS * 32, 0, s>>>(
-      (const __nv_bfloat16*)x, (__nv_bfloat16*)y, M, C)));
+      (const __nv_bfloat16*)x, (__nv_bfloat16*)y, amax_y, M, C)));
   return cudaGetLastError();
 }
 
-cudaError_t normadd_bwd(const void* dy, const void* x, const void* dres, void* dx, int M, int C, cudaStream_t s) {
+cudaError_t normadd_bwd(const void* dy, const void* x, const void* dres, void* dx, float* amax_dx, int M, int C,
+                        cudaStream_t s) {
   if (C & 7) return cudaErrorInvalidValue;
   NC_DISPATCH_NV(C, (normadd_bwd_kernel<NV><<<row_grid(M), ROW_WARPS * 32, 0, s>>>(
-      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, M, C)));
+      (const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, amax_dx, M,
+      C)));
   return cudaGetLastError();
 }
 
 cudaError_t mixnorm_bwd(const void* dxn, const void* dres, const float* dgate, const void* xm, const void* x,
                         const void* x0, const float* lam_r, const float* lam_0, int layer, void* dx, void* dx0,
-                        int accumulate_dx0, float* dlam_r, float* dlam_0, int M, int C, cudaStream_t s) {
+                        int accumulate_dx0, float* dlam_r, float* dlam_0, float* amax_dx, int M, int C,
+                        cudaStream_t s) {
   if (C & 7) return cudaErrorInvalidValue;
   NC_DISPATCH_NV(C, (mixnorm_bwd_kernel<NV><<<row_grid(M), ROW_WARPS * 32, 0, s>>>(
       (const __nv_bfloat16*)dxn, (const __nv_bfloat16*)dres, dgate, (const __nv_bfloat16*)xm,
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)x0, lam_r, lam_0, layer, (__nv_bfloat16*)dx,
-      (__nv_bfloat16*)dx0, accumulate_dx0, dlam_r, dlam_0, M, C)));
+      (__nv_bfloat16*)dx0, accumulate_dx0, dlam_r, dlam_0, amax_dx, M, C)));
   return cudaGetLastError();
 }
 

@@ -9,13 +9,17 @@
 namespace nc {
 
 // ---- transformer layer (fused.cu)
+// The optional amax_* words receive max |output| (atomic max on the fp32 bits; zero them first): the per-tensor
+// scale of an fp8 GEMM operand then needs no extra pass over the tensor.
 cudaError_t mixnorm_fwd(const void* x, const void* x0, const float* lam_r, const float* lam_0, int layer,
-                        void* xm, void* xn, int M, int C, cudaStream_t s);
-cudaError_t norm_fwd(const void* x, void* y, int M, int C, cudaStream_t s);
-cudaError_t normadd_bwd(const void* dy, const void* x, const void* dres, void* dx, int M, int C, cudaStream_t s);
+                        void* xm, void* xn, float* amax_xn, int M, int C, cudaStream_t s);
+cudaError_t norm_fwd(const void* x, void* y, float* amax_y, int M, int C, cudaStream_t s);
+cudaError_t normadd_bwd(const void* dy, const void* x, const void* dres, void* dx, float* amax_dx, int M, int C,
+                        cudaStream_t s);
 cudaError_t mixnorm_bwd(const void* dxn, const void* dres, const float* dgate, const void* xm, const void* x,
                         const void* x0, const float* lam_r, const float* lam_0, int layer, void* dx, void* dx0,
-                        int accumulate_dx0, float* dlam_r, float* dlam_0, int M, int C, cudaStream_t s);
+                        int accumulate_dx0, float* dlam_r, float* dlam_0, float* amax_dx, int M, int C,
+                        cudaStream_t s);
 cudaError_t backout_norm_fwd(const void* x, const void* xb, const float* lam, void* y, int M, int C, cudaStream_t s);
 cudaError_t backout_norm_bwd(const void* dy, const void* x, const void* xb, const float* lam, void* dx, void* dxb,
                              float* dlam, int M, int C, cudaStream_t s);

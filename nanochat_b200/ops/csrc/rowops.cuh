@@ -86,4 +86,19 @@ __device__ __forceinline__ float row_dot(const RowF<NV>& a, const RowF<NV>& b) {
 template <int NV>
 __device__ __forceinline__ float row_sumsq(const RowF<NV>& a) { return row_dot(a, a); }
 
+// max |a| over this lane's part of the row, as the values will read back from bf16 storage
+template <int NV>
+__device__ __forceinline__ float lane_absmax_bf16(const RowF<NV>& a, float m) {
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(bf16_round(a.v[i][j])));
+  return m;
+}
+// One atomic per warp: non-negative floats order like their bit patterns.
+__device__ __forceinline__ void publish_absmax(float m, float* amax, int lane) {
+  m = warp_max(m);
+  if (lane == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int*>(amax), __float_as_uint(m));
+}
+
 }  // namespace nc

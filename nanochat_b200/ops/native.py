@@ -147,6 +147,7 @@ _weights_epoch = 0
 _fp8_weights = {}
 _amax_pool = None
 _amax_next = 0
+_amax_hints = {}       # data_ptr of a just-written gradient tensor -> device scalar with its max|.|
 
 
 def set_fp8(enabled):
@@ -173,6 +174,7 @@ def begin_microstep(device):
     else:
         _amax_pool.zero_()
     _amax_next = 0
+    _amax_hints.clear()
 
 
 def _zeroed_scalar(device):
@@ -294,7 +296,7 @@ class _RmsNormFn(Function):
     def forward(ctx, x):
         xc = x.contiguous()
         y = torch.empty_like(xc)
-        _C.norm_fwd(xc, y)
+        _C.norm_fwd(xc, y, None)
         ctx.save_for_backward(xc)
         return y
 
@@ -302,7 +304,7 @@ class _RmsNormFn(Function):
     def backward(ctx, dy):
         (x,) = ctx.saved_tensors
         dx = torch.empty_like(x)
-        _C.normadd_bwd(dy.contiguous(), x, None, dx)
+        _C.normadd_bwd(dy.contiguous(), x, None, dx, None)
         return dx
 
 
@@ -463,16 +465,18 @@ class _LayerFn(Function):
         x2, x02 = x.reshape(M, C), x0.reshape(M, C)
         xm = torch.empty(M, C, dtype=BF16, device=dev)
         xn = torch.empty(M, C, dtype=BF16, device=dev)
-        _C.mixnorm_fwd(x2, x02, resid_lambdas, x0_lambdas, layer, xm, xn)
-
         nq, nkv = n_head * D, n_kv_head * D
-        qkv = torch.empty(M, nq + 2 * nkv, dtype=BF16, device=dev)
         sq, sk, sv = shadow_of(wq), shadow_of(wk), shadow_of(wv)
         fused_w = _contiguous_rows([sq, sk, sv])
         fp8 = fused_w is not None and _fp8_ok(C, nq, nkv, wfc.shape[0])
+        # producers that hold whole rows report max|output| themselves: no separate pass for the fp8 scale
+        amax_xn = _zeroed_scalar(dev) if fp8 else None
+        _C.mixnorm_fwd(x2, x02, resid_lambdas, x0_lambdas, layer, xm, xn, amax_xn)
+
+        qkv = torch.empty(M, nq + 2 * nkv, dtype=BF16, device=dev)
         f8 = None          # fp8 copies of the GEMM inputs, kept for the weight-gradient GEMMs
         if fp8:
-            xq8, sx = quantize(xn)
+            xq8, sx = quantize(xn, amax=amax_xn)
             w8, sw = fp8_weight(fused_w)
             gemm(xq8, w8, qkv, scale_a=sx, scale_b=sw)
         elif fused_w is not None:
@@ -502,8 +506,9 @@ class _LayerFn(Function):
             yq8, sy = quantize(y2)
             w8, sw = fp8_weight(shadow_of(wo))
             gemm(yq8, w8, xa, aux=xm, beta=1.0, scale_a=sy, scale_b=sw)
-            _C.norm_fwd(xa, xn2)
-            x2q8, s2 = quantize(xn2)
+            amax_xn2 = _zeroed_scalar(dev)
+            _C.norm_fwd(xa, xn2, amax_xn2)
+            x2q8, s2 = quantize(xn2, amax=amax_xn2)
             w8, sw = fp8_weight(shadow_of(wfc))
             amax_h = _zeroed_scalar(dev)
             gemm(x2q8, w8, h, epi=EPI_RELU2, scale_a=s2, scale_b=sw, amax_out=amax_h)
@@ -513,7 +518,7 @@ class _LayerFn(Function):
             f8 = (xq8, sx, yq8, sy, x2q8, s2, hq8, sh)
         else:
             gemm(y2, shadow_of(wo), xa, aux=xm, beta=1.0)
-            _C.norm_fwd(xa, xn2)
+            _C.norm_fwd(xa, xn2, None)
             gemm(xn2, shadow_of(wfc), h, epi=EPI_RELU2)
             gemm(h, shadow_of(wpr), xo, aux=xa, beta=1.0)
 
@@ -540,7 +545,10 @@ class _LayerFn(Function):
         dh = torch.empty_like(h)
         dxn2 = torch.empty(M, C, dtype=BF16, device=dev)
         if f8 is not None:
-            g8, sg = quantize(dxo2, E5M2)
+            # the layer above published max|dx| when its mix+norm backward wrote this very tensor
+            hint = _amax_hints.pop(dxo2.data_ptr(), None)
+            _amax_hints.clear()
+            g8, sg = quantize(dxo2, E5M2, amax=hint)
             w8, sw = fp8_weight(shadow_of(wpr))
             amax_dh = _zeroed_scalar(dev)
             gemm(g8, w8, dh, b_mn=True, aux=h, epi=EPI_MUL2SQRT, scale_a=sg, scale_b=sw, amax_out=amax_dh)
@@ -558,12 +566,13 @@ class _LayerFn(Function):
             _accumulate_wgrad(wfc, dh, xn2)
         del dh
         dxa = torch.empty(M, C, dtype=BF16, device=dev)
-        _C.normadd_bwd(dxn2, xa, dxo2, dxa)
+        amax_dxa = _zeroed_scalar(dev) if f8 is not None else None
+        _C.normadd_bwd(dxn2, xa, dxo2, dxa, amax_dxa)
 
         # ---- attention output projection
         dy = dxn2  # reuse
         if f8 is not None:
-            a8, sa = quantize(dxa, E5M2)
+            a8, sa = quantize(dxa, E5M2, amax=amax_dxa)
             w8, sw = fp8_weight(shadow_of(wo))
             gemm(a8, w8, dy, b_mn=True, scale_a=sa, scale_b=sw)
             _accumulate_wgrad(wo, a8, yq8, sa, sy)
@@ -628,8 +637,11 @@ class _LayerFn(Function):
         # ---- mix + norm
         dx = torch.empty(M, C, dtype=BF16, device=dev)
         dx0 = torch.empty(M, C, dtype=BF16, device=dev)
+        amax_dx = _zeroed_scalar(dev) if f8 is not None else None
         _C.mixnorm_bwd(dxn, dxa, dgate_x, xm, x2, x02, resid_lambdas, x0_lambdas, layer, dx, dx0, False,
-                       _grad_buffer(resid_lambdas), _grad_buffer(x0_lambdas))
+                       _grad_buffer(resid_lambdas), _grad_buffer(x0_lambdas), amax_dx)
+        if amax_dx is not None:
+            _amax_hints[dx.data_ptr()] = amax_dx
         return (dx.view(B, T, C), dx0.view(B, T, C)) + (None,) * 17
 
 

@@ -102,7 +102,7 @@ class DecodeGraph:
         backout_layer = m.config.n_layer // 2
         scale = 1.0 / (128 ** 0.5)
         for i, w in enumerate(self.w):
-            C_.mixnorm_fwd(x, x0, m.resid_lambdas, m.x0_lambdas, i, self.xm, self.xn)
+            C_.mixnorm_fwd(x, x0, m.resid_lambdas, m.x0_lambdas, i, self.xm, self.xn, None)
             C_.gemv_rows(self.xn, w["qkv"], self.qkv, None, 0)
             ve = m.value_embeds[str(i)].weight if str(i) in m.value_embeds else None
             kc, vc = cache.get_layer_cache(i)
@@ -113,7 +113,7 @@ class DecodeGraph:
             window = window if 0 <= window < cache.max_seq_len else -1
             C_.decode_attn(self.qkv[:, :nq], kc, vc, cache.cache_seqlens, H, Hkv, window, scale, self.scratch, self.y)
             C_.gemv_rows(self.y, w["o"], self.xa, self.xm, 0)
-            C_.norm_fwd(self.xa, self.xn2)
+            C_.norm_fwd(self.xa, self.xn2, None)
             C_.gemv_rows(self.xn2, w["fc"], self.h, None, 1)
             out = self.x_backout if i == backout_layer else self.xs[i & 1]
             C_.gemv_rows(self.h, w["pr"], out, self.xa, 0)
