@@ -246,7 +246,8 @@ void softcap_logits(const Tensor& logits, Tensor& out, int64_t V, double cap) {
 }
 
 // ---------------------------------------------------------------------------- decode
-void gemv_rows(const Tensor& x, const Tensor& W, Tensor& out, const optional<Tensor>& aux, int64_t epi) {
+void gemv_rows(const Tensor& x, const Tensor& W, Tensor& out, const optional<Tensor>& aux, int64_t epi,
+               bool norm_input) {
   check_bf16(x, "x"); check_bf16(W, "W"); check_bf16(out, "out");
   TORCH_CHECK(x.dim() == 2 && W.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && W.stride(1) == 1 &&
               out.stride(1) == 1, "gemv: 2-D row-major tensors");
@@ -259,7 +260,7 @@ void gemv_rows(const Tensor& x, const Tensor& W, Tensor& out, const optional<Ten
     ap = aux->data_ptr(); lda = aux->stride(0);
   }
   NC_CHECK(nc::gemv_rows(x.data_ptr(), x.stride(0), W.data_ptr(), W.stride(0), out.data_ptr(), out.stride(0), ap, lda,
-                         (int)x.size(0), (int)W.size(0), (int)x.size(1), (int)epi, cur_stream()));
+                         (int)x.size(0), (int)W.size(0), (int)x.size(1), (int)epi, norm_input ? 1 : 0, cur_stream()));
 }
 
 // qkv: (B, (H+2Hkv)*128); cos/sin: (Tmax, 64); seqlens: int32 (B); k_cache/v_cache: (B, Tmax, Hkv, 128) of one layer.
@@ -294,12 +295,23 @@ void decode_attn(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, 
   TORCH_CHECK(scratch.scalar_type() == at::kFloat &&
               (size_t)scratch.numel() >= nc::decode_attn_scratch_floats((int)q.size(0), (int)H), "scratch too small");
   const c10::cuda::CUDAGuard guard(q.device());
-  g_launches += 1;
   NC_CHECK(nc::decode_attn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0),
                            k_cache.stride(1), seqlens.data_ptr<int>(), (int)q.size(0), (int)H, (int)Hkv, (int)window,
                            (float)scale, scratch.data_ptr<float>(), y.data_ptr(), y.stride(0), cur_stream()));
 }
 int64_t decode_attn_scratch(int64_t B, int64_t H) { return (int64_t)nc::decode_attn_scratch_floats((int)B, (int)H); }
+
+void sample_next_token(const Tensor& logits, const Tensor& u, double temperature, int64_t top_k, Tensor& out) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1,
+              "logits: CUDA fp32 (B, V)");
+  TORCH_CHECK(u.is_cuda() && u.scalar_type() == at::kFloat && u.is_contiguous() && u.numel() == logits.size(0), "u: fp32 (B)");
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kLong && out.is_contiguous() && out.numel() == logits.size(0),
+              "out: int64 (B)");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  NC_CHECK(nc::sample_next_token(logits.data_ptr<float>(), logits.stride(0), (int)logits.size(0), (int)logits.size(1),
+                                 u.data_ptr<float>(), (float)temperature, (int)top_k,
+                                 reinterpret_cast<long long*>(out.data_ptr<int64_t>()), cur_stream()));
+}
 
 // ------------------------------------------------------------------------- optimizer
 void adamw_step(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const optional<Tensor>& shadow, double lr,
@@ -437,6 +449,7 @@ void p2p_small_adamw(const std::vector<int64_t>& grads, int64_t grad_off, Tensor
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_pick_bn", &gemm_pick_bn);
+  m.def("sample_next_token", &sample_next_token);
   m.def("gemv_rows", &gemv_rows);
   m.def("decode_qkv_post", &decode_qkv_post);
   m.def("decode_attn", &decode_attn);

@@ -8,7 +8,7 @@
 //   decode_qkv_post  rotary at position seqlens[b], RMS norm and scale of q and k, value-embedding gate
 //                    on v, and the append of k and v to the (B, T, Hkv, D) cache: one warp per head.
 //   decode_attn      flash-decoding: grid (splits, heads, rows), each CTA reduces a slice of the visible
-//                    keys with an online softmax; decode_attn_combine merges the slices.
+//                    keys with an online softmax; the CTA that finishes last merges the slices.
 // The reference does these steps with generic library ops (reference: nanochat/gpt.py:84-107,
 // nanochat/flash_attention.py:113-170 for the cached-attention call).
 #include "decode.h"
@@ -56,14 +56,14 @@ template <int B>
 __global__ void __launch_bounds__(256)
 gemv_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ W, long long ldw,
                  __nv_bfloat16* __restrict__ out, long long ldo, const __nv_bfloat16* __restrict__ aux, long long ldaux,
-                 int N, int K, int epi) {
+                 int N, int K, int epi, int norm_input) {
   const int lane = threadIdx.x & 31;
   const int n = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (n >= N) return;                       // whole warps leave together
   const __nv_bfloat16* wrow = W + (long long)n * ldw;
-  float acc[B];
+  float acc[B], ss[B];
 #pragma unroll
-  for (int b = 0; b < B; ++b) acc[b] = 0.f;
+  for (int b = 0; b < B; ++b) { acc[b] = 0.f; ss[b] = 0.f; }
   // the weights do not depend on the previous kernel: the first loads are in flight while it finishes
   constexpr int PRE = 4;
   uint4 pre[PRE];
@@ -82,6 +82,10 @@ gemv_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_
       const float2 x0 = unpack_bf16(xv.x), x1 = unpack_bf16(xv.y), x2 = unpack_bf16(xv.z), x3 = unpack_bf16(xv.w);
       acc[b] += w0.x * x0.x + w0.y * x0.y + w1.x * x1.x + w1.y * x1.y + w2.x * x2.x + w2.y * x2.y + w3.x * x3.x +
                 w3.y * x3.y;
+      // rmsnorm(x) . w = rstd * (x . w): the row's sum of squares rides along (every warp sees the whole row)
+      if (norm_input)
+        ss[b] += x0.x * x0.x + x0.y * x0.y + x1.x * x1.x + x1.y * x1.y + x2.x * x2.x + x2.y * x2.y + x3.x * x3.x +
+                 x3.y * x3.y;
     }
   };
 #pragma unroll
@@ -92,7 +96,10 @@ gemv_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_
 #pragma unroll 4
   for (int k = lane * 8 + PRE * 256; k < K; k += 256) fma_chunk(ld_stream(wrow + k), k);
 #pragma unroll
-  for (int b = 0; b < B; ++b) acc[b] = warp_sum(acc[b]);
+  for (int b = 0; b < B; ++b) {
+    acc[b] = warp_sum(acc[b]);
+    if (norm_input) acc[b] *= rsqrtf(warp_sum(ss[b]) / K + kRmsEps);
+  }
   if (lane < B) {
     float v = 0.f;
 #pragma unroll
@@ -164,7 +171,8 @@ __global__ void __launch_bounds__(128)
 decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __nv_bfloat16* __restrict__ k_cache,
                    const __nv_bfloat16* __restrict__ v_cache, long long c_bat, long long c_tok,
                    const int* __restrict__ seqlens, int H, int Hkv, int window, float scale_log2,
-                   float* __restrict__ partial) {
+                   float* __restrict__ partial, unsigned int* __restrict__ arrivals, __nv_bfloat16* __restrict__ y,
+                   long long ldy) {
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hkv = h / (H / Hkv);
@@ -209,32 +217,32 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
   float* dst = partial + (((long long)b * H + h) * kSplits + split) * 130;
   if (d == 0) { dst[0] = M; dst[1] = L; }
   dst[2 + d] = O;
-}
-
-// grid (H, B), 128 threads
-__global__ void __launch_bounds__(128)
-decode_attn_combine_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ y, long long ldy, int H) {
-  const int h = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
-  pdl_wait();
-  pdl_trigger();
-  const float* src = partial + ((long long)b * H + h) * kSplits * 130;
-  float M = -1.0e30f;
+  // the split that arrives last merges all of them (the counter wraps back to zero by itself)
+  __shared__ unsigned int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = atomicInc(arrivals + b * H + h, kSplits - 1) == kSplits - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const volatile float* src = partial + ((long long)b * H + h) * kSplits * 130;
+  float Mx = -1.0e30f;
 #pragma unroll
-  for (int s = 0; s < kSplits; ++s) M = fmaxf(M, src[s * 130]);
-  float L = 0.f, O = 0.f;
+  for (int s = 0; s < kSplits; ++s) Mx = fmaxf(Mx, src[s * 130]);
+  float Ls = 0.f, Os = 0.f;
 #pragma unroll
   for (int s = 0; s < kSplits; ++s) {
-    const float f = exp2f(src[s * 130] - M);
-    L += f * src[s * 130 + 1];
-    O += f * src[s * 130 + 2 + d];
+    const float f = exp2f(src[s * 130] - Mx);
+    Ls += f * src[s * 130 + 1];
+    Os += f * src[s * 130 + 2 + d];
   }
-  y[b * ldy + h * 128 + d] = __float2bfloat16(L > 0.f ? O / L : 0.f);
+  y[b * ldy + h * 128 + d] = __float2bfloat16(Ls > 0.f ? Os / Ls : 0.f);
 }
 
 }  // namespace
 
 cudaError_t gemv_rows(const void* x, long long ldx, const void* W, long long ldw, void* out, long long ldo,
-                      const void* aux, long long ldaux, int B, int N, int K, int epi, cudaStream_t s) {
+                      const void* aux, long long ldaux, int B, int N, int K, int epi, int norm_input, cudaStream_t s) {
   if (B < 1 || B > 8 || (K & 7) || (ldx & 7) || (ldw & 7)) return cudaErrorInvalidValue;
   const int grid = (N + 7) / 8;
   auto xp = reinterpret_cast<const __nv_bfloat16*>(x);
@@ -242,7 +250,7 @@ cudaError_t gemv_rows(const void* x, long long ldx, const void* W, long long ldw
   auto op = reinterpret_cast<__nv_bfloat16*>(out);
   auto ap = reinterpret_cast<const __nv_bfloat16*>(aux);
   cudaError_t e = cudaSuccess;
-#define NC_GEMV(BB) case BB: e = launch_pdl(gemv_rows_kernel<BB>, dim3(grid), dim3(256), s, xp, ldx, wp, ldw, op, ldo, ap, ldaux, N, K, epi); break;
+#define NC_GEMV(BB) case BB: e = launch_pdl(gemv_rows_kernel<BB>, dim3(grid), dim3(256), s, xp, ldx, wp, ldw, op, ldo, ap, ldaux, N, K, epi, norm_input); break;
   switch (B) {
     NC_GEMV(1) NC_GEMV(2) NC_GEMV(3) NC_GEMV(4) NC_GEMV(5) NC_GEMV(6) NC_GEMV(7) NC_GEMV(8)
   }
@@ -262,19 +270,18 @@ cudaError_t decode_qkv_post(void* qkv, long long ld, int H, int Hkv, const void*
       reinterpret_cast<__nv_bfloat16*>(v_cache), c_bat, c_tok, t_max, B, status);
 }
 
-size_t decode_attn_scratch_floats(int B, int H) { return (size_t)B * H * kSplits * 130; }
+// partial results plus one arrival counter per (row, head); the counters must start at zero (they return to zero)
+size_t decode_attn_scratch_floats(int B, int H) { return (size_t)B * H * kSplits * 130 + (size_t)B * H; }
 
 cudaError_t decode_attn(const void* q, long long ldq, const void* k_cache, const void* v_cache, long long c_bat,
                         long long c_tok, const int* seqlens, int B, int H, int Hkv, int window, float scale,
                         float* scratch, void* y, long long ldy, cudaStream_t s) {
   if (H % Hkv != 0) return cudaErrorInvalidValue;
-  cudaError_t e = launch_pdl(decode_attn_kernel, dim3(kSplits, H, B), dim3(128), s,
+  unsigned int* arrivals = reinterpret_cast<unsigned int*>(scratch + (size_t)B * H * kSplits * 130);
+  return launch_pdl(decode_attn_kernel, dim3(kSplits, H, B), dim3(128), s,
       reinterpret_cast<const __nv_bfloat16*>(q), ldq, reinterpret_cast<const __nv_bfloat16*>(k_cache),
       reinterpret_cast<const __nv_bfloat16*>(v_cache), c_bat, c_tok, seqlens, H, Hkv, window,
-      scale * 1.4426950408889634f, scratch);
-  if (e != cudaSuccess) return e;
-  return launch_pdl(decode_attn_combine_kernel, dim3(H, B), dim3(128), s, static_cast<const float*>(scratch),
-                    reinterpret_cast<__nv_bfloat16*>(y), ldy, H);
+      scale * 1.4426950408889634f, scratch, arrivals, reinterpret_cast<__nv_bfloat16*>(y), ldy);
 }
 
 }  // namespace nc

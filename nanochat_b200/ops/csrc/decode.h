@@ -8,9 +8,10 @@ namespace nc {
 
 enum DecodeEpilogue : int { DEC_EPI_NONE = 0, DEC_EPI_RELU2 = 1 };
 
-// out[b, n] = epi(sum_k x[b, k] * W[n, k]) + aux[b, n]   for b < B <= 8 (aux optional). K, ldx, ldw multiples of 8.
+// out[b, n] = epi(sum_k xe[b, k] * W[n, k]) + aux[b, n]   for b < B <= 8 (aux optional). K, ldx, ldw multiples of 8.
+// norm_input != 0: xe = rmsnorm(x) (the normalisation is folded into the dot products), else xe = x.
 cudaError_t gemv_rows(const void* x, long long ldx, const void* W, long long ldw, void* out, long long ldo,
-                      const void* aux, long long ldaux, int B, int N, int K, int epi, cudaStream_t s);
+                      const void* aux, long long ldaux, int B, int N, int K, int epi, int norm_input, cudaStream_t s);
 
 // In place on qkv (B rows of [q heads | k heads | v heads]): rotary at position seqlens[b] + RMS norm + 1.2 on
 // q and k; v += 3*sigmoid(xn[:12] . wg[hkv]) * ve[idx[b]] when ve != nullptr; k and v are appended to the
@@ -22,7 +23,7 @@ cudaError_t decode_qkv_post(void* qkv, long long ld, int H, int Hkv, const void*
                             long long c_tok, int t_max, int B, int* status, cudaStream_t s);
 
 // y[b, h, :] = softmax(q[b, h] . K[b, lo..pos, hkv] * scale) V, pos = seqlens[b], lo = max(0, pos - window)
-// (window < 0: 0). scratch: decode_attn_scratch_floats(B, H) floats.
+// (window < 0: 0). scratch: decode_attn_scratch_floats(B, H) floats, zeroed once before the first call.
 size_t decode_attn_scratch_floats(int B, int H);
 cudaError_t decode_attn(const void* q, long long ldq, const void* k_cache, const void* v_cache, long long c_bat,
                         long long c_tok, const int* seqlens, int B, int H, int Hkv, int window, float scale,

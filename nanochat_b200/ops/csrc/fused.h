@@ -54,6 +54,11 @@ cudaError_t softcap_ce_bwd(void* logits, long long ld, const long long* targets,
 // Inference: out[row, :V] = cap*tanh(l/cap) in fp32.
 cudaError_t softcap_logits(const void* logits, long long ld, float* out, int M, int V, float cap, cudaStream_t s);
 
+// ---- sampling (sample.cu): out[b] = argmax (temperature <= 0) or a draw from softmax(top_k(logits[b]) / temperature)
+// at the uniform number u[b] in [0, 1); top_k <= 0 keeps the whole vocabulary. logits fp32 (B, V), row pitch ld.
+cudaError_t sample_next_token(const float* logits, long long ld, int B, int V, const float* u, float temperature,
+                              int top_k, long long* out, cudaStream_t s);
+
 // ---- optimizer (optim.cu)
 struct AdamWArgs {
   float lr, beta1, beta2, eps, wd, bias1, bias2;   // bias_i = 1 - beta_i^step

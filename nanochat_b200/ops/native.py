@@ -342,6 +342,22 @@ def softcap_logits(x, w, vocab_size, softcap=ref_ops.SOFTCAP):
     return out.view(*x.shape[:-1], vocab_size)
 
 
+def sample_next_token(logits, rng, temperature=1.0, top_k=None):
+    """(B, V) fp32 logits -> (B, 1) ids in one kernel. The uniform numbers come from `rng`, so a seed fixes the
+    tokens; the draw differs from torch.multinomial's for the same seed (same distribution)."""
+    assert temperature >= 0.0, "temperature must be non-negative"
+    B = logits.shape[0]
+    if logits.stride(1) != 1:
+        logits = logits.contiguous()
+    if temperature > 0.0:
+        u = torch.rand(B, generator=rng, device=logits.device, dtype=torch.float32)
+    else:
+        u = torch.zeros(B, device=logits.device, dtype=torch.float32)
+    out = torch.empty(B, dtype=torch.long, device=logits.device)
+    _C.sample_next_token(logits, u, float(temperature), int(top_k) if top_k else 0, out)
+    return out.view(B, 1)
+
+
 # --------------------------------------------------------------------------- attention
 
 def _attention_sdpa_fwd(q, k, v, window):

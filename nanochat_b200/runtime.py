@@ -43,7 +43,7 @@ class DecodeGraph:
         self.qkv, self.y, self.h = e(B, nq + 2 * nkv), e(B, nq), e(B, 4 * C)
         self.logits_bf16 = e(B, model.lm_head.weight.shape[0])
         self.logits = e(B, cfg.vocab_size, dtype=torch.float32)
-        self.scratch = e(self.C_.decode_attn_scratch(B, self.H), dtype=torch.float32)
+        self.scratch = torch.zeros(self.C_.decode_attn_scratch(B, self.H), dtype=torch.float32, device=dev)
         self.cos = model.cos.reshape(-1, 64).contiguous()
         self.sin = model.sin.reshape(-1, 64).contiguous()
         self.weights_epoch = None
@@ -103,7 +103,7 @@ class DecodeGraph:
         scale = 1.0 / (128 ** 0.5)
         for i, w in enumerate(self.w):
             C_.mixnorm_fwd(x, x0, m.resid_lambdas, m.x0_lambdas, i, self.xm, self.xn, None)
-            C_.gemv_rows(self.xn, w["qkv"], self.qkv, None, 0)
+            C_.gemv_rows(self.xn, w["qkv"], self.qkv, None, 0, False)
             ve = m.value_embeds[str(i)].weight if str(i) in m.value_embeds else None
             kc, vc = cache.get_layer_cache(i)
             C_.decode_qkv_post(self.qkv, H, Hkv, self.cos, self.sin, cache.cache_seqlens,
@@ -112,14 +112,13 @@ class DecodeGraph:
             window = m.window_sizes[i][0]
             window = window if 0 <= window < cache.max_seq_len else -1
             C_.decode_attn(self.qkv[:, :nq], kc, vc, cache.cache_seqlens, H, Hkv, window, scale, self.scratch, self.y)
-            C_.gemv_rows(self.y, w["o"], self.xa, self.xm, 0)
-            C_.norm_fwd(self.xa, self.xn2, None)
-            C_.gemv_rows(self.xn2, w["fc"], self.h, None, 1)
+            C_.gemv_rows(self.y, w["o"], self.xa, self.xm, 0, False)
+            C_.gemv_rows(self.xa, w["fc"], self.h, None, 1, True)          # norm(xa) folded into the GEMV
             out = self.x_backout if i == backout_layer else self.xs[i & 1]
-            C_.gemv_rows(self.h, w["pr"], out, self.xa, 0)
+            C_.gemv_rows(self.h, w["pr"], out, self.xa, 0, False)
             x = out
         C_.backout_norm_fwd(x, self.x_backout, m.backout_lambda.detach().float(), self.xn)
-        C_.gemv_rows(self.xn, self.lm_head, self.logits_bf16, None, 0)
+        C_.gemv_rows(self.xn, self.lm_head, self.logits_bf16, None, 0, False)
         C_.softcap_logits(self.logits_bf16, self.logits, m.config.vocab_size, ref_ops.SOFTCAP)
         cache.cache_seqlens.add_(1)
 

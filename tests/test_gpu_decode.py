@@ -54,12 +54,16 @@ def test_gemv_rows_matches_fp32():
         W = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(BF16)
         aux = torch.randn(B, N, device="cuda", generator=g).to(BF16)
         out = torch.empty(B, N, dtype=BF16, device="cuda")
-        nat._C.gemv_rows(x, W, out, None, 0)
+        nat._C.gemv_rows(x, W, out, None, 0, False)
         ref = x.float() @ W.float().t()
         assert ((out.float() - ref).norm() / ref.norm()).item() < 1e-2
-        nat._C.gemv_rows(x, W, out, aux, 1)
+        nat._C.gemv_rows(x, W, out, aux, 1, False)
         ref2 = torch.relu(ref) ** 2 + aux.float()
         assert ((out.float() - ref2).norm() / ref2.norm()).item() < 1e-2
+        nat._C.gemv_rows(x, W, out, None, 0, True)       # rmsnorm of the input rows folded in
+        xf = x.float()
+        ref3 = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1.1920929e-07)) @ W.float().t()
+        assert ((out.float() - ref3).norm() / ref3.norm()).item() < 1e-2
 
 
 def test_decode_attention_matches_fp32():
@@ -70,7 +74,7 @@ def test_decode_attention_matches_fp32():
     vc = torch.randn(B, T, Hkv, 128, device="cuda", generator=g).to(BF16)
     q = torch.randn(B, H * 128, device="cuda", generator=g).to(BF16)
     seqlens = torch.tensor([5, 150, 299], dtype=torch.int32, device="cuda")
-    scratch = torch.empty(nat._C.decode_attn_scratch(B, H), dtype=torch.float32, device="cuda")
+    scratch = torch.zeros(nat._C.decode_attn_scratch(B, H), dtype=torch.float32, device="cuda")
     for window in (-1, 64):
         y = torch.empty(B, H * 128, dtype=BF16, device="cuda")
         nat._C.decode_attn(q, kc, vc, seqlens, H, Hkv, window, 1.0 / math.sqrt(128), scratch, y)
@@ -111,3 +115,40 @@ def test_decode_graph_matches_cached_forward_and_engine_is_greedy_consistent():
     # a second generation reuses the captured graph and gives the same tokens
     again = [c for c, _ in eng.generate(prompt, num_samples=2, max_tokens=40, temperature=0.0)]
     assert again == fast
+
+
+def test_sampling_kernel_semantics():
+    from nanochat_b200.ops import native as nat
+    g = torch.Generator(device="cuda").manual_seed(7)
+    B, V = 4, 32768
+    logits = (torch.randn(B, V, device="cuda", generator=g) * 3).float()
+    logits[1, 77] = 50.0
+    # temperature 0: argmax, first index on ties
+    logits[2, 100] = logits[2, 200] = 60.0
+    out = nat.sample_next_token(logits, None, 0.0, None)
+    assert out[:, 0].tolist() == logits.argmax(dim=-1).tolist() and out[2, 0].item() == 100
+    # top-k: every draw lies inside the top-k set; same seed -> same tokens; different seeds differ somewhere
+    k = 50
+    topk = torch.topk(logits, k, dim=-1).indices
+    draws = []
+    for seed in (1, 1, 2):
+        rng = torch.Generator(device="cuda").manual_seed(seed)
+        cols = [nat.sample_next_token(logits, rng, 1.0, k)[:, 0] for _ in range(16)]
+        draws.append(torch.stack(cols, 1))
+    assert torch.equal(draws[0], draws[1]) and not torch.equal(draws[0], draws[2])
+    for b in range(B):
+        assert set(draws[0][b].tolist()) <= set(topk[b].tolist())
+    assert (draws[0][1] == 77).all()                    # a dominating logit is always drawn
+    # distribution: empirical frequencies of the top entries follow softmax over the top-k set
+    row = logits[0:1].expand(4096, V).contiguous()
+    rng = torch.Generator(device="cuda").manual_seed(3)
+    samples = nat.sample_next_token(row, rng, 1.0, k)[:, 0]
+    vals, idx = torch.topk(logits[0], k)
+    probs = torch.softmax(vals, 0)
+    for j in range(3):
+        freq = (samples == idx[j]).float().mean().item()
+        assert abs(freq - probs[j].item()) < 0.03 + 0.2 * probs[j].item(), (j, freq, probs[j].item())
+    # no top-k: full-vocabulary sampling at a low temperature concentrates on the maximum
+    rng = torch.Generator(device="cuda").manual_seed(4)
+    cold = nat.sample_next_token(logits, rng, 0.05, None)[:, 0]
+    assert (cold == logits.argmax(-1)).float().mean().item() >= 0.5
