@@ -117,6 +117,7 @@ def softcap_cross_entropy(x, w, targets, vocab_size, reduction="mean", softcap=r
 
 
 def sample_next_token(logits, rng, temperature=1.0, top_k=None):
-    if logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and _MODE == "native":
+    if (logits.is_cuda and logits.dtype == torch.float32 and logits.dim() == 2 and logits.size(1) <= 32768
+            and _MODE == "native"):
         return native_module().sample_next_token(logits, rng, temperature, top_k)
     return reference.sample_next_token(logits, rng, temperature, top_k)

@@ -1,10 +1,11 @@
 // Single-token decode kernels (a few rows per step, positions read from device memory so that a
 // captured CUDA graph can be replayed without host-side arguments changing).
 //
-//   gemv_rows        out[b, n] = epi( sum_k x[b, k] W[n, k] , aux[b, n] ),  b < 8. One warp per output
-//                    column streams its weight row once with 16-byte loads; the handful of activation
-//                    rows stay in L1. Decode is bound by reading every weight once per token, so the
-//                    kernel is a bandwidth kernel: no tensor cores, many loads in flight.
+//   gemv_rows        out[b, n] = epi( sum_k x[b, k] W[n, k] , aux[b, n] ),  b < 8. A CTA owns four output
+//                    columns and its 256 threads split K, streaming the weight rows once with 16-byte
+//                    loads; the handful of activation rows stay in L1. Decode is bound by reading every
+//                    weight once per token, so the kernel is a bandwidth kernel: no tensor cores, many
+//                    loads in flight on every SM whatever the shape.
 //   decode_qkv_post  rotary at position seqlens[b], RMS norm and scale of q and k, value-embedding gate
 //                    on v, and the append of k and v to the (B, T, Hkv, D) cache: one warp per head.
 //   decode_attn      flash-decoding: grid (splits, heads, rows), each CTA reduces a slice of the visible
@@ -52,61 +53,91 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+constexpr int GEMV_ROWS = 4;       // output columns per CTA: all 256 threads split K for each of them
+
 template <int B>
 __global__ void __launch_bounds__(256)
 gemv_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ W, long long ldw,
                  __nv_bfloat16* __restrict__ out, long long ldo, const __nv_bfloat16* __restrict__ aux, long long ldaux,
                  int N, int K, int epi, int norm_input) {
-  const int lane = threadIdx.x & 31;
-  const int n = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  if (n >= N) return;                       // whole warps leave together
-  const __nv_bfloat16* wrow = W + (long long)n * ldw;
-  float acc[B], ss[B];
+  __shared__ float s_acc[8][GEMV_ROWS][B];
+  __shared__ float s_ss[8][B];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n0 = blockIdx.x * GEMV_ROWS;
+  float acc[GEMV_ROWS][B], ss[B];
 #pragma unroll
-  for (int b = 0; b < B; ++b) { acc[b] = 0.f; ss[b] = 0.f; }
+  for (int b = 0; b < B; ++b) {
+    ss[b] = 0.f;
+#pragma unroll
+    for (int r = 0; r < GEMV_ROWS; ++r) acc[r][b] = 0.f;
+  }
   // the weights do not depend on the previous kernel: the first loads are in flight while it finishes
-  constexpr int PRE = 4;
-  uint4 pre[PRE];
+  uint4 pre[GEMV_ROWS];
+  const int k_first = tid * 8;
 #pragma unroll
-  for (int i = 0; i < PRE; ++i) {
-    const int k = lane * 8 + i * 256;
-    pre[i] = k < K ? ld_stream(wrow + k) : make_uint4(0, 0, 0, 0);
+  for (int r = 0; r < GEMV_ROWS; ++r) {
+    const int n = min(n0 + r, N - 1);
+    pre[r] = k_first < K ? ld_stream(W + (long long)n * ldw + k_first) : make_uint4(0, 0, 0, 0);
   }
   pdl_wait();
   pdl_trigger();
-  auto fma_chunk = [&](const uint4& wv, int k) {
-    const float2 w0 = unpack_bf16(wv.x), w1 = unpack_bf16(wv.y), w2 = unpack_bf16(wv.z), w3 = unpack_bf16(wv.w);
+  auto fma_chunk = [&](const uint4 (&wv)[GEMV_ROWS], int k) {
+    float wf[GEMV_ROWS][8];
+#pragma unroll
+    for (int r = 0; r < GEMV_ROWS; ++r) {
+      const float2 w0 = unpack_bf16(wv[r].x), w1 = unpack_bf16(wv[r].y), w2 = unpack_bf16(wv[r].z), w3 = unpack_bf16(wv[r].w);
+      wf[r][0] = w0.x; wf[r][1] = w0.y; wf[r][2] = w1.x; wf[r][3] = w1.y;
+      wf[r][4] = w2.x; wf[r][5] = w2.y; wf[r][6] = w3.x; wf[r][7] = w3.y;
+    }
 #pragma unroll
     for (int b = 0; b < B; ++b) {
       const uint4 xv = *reinterpret_cast<const uint4*>(x + b * ldx + k);
       const float2 x0 = unpack_bf16(xv.x), x1 = unpack_bf16(xv.y), x2 = unpack_bf16(xv.z), x3 = unpack_bf16(xv.w);
-      acc[b] += w0.x * x0.x + w0.y * x0.y + w1.x * x1.x + w1.y * x1.y + w2.x * x2.x + w2.y * x2.y + w3.x * x3.x +
-                w3.y * x3.y;
-      // rmsnorm(x) . w = rstd * (x . w): the row's sum of squares rides along (every warp sees the whole row)
-      if (norm_input)
-        ss[b] += x0.x * x0.x + x0.y * x0.y + x1.x * x1.x + x1.y * x1.y + x2.x * x2.x + x2.y * x2.y + x3.x * x3.x +
-                 x3.y * x3.y;
+      const float xf[8] = {x0.x, x0.y, x1.x, x1.y, x2.x, x2.y, x3.x, x3.y};
+      // rmsnorm(x) . w = rstd * (x . w): the row's sum of squares rides along
+      if (norm_input) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss[b] += xf[j] * xf[j];
+      }
+#pragma unroll
+      for (int r = 0; r < GEMV_ROWS; ++r)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[r][b] += wf[r][j] * xf[j];
     }
   };
+  if (k_first < K) fma_chunk(pre, k_first);
+#pragma unroll 2
+  for (int k = k_first + 2048; k < K; k += 2048) {
+    uint4 wv[GEMV_ROWS];
 #pragma unroll
-  for (int i = 0; i < PRE; ++i) {
-    const int k = lane * 8 + i * 256;
-    if (k < K) fma_chunk(pre[i], k);
+    for (int r = 0; r < GEMV_ROWS; ++r) wv[r] = ld_stream(W + (long long)min(n0 + r, N - 1) * ldw + k);
+    fma_chunk(wv, k);
   }
-#pragma unroll 4
-  for (int k = lane * 8 + PRE * 256; k < K; k += 256) fma_chunk(ld_stream(wrow + k), k);
 #pragma unroll
   for (int b = 0; b < B; ++b) {
-    acc[b] = warp_sum(acc[b]);
-    if (norm_input) acc[b] *= rsqrtf(warp_sum(ss[b]) / K + kRmsEps);
-  }
-  if (lane < B) {
-    float v = 0.f;
 #pragma unroll
-    for (int b = 0; b < B; ++b) v = lane == b ? acc[b] : v;
-    if (epi == DEC_EPI_RELU2) { v = fmaxf(v, 0.f); v *= v; }
-    if (aux) v += __bfloat162float(aux[lane * ldaux + n]);
-    out[lane * ldo + n] = __float2bfloat16(v);
+    for (int r = 0; r < GEMV_ROWS; ++r) {
+      const float v = warp_sum(acc[r][b]);
+      if (lane == 0) s_acc[warp][r][b] = v;
+    }
+    if (norm_input) {
+      const float v = warp_sum(ss[b]);
+      if (lane == 0) s_ss[warp][b] = v;
+    }
+  }
+  __syncthreads();
+  if (tid < GEMV_ROWS * B) {
+    const int r = tid / B, b = tid - r * B;
+    const int n = n0 + r;
+    if (n < N) {
+      float v = 0.f, q = 0.f;
+#pragma unroll
+      for (int w = 0; w < 8; ++w) { v += s_acc[w][r][b]; if (norm_input) q += s_ss[w][b]; }
+      if (norm_input) v *= rsqrtf(q / K + kRmsEps);
+      if (epi == DEC_EPI_RELU2) { v = fmaxf(v, 0.f); v *= v; }
+      if (aux) v += __bfloat162float(aux[b * ldaux + n]);
+      out[b * ldo + n] = __float2bfloat16(v);
+    }
   }
 }
 
@@ -184,35 +215,64 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
   const int chunk = (n_keys + kSplits - 1) / kSplits;
   const int k_begin = lo + split * chunk;
   const int k_end = min(pos + 1, k_begin + chunk);
-  const uint2 qraw = *reinterpret_cast<const uint2*>(q + b * ldq + h * 128 + lane * 4);
-  const float2 q01 = unpack_bf16(qraw.x), q23 = unpack_bf16(qraw.y);
-  const __nv_bfloat16* kb = k_cache + b * c_bat + hkv * 128 + lane * 4;
-  const __nv_bfloat16* vb = v_cache + b * c_bat + hkv * 128 + lane * 4;
-  float m = -1.0e30f, l = 0.f, o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-  for (int j = k_begin + warp; j < k_end; j += 4) {
-    const uint2 kr = *reinterpret_cast<const uint2*>(kb + (long long)j * c_tok);
-    const uint2 vr = *reinterpret_cast<const uint2*>(vb + (long long)j * c_tok);
-    const float2 k01 = unpack_bf16(kr.x), k23 = unpack_bf16(kr.y);
-    const float s = warp_sum(q01.x * k01.x + q01.y * k01.y + q23.x * k23.x + q23.y * k23.y) * scale_log2;
-    const float m_new = fmaxf(m, s);
-    const float alpha = exp2f(m - m_new), p = exp2f(s - m_new);
-    const float2 v01 = unpack_bf16(vr.x), v23 = unpack_bf16(vr.y);
-    l = l * alpha + p;
-    o0 = o0 * alpha + p * v01.x; o1 = o1 * alpha + p * v01.y; o2 = o2 * alpha + p * v23.x; o3 = o3 * alpha + p * v23.y;
-    m = m_new;
-  }
-  __shared__ float sm[4][130];
-  if (lane == 0) { sm[warp][0] = m; sm[warp][1] = l; }
-  sm[warp][2 + lane * 4] = o0; sm[warp][3 + lane * 4] = o1; sm[warp][4 + lane * 4] = o2; sm[warp][5 + lane * 4] = o3;
+  // Two phases per tile of up to 128 keys: scores with one thread per key (no shuffles in the dot product),
+  // then the weighted sum of V with one thread per output dim (coalesced rows of V).
+  __shared__ float s_q[128];
+  __shared__ float s_p[128];
+  __shared__ float s_red[8];
+  __shared__ float s_o[4][128];
+  const int d = threadIdx.x;
+  s_q[d] = __bfloat162float(q[b * ldq + h * 128 + d]);
   __syncthreads();
-  const int d = threadIdx.x;                          // 128 threads = 128 output dims
-  const float M = fmaxf(fmaxf(sm[0][0], sm[1][0]), fmaxf(sm[2][0], sm[3][0]));
-  float L = 0.f, O = 0.f;
+  const __nv_bfloat16* kb = k_cache + b * c_bat + hkv * 128;
+  const __nv_bfloat16* vb = v_cache + b * c_bat + hkv * 128 + lane * 4;   // phase 2: a lane owns 4 dims
+  float M = -1.0e30f, L = 0.f, O = 0.f;
+  for (int tile = k_begin; tile < k_end; tile += 128) {
+    const int j = tile + d;
+    float sc = -1.0e30f;
+    if (j < k_end) {
+      const uint4* kr = reinterpret_cast<const uint4*>(kb + (long long)j * c_tok);
+      float acc = 0.f;
 #pragma unroll
-  for (int w = 0; w < 4; ++w) {
-    const float f = exp2f(sm[w][0] - M);
-    L += f * sm[w][1];
-    O += f * sm[w][2 + d];
+      for (int i = 0; i < 16; ++i) {
+        const uint4 kv = kr[i];
+        const float2 k0 = unpack_bf16(kv.x), k1 = unpack_bf16(kv.y), k2 = unpack_bf16(kv.z), k3 = unpack_bf16(kv.w);
+        const float* qq = s_q + i * 8;
+        acc += k0.x * qq[0] + k0.y * qq[1] + k1.x * qq[2] + k1.y * qq[3] + k2.x * qq[4] + k2.y * qq[5] + k3.x * qq[6] +
+               k3.y * qq[7];
+      }
+      sc = acc * scale_log2;
+    }
+    float mx = sc;
+#pragma unroll
+    for (int w = 16; w > 0; w >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, w));
+    if (lane == 0) s_red[warp] = mx;
+    __syncthreads();
+    const float m_new = fmaxf(M, fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3])));
+    const float pj = j < k_end ? exp2f(sc - m_new) : 0.f;
+    s_p[d] = pj;
+    const float ps = warp_sum(pj);
+    if (lane == 0) s_red[4 + warp] = ps;
+    __syncthreads();
+    const float alpha = exp2f(M - m_new);
+    L = L * alpha + (s_red[4] + s_red[5]) + (s_red[6] + s_red[7]);
+    // weighted sum of V: warp w takes keys w, w+4, ... (independent 8-byte loads, many in flight), then the four
+    // partial vectors are added per dim
+    const int cnt = min(128, k_end - tile);
+    const __nv_bfloat16* vt = vb + (long long)tile * c_tok;
+    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
+#pragma unroll 8
+    for (int jj = warp; jj < cnt; jj += 4) {
+      const uint2 vr = *reinterpret_cast<const uint2*>(vt + (long long)jj * c_tok);
+      const float2 v01 = unpack_bf16(vr.x), v23 = unpack_bf16(vr.y);
+      const float pw = s_p[jj];
+      o0 += pw * v01.x; o1 += pw * v01.y; o2 += pw * v23.x; o3 += pw * v23.y;
+    }
+    *reinterpret_cast<float4*>(&s_o[warp][lane * 4]) = make_float4(o0, o1, o2, o3);
+    __syncthreads();
+    O = O * alpha + (s_o[0][d] + s_o[1][d]) + (s_o[2][d] + s_o[3][d]);
+    M = m_new;
+    __syncthreads();                                   // s_p, s_o and s_red are rewritten by the next tile
   }
   float* dst = partial + (((long long)b * H + h) * kSplits + split) * 130;
   if (d == 0) { dst[0] = M; dst[1] = L; }
@@ -244,7 +304,7 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
 cudaError_t gemv_rows(const void* x, long long ldx, const void* W, long long ldw, void* out, long long ldo,
                       const void* aux, long long ldaux, int B, int N, int K, int epi, int norm_input, cudaStream_t s) {
   if (B < 1 || B > 8 || (K & 7) || (ldx & 7) || (ldw & 7)) return cudaErrorInvalidValue;
-  const int grid = (N + 7) / 8;
+  const int grid = (N + GEMV_ROWS - 1) / GEMV_ROWS;
   auto xp = reinterpret_cast<const __nv_bfloat16*>(x);
   auto wp = reinterpret_cast<const __nv_bfloat16*>(W);
   auto op = reinterpret_cast<__nv_bfloat16*>(out);

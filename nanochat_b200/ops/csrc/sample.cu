@@ -17,6 +17,7 @@ namespace nc {
 namespace {
 
 constexpr int SAMPLE_THREADS = 1024;
+constexpr int PER_MAX = 32;                 // logits per thread held in registers
 
 __device__ __forceinline__ uint32_t ordered_key(float v) {
   const uint32_t b = __float_as_uint(v);
@@ -36,14 +37,27 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
   __shared__ int s_choice;
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float* x = logits + (long long)row * ld;
-  const int per = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;   // contiguous chunk per thread (index order)
+  // contiguous chunk per thread (index order), kept in registers for every pass: V <= 32 * 1024
+  const int per = ((V + SAMPLE_THREADS - 1) / SAMPLE_THREADS + 3) & ~3;
   const int lo = min(V, tid * per), hi = min(V, lo + per);
+  float xv[PER_MAX];
+  if ((ld & 3) == 0 && (V & 3) == 0) {
+#pragma unroll
+    for (int i = 0; i < PER_MAX; i += 4) {
+      float4 t = make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      if (lo + i < hi) t = *reinterpret_cast<const float4*>(x + lo + i);     // chunks are multiples of 4: all or nothing
+      xv[i] = t.x; xv[i + 1] = t.y; xv[i + 2] = t.z; xv[i + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < PER_MAX; ++i) xv[i] = lo + i < hi ? x[lo + i] : -INFINITY;
+  }
 
   // ---- 1. maximum and its first index
   float best = -INFINITY; int best_i = V;
-  for (int i = lo; i < hi; ++i) {
-    const float v = x[i];
-    if (v > best) { best = v; best_i = i; }
+#pragma unroll
+  for (int i = 0; i < PER_MAX; ++i) {
+    if (xv[i] > best) { best = xv[i]; best_i = lo + i; }
   }
 #pragma unroll
   for (int w = 16; w > 0; w >>= 1) {
@@ -80,9 +94,18 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
       if (tid < 256) s_hist[tid] = 0;
       __syncthreads();
       const uint32_t prefix = s_prefix;
-      for (int i = lo; i < hi; ++i) {
-        const uint32_t k = ordered_key(x[i]);
-        if ((k & mask) == prefix) atomicAdd(&s_hist[(k >> shift) & 0xffu], 1u);
+#pragma unroll
+      for (int i = 0; i < PER_MAX; ++i) {
+        // logits share most of their high bits, so almost every entry lands in the same few bins: lanes with
+        // equal bins elect one of them to add the whole group
+        const uint32_t k = ordered_key(xv[i]);
+        const bool hit = lo + i < hi && (k & mask) == prefix;
+        const unsigned hits = __ballot_sync(0xffffffffu, hit);
+        if (hit) {
+          const unsigned bin = (k >> shift) & 0xffu;
+          const unsigned peers = __match_any_sync(hits, bin);
+          if (lane == __ffs(peers) - 1) atomicAdd(&s_hist[bin], static_cast<unsigned>(__popc(peers)));
+        }
       }
       __syncthreads();
       if (tid == 0) {
@@ -103,9 +126,9 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
   // ---- 3. weights, scan, draw
   const float inv_t = 1.4426950408889634f / temperature;
   float part = 0.f;
-  for (int i = lo; i < hi; ++i) {
-    const float v = x[i];
-    if (ordered_key(v) >= threshold) part += exp2f((v - vmax) * inv_t);
+#pragma unroll
+  for (int i = 0; i < PER_MAX; ++i) {
+    if (lo + i < hi && ordered_key(xv[i]) >= threshold) part += exp2f((xv[i] - vmax) * inv_t);
   }
   float incl = part;                              // inclusive scan inside the warp
 #pragma unroll
@@ -133,12 +156,12 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
   if (target >= total) target = total * 0.99999994f;
   if (part > 0.f && target >= before && target < before + part) {
     float run = before; int pick = -1, last = -1;
-    for (int i = lo; i < hi; ++i) {
-      const float v = x[i];
-      if (ordered_key(v) >= threshold) {
-        last = i;
-        run += exp2f((v - vmax) * inv_t);
-        if (target < run) { pick = i; break; }
+#pragma unroll
+    for (int i = 0; i < PER_MAX; ++i) {
+      if (pick < 0 && lo + i < hi && ordered_key(xv[i]) >= threshold) {
+        last = lo + i;
+        run += exp2f((xv[i] - vmax) * inv_t);
+        if (target < run) pick = lo + i;
       }
     }
     atomicMax(&s_choice, pick >= 0 ? pick : last);   // rounding may leave the interval open: take its last entry
@@ -152,7 +175,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, const float
 
 cudaError_t sample_next_token(const float* logits, long long ld, int B, int V, const float* u, float temperature,
                               int top_k, long long* out, cudaStream_t s) {
-  if (B <= 0 || V <= 0) return cudaErrorInvalidValue;
+  if (B <= 0 || V <= 0 || V > SAMPLE_THREADS * PER_MAX) return cudaErrorInvalidValue;
   sample_kernel<<<B, SAMPLE_THREADS, 0, s>>>(logits, ld, V, u, temperature, top_k, out);
   return cudaGetLastError();
 }
