@@ -381,3 +381,24 @@ def test_backout_norm_kernels_against_fp32_oracle(nat):
     assert _rel_err(y, yf) < 1e-2
     assert _rel_err(dx, xf.grad) < 2e-2 and _rel_err(dxb, xbf.grad) < 2e-2
     assert abs(dlam.item() - lf.grad.item()) < 2e-2 * abs(lf.grad.item()) + 0.5
+
+
+def test_bounded_wait_reports_a_peer_that_never_arrives(nat):
+    """Failure detection without a fault: a 2-rank barrier whose peer slot nothing ever sets. The wait gives up
+    after its limit, the kernel returns normally, and the host reads which peer and which epoch it waited for."""
+    import time
+    my_pad = torch.zeros(64, dtype=torch.int32, device="cuda")
+    peer_pad = torch.zeros(64, dtype=torch.int32, device="cuda")     # stands in for the absent rank's pad
+    nat.check_status(my_pad)                                         # clean slate
+    t0 = time.time()
+    nat._C.p2p_barrier([my_pad.data_ptr(), peer_pad.data_ptr()], 0, 1, my_pad)
+    with pytest.raises(RuntimeError, match="failed wait: code=5"):
+        nat.check_status(my_pad)
+    assert 1.0 < time.time() - t0 < 20.0                             # it waited its limit, not forever
+    assert my_pad[0].item() == 1 and peer_pad[0].item() == 1         # this rank did announce itself
+    nat.check_status(my_pad)                                         # the status word was consumed: clean again
+    # the context is intact: an ordinary kernel still runs
+    x = torch.ones(8, 256, device="cuda", dtype=BF16)
+    y = torch.empty_like(x)
+    nat._C.norm_fwd(x, y, None)
+    assert torch.isfinite(y.float()).all()

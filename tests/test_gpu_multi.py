@@ -30,8 +30,8 @@ def test_fused_p2p_optimizer_matches_nccl(world, tmp_path):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
     records = json.load(open(out))
-    scratch = os.path.join(os.path.dirname(HERE), "gpurun_out")
-    if os.path.isdir(scratch):                      # keep the per-rank comparison for inspection
+    scratch = os.environ.get("NANOCHAT_TEST_DUMP_DIR", "")
+    if scratch and os.path.isdir(scratch):          # keep the per-rank comparison for inspection
         with open(os.path.join(scratch, f"p2p_world{world}.json"), "w") as f:
             json.dump(records, f, indent=1)
     for rec in records:

@@ -9,7 +9,8 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
-CANDIDATES = [os.path.join(ROOT, "baseline", "_ref"), "/root/reference"]
+CANDIDATES = [os.path.join(ROOT, "baseline", "_ref")] + (
+    [os.environ["NANOCHAT_REFERENCE_DIR"]] if os.environ.get("NANOCHAT_REFERENCE_DIR") else [])
 REF = next((c for c in CANDIDATES if os.path.isdir(os.path.join(c, "nanochat"))), None)
 pytestmark = [pytest.mark.slow, pytest.mark.skipif(REF is None, reason="reference sources not available")]
 
