@@ -42,6 +42,7 @@ constexpr float RESCALE_STEP = 8.f;              // log2 units the row maximum m
 struct AttnKernelArgs {
   void* o;
   float* lse;
+  float* amax_o;        // optional max |o|
   long long o_bat, o_tok, o_head;
   int Tq, Tk, H, Hkv;
   int window;           // < 0: unlimited
@@ -287,6 +288,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (__all_sync(0xffffffffu, ok) && n > 0) {
       const bool row_ok = qi < args.Tq;
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      float mxo = 0.f;
       __nv_bfloat16* orow = reinterpret_cast<__nv_bfloat16*>(args.o) + (long long)b * args.o_bat +
                             (long long)qi * args.o_tok + (long long)h * args.o_head;
 #pragma unroll 1
@@ -303,6 +305,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           w.w = pack_bf16(__uint_as_float(v[e + 6]) * inv_l, __uint_as_float(v[e + 7]) * inv_l);
           if (row_ok) *reinterpret_cast<uint4*>(orow + c * 32 + e) = w;
         }
+        if (args.amax_o && row_ok) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) mxo = fmaxf(mxo, fabsf(__uint_as_float(v[e])));
+        }
+      }
+      if (args.amax_o) {
+        mxo *= inv_l * 1.00390625f;                   // bf16 rounding may push a stored value up by one part in 256
+#pragma unroll
+        for (int w = 16; w > 0; w >>= 1) mxo = fmaxf(mxo, __shfl_xor_sync(0xffffffffu, mxo, w));
+        if (lane == 0 && mxo > 0.f) atomicMax(reinterpret_cast<unsigned int*>(args.amax_o), __float_as_uint(mxo));
       }
       if (row_ok && args.lse)
         args.lse[((long long)b * args.H + h) * args.Tq + qi] = (m_used + log2f(l_run)) * 0.6931471805599453f;
@@ -343,7 +355,7 @@ cudaError_t attention_fwd(const AttnDesc& d, int* status, cudaStream_t stream) {
   if (!make_qkv_map(&tmK, d.k, d.Tk, d.Hkv, d.B, d.k_tok, d.k_head, d.k_bat)) return cudaErrorInvalidValue;
   if (!make_qkv_map(&tmV, d.v, d.Tk, d.Hkv, d.B, d.v_tok, d.v_head, d.v_bat)) return cudaErrorInvalidValue;
   AttnKernelArgs a;
-  a.o = d.o; a.lse = d.lse; a.o_bat = d.o_bat; a.o_tok = d.o_tok; a.o_head = d.o_head;
+  a.o = d.o; a.lse = d.lse; a.amax_o = d.amax_o; a.o_bat = d.o_bat; a.o_tok = d.o_tok; a.o_head = d.o_head;
   a.Tq = d.Tq; a.Tk = d.Tk; a.H = d.H; a.Hkv = d.Hkv;
   a.window = d.window;
   a.scale_log2 = d.scale * 1.4426950408889634f;

@@ -16,6 +16,7 @@ struct AttnDesc {
   int B, Tq, Tk, H, Hkv, D;
   int window;
   float scale;
+  float* amax_o = nullptr;   // optional: receives max |o| (atomic max on the fp32 bits; zero it first)
 };
 
 cudaError_t attention_fwd(const AttnDesc& d, int* status, cudaStream_t stream);
@@ -29,6 +30,7 @@ struct AttnBwdDesc {
   void *dq, *dk, *dv;
   long long dq_bat, dq_tok, dq_head, dk_bat, dk_tok, dk_head, dv_bat, dv_tok, dv_head;
   float* delta;
+  float* amax_dv = nullptr;  // optional: receives max |dv| (atomic max on the fp32 bits; zero it first)
 };
 cudaError_t attention_bwd(const AttnBwdDesc& d, int* status, cudaStream_t stream);
 

@@ -65,6 +65,7 @@ struct AttnBwdArgs {
   const float* delta;    // (B, H, Tq)
   void* out1;            // MODE_DKV: dV ; MODE_DQ: dQ
   void* out2;            // MODE_DKV: dK ; MODE_DQ: unused
+  float* amax1;          // optional max |out1| (used for dV)
   long long o1_bat, o1_tok, o1_head, o2_bat, o2_tok, o2_head;
   int Tq, Tk, H, Hkv;
   int window;
@@ -352,6 +353,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
                        : reinterpret_cast<__nv_bfloat16*>(args.out2) + (long long)b * args.o2_bat +
                              (long long)xi * args.o2_tok + (long long)hx * args.o2_head;
         const uint32_t col0 = which == 0 ? COL_ACC1 : COL_ACC2;
+        const bool track = DKV && which == 0 && args.amax1 != nullptr;
+        float mx1 = 0.f;
 #pragma unroll 1
         for (int c = c_lo; c < c_hi; ++c) {
           uint32_t v[32];
@@ -371,6 +374,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
             w.w = pack_bf16(__uint_as_float(v[j + 6]) * mul, __uint_as_float(v[j + 7]) * mul);
             if (store_row_ok) *reinterpret_cast<uint4*>(orow + c * 32 + j) = w;
           }
+          if (track && store_row_ok) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) mx1 = fmaxf(mx1, fabsf(__uint_as_float(v[j])));
+          }
+        }
+        if (track) {                                  // warp-uniform: every lane takes part in the shuffles
+          mx1 *= mul * 1.00390625f;                   // bf16 rounding may push a stored value up by one part in 256
+#pragma unroll
+          for (int w = 16; w > 0; w >>= 1) mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, w));
+          if (lane == 0 && mx1 > 0.f) atomicMax(reinterpret_cast<unsigned int*>(args.amax1), __float_as_uint(mx1));
         }
       }
     }
@@ -454,11 +467,13 @@ cudaError_t attention_bwd(const AttnBwdDesc& d, int* status, cudaStream_t stream
   // dK, dV
   a.out1 = d.dv; a.o1_bat = d.dv_bat; a.o1_tok = d.dv_tok; a.o1_head = d.dv_head;
   a.out2 = d.dk; a.o2_bat = d.dk_bat; a.o2_tok = d.dk_tok; a.o2_head = d.dk_head;
+  a.amax1 = d.amax_dv;
   dim3 grid_kv((f.Tk + ab::BX - 1) / ab::BX, f.Hkv, f.B);
   attn_bwd_kernel<true><<<grid_kv, ab::THREADS, ab::SMEM_BYTES, stream>>>(k128, v128, q64, do64, a);
   // dQ
   a.out1 = d.dq; a.o1_bat = d.dq_bat; a.o1_tok = d.dq_tok; a.o1_head = d.dq_head;
   a.out2 = nullptr;
+  a.amax1 = nullptr;
   dim3 grid_q((f.Tq + ab::BX - 1) / ab::BX, f.H, f.B);
   attn_bwd_kernel<false><<<grid_q, ab::THREADS, ab::SMEM_BYTES, stream>>>(q128, do128, k64, v64, a);
   return cudaGetLastError();

@@ -169,7 +169,7 @@ void qkv_post_fwd(Tensor& qkv, int64_t H, int64_t Hkv, const Tensor& cos_t, cons
 void qkv_post_bwd(Tensor& dqkv, const Tensor& qkv, int64_t H, int64_t Hkv, const Tensor& cos_t, const Tensor& sin_t,
                   int64_t T, const Tensor& rstd, const optional<Tensor>& xn, const optional<Tensor>& wg,
                   const optional<Tensor>& ve, const optional<Tensor>& idx, const optional<Tensor>& dve,
-                  const optional<Tensor>& dwg, const optional<Tensor>& dgate_x) {
+                  const optional<Tensor>& dwg, const optional<Tensor>& dgate_x, const optional<Tensor>& amax_qk) {
   const c10::cuda::CUDAGuard guard(qkv.device());
   const int M = (int)(qkv.numel() / qkv.size(-1));
   const bool has_ve = ve.has_value() && ve->defined();
@@ -180,7 +180,7 @@ void qkv_post_bwd(Tensor& dqkv, const Tensor& qkv, int64_t H, int64_t Hkv, const
                             has_ve ? ve->data_ptr() : nullptr,
                             has_ve ? (const long long*)idx->data_ptr<int64_t>() : nullptr,
                             has_ve ? dve->data_ptr<float>() : nullptr, has_ve ? dwg->data_ptr<float>() : nullptr,
-                            has_ve ? dgate_x->data_ptr<float>() : nullptr, M, cur_stream()));
+                            has_ve ? dgate_x->data_ptr<float>() : nullptr, opt_scalar(amax_qk), M, cur_stream()));
 }
 void embed_fwd(const Tensor& idx, const Tensor& wte, const Tensor& gate_w, const Tensor& lam, Tensor& x,
                const optional<Tensor>& e_last) {
@@ -355,7 +355,7 @@ int64_t launch_count() { return (int64_t)g_launches.load(); }
 
 // ------------------------------------------------------------------------- attention
 void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tensor& lse, int64_t window,
-              double scale) {
+              double scale, const optional<Tensor>& amax_o) {
   const c10::cuda::CUDAGuard guard(q.device());
   nc::AttnDesc d{};
   d.B = (int)q.size(0); d.Tq = (int)q.size(1); d.H = (int)q.size(2); d.D = (int)q.size(3);
@@ -365,11 +365,13 @@ void attn_fwd(const Tensor& q, const Tensor& k, const Tensor& v, Tensor& o, Tens
   d.q_bat = q.stride(0); d.k_bat = k.stride(0); d.v_bat = v.stride(0); d.o_bat = o.stride(0);
   d.q_head = q.stride(2); d.k_head = k.stride(2); d.v_head = v.stride(2); d.o_head = o.stride(2);
   d.window = (int)window; d.scale = (float)scale;
+  d.amax_o = opt_scalar(amax_o);
   NC_CHECK(nc::attention_fwd(d, status_ptr(q), cur_stream()));
 }
 
 void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o, const Tensor& lse,
-              const Tensor& d_o, Tensor& dq, Tensor& dk, Tensor& dv, Tensor& delta, int64_t window, double scale) {
+              const Tensor& d_o, Tensor& dq, Tensor& dk, Tensor& dv, Tensor& delta, int64_t window, double scale,
+              const optional<Tensor>& amax_dv) {
   const c10::cuda::CUDAGuard guard(q.device());
   nc::AttnBwdDesc d{};
   nc::AttnDesc& f = d.fwd;
@@ -388,6 +390,7 @@ void attn_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o
   d.dk = dk.data_ptr(); d.dk_bat = dk.stride(0); d.dk_tok = dk.stride(1); d.dk_head = dk.stride(2);
   d.dv = dv.data_ptr(); d.dv_bat = dv.stride(0); d.dv_tok = dv.stride(1); d.dv_head = dv.stride(2);
   d.delta = delta.data_ptr<float>();
+  d.amax_dv = opt_scalar(amax_dv);
   NC_CHECK(nc::attention_bwd(d, status_ptr(q), cur_stream()));
   g_launches += 2;   // delta pre-pass + dK/dV kernel + dQ kernel
 }
@@ -481,6 +484,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("p2p_muon_momentum", &p2p_muon_momentum);
   m.def("p2p_bcast_bf16", &p2p_bcast_bf16);
   m.def("p2p_small_adamw", &p2p_small_adamw);
-  m.def("attn_fwd", &attn_fwd);
-  m.def("attn_bwd", &attn_bwd);
+  m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("lse"), py::arg("window"),
+        py::arg("scale"), py::arg("amax_o") = py::none());
+  m.def("attn_bwd", &attn_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("lse"), py::arg("d_o"),
+        py::arg("dq"), py::arg("dk"), py::arg("dv"), py::arg("delta"), py::arg("window"), py::arg("scale"),
+        py::arg("amax_dv") = py::none());
 }

@@ -343,7 +343,8 @@ qkv_post_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __res
                     const __nv_bfloat16* __restrict__ xn, long long ld_xn, const float* __restrict__ wg,
                     const __nv_bfloat16* __restrict__ ve, const long long* __restrict__ idx,
                     float* __restrict__ dve /* [V, Hkv*128] fp32 */, float* __restrict__ dwg /* [Hkv,12] */,
-                    float* __restrict__ dgate_x /* [M,12] */, int M) {
+                    float* __restrict__ dgate_x /* [M,12] */, float* __restrict__ amax_qk /* max |dq|, |dk| or null */,
+                    int M) {
   __shared__ float s_dwg[32 * 12];     // Hkv <= 32
   __shared__ float s_dz[4][32];        // per warp, per kv head
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -352,6 +353,7 @@ qkv_post_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __res
   const int n_items = n_rot + (ve ? Hkv : 0);
   for (int i = threadIdx.x; i < Hkv * 12; i += blockDim.x) s_dwg[i] = 0.f;
   __syncthreads();
+  float mxqk = 0.f;
   for (int tok = blockIdx.x * 4 + warp; tok < M; tok += gridDim.x * 4) {
     const int t = tok % T;
     __nv_bfloat16* drow = dqkv + (size_t)tok * ld;
@@ -384,6 +386,7 @@ qkv_post_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __res
           const float d2 = rstd * (gb[j] - yb[j] * dot);
           ga[j] = d1 * c[j] - d2 * s[j];                    // inverse rotation
           gb[j] = d1 * s[j] + d2 * c[j];
+          mxqk = fmaxf(mxqk, fmaxf(fabsf(ga[j]), fabsf(gb[j])));
         }
         *(reinterpret_cast<uint4*>(dh) + sub) = pack8(ga);
         *(reinterpret_cast<uint4*>(dh) + 8 + sub) = pack8(gb);
@@ -434,6 +437,7 @@ qkv_post_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __res
   __syncthreads();
   if (ve)
     for (int i = threadIdx.x; i < Hkv * 12; i += blockDim.x) atomicAdd(dwg + i, s_dwg[i]);
+  if (amax_qk) publish_absmax(mxqk * 1.00390625f, amax_qk, lane);   // margin for the bf16 rounding of the stores
 }
 
 // -------------------------------------------------------------------------- embedding
@@ -653,13 +657,13 @@ cudaError_t qkv_post_fwd(void* qkv, long long ld, int H, int Hkv, const void* co
 cudaError_t qkv_post_bwd(void* dqkv, const void* qkv, long long ld, int H, int Hkv, const void* cos_t,
                          const void* sin_t, int T, const float* rstd, const void* xn, long long ld_xn,
                          const float* wg, const void* ve, const long long* idx, float* dve, float* dwg,
-                         float* dgate_x, int M, cudaStream_t s) {
+                         float* dgate_x, float* amax_qk, int M, cudaStream_t s) {
   if (Hkv > 32 || (ld & 7)) return cudaErrorInvalidValue;
   const int grid = (M + 3) / 4 < 148 * 8 ? (M + 3) / 4 : 148 * 8;
   qkv_post_bwd_kernel<<<grid, 128, 0, s>>>((__nv_bfloat16*)dqkv, (const __nv_bfloat16*)qkv, ld, H, Hkv,
                                            (const __nv_bfloat16*)cos_t, (const __nv_bfloat16*)sin_t, T, rstd,
                                            (const __nv_bfloat16*)xn, ld_xn, wg, (const __nv_bfloat16*)ve, idx, dve,
-                                           dwg, dgate_x, M);
+                                           dwg, dgate_x, amax_qk, M);
   return cudaGetLastError();
 }
 

@@ -29,7 +29,7 @@ cudaError_t qkv_post_fwd(void* qkv, long long ld, int H, int Hkv, const void* co
 cudaError_t qkv_post_bwd(void* dqkv, const void* qkv, long long ld, int H, int Hkv, const void* cos_t,
                          const void* sin_t, int T, const float* rstd, const void* xn, long long ld_xn,
                          const float* wg, const void* ve, const long long* idx, float* dve, float* dwg,
-                         float* dgate_x, int M, cudaStream_t s);
+                         float* dgate_x, float* amax_qk /* optional: max |dq|, |dk| written */, int M, cudaStream_t s);
 cudaError_t embed_fwd(const long long* idx, const void* wte, const float* gate_w, const float* lam, void* x,
                       void* e_last, int M, int T, int C, cudaStream_t s);
 cudaError_t embed_bwd(const void* dx, const long long* idx, const void* wte, const float* gate_w, const float* lam,

@@ -364,26 +364,28 @@ def _attention_sdpa_fwd(q, k, v, window):
     return ref_ops.attention(q, k, v, window)
 
 
-def attention_forward(q, k, v, window):
-    """Returns (y, lse); lse is None on the SDPA path."""
+def attention_forward(q, k, v, window, amax_out=None):
+    """Returns (y, lse); lse is None on the SDPA path. `amax_out`: zeroed device scalar that receives max|y|
+    (native kernel only; check `lse is not None` before relying on it)."""
     if ATTENTION_IMPL == "native" and q.shape[-1] == 128 and q.shape[1] <= k.shape[1]:
         B, T, H, D = q.shape
         y = torch.empty(B, T, H, D, dtype=BF16, device=q.device)
         lse = torch.empty(B, H, T, dtype=torch.float32, device=q.device)
-        _C.attn_fwd(q, k, v, y, lse, window if 0 <= window < k.shape[1] else -1, 1.0 / math.sqrt(D))
+        _C.attn_fwd(q, k, v, y, lse, window if 0 <= window < k.shape[1] else -1, 1.0 / math.sqrt(D), amax_out)
         return y, lse
     return _attention_sdpa_fwd(q, k, v, window), None
 
 
-def attention_backward(dy, q, k, v, y, lse, window, dqkv_views):
-    """Writes dq, dk, dv into the given (strided) views."""
+def attention_backward(dy, q, k, v, y, lse, window, dqkv_views, amax_dv=None):
+    """Writes dq, dk, dv into the given (strided) views. `amax_dv`: zeroed device scalar that receives max|dv|
+    on the native kernel path (returns True when it was filled)."""
     dq_v, dk_v, dv_v = dqkv_views
     if ATTENTION_IMPL == "native" and lse is not None:
         B, T, H, D = q.shape
         delta = torch.empty(B, H, T, dtype=torch.float32, device=q.device)
         _C.attn_bwd(q, k, v, y, lse, dy, dq_v, dk_v, dv_v, delta,
-                    window if 0 <= window < k.shape[1] else -1, 1.0 / math.sqrt(D))
-        return
+                    window if 0 <= window < k.shape[1] else -1, 1.0 / math.sqrt(D), amax_dv)
+        return amax_dv is not None
     with torch.enable_grad():
         q_ = q.detach().requires_grad_(True)
         k_ = k.detach().requires_grad_(True)
@@ -511,7 +513,10 @@ class _LayerFn(Function):
         q = qkv[:, :nq].view(B, T, n_head, D)
         k = qkv[:, nq:nq + nkv].view(B, T, n_kv_head, D)
         v = qkv[:, nq + nkv:].view(B, T, n_kv_head, D)
-        y, lse = attention_forward(q, k, v, window)
+        amax_y = _zeroed_scalar(dev) if fp8 else None
+        y, lse = attention_forward(q, k, v, window, amax_y)
+        if lse is None:
+            amax_y = None            # fallback attention path: the scalar was not filled
         y2 = y.reshape(M, nq)
 
         xa = torch.empty(M, C, dtype=BF16, device=dev)
@@ -519,7 +524,7 @@ class _LayerFn(Function):
         h = torch.empty(M, wfc.shape[0], dtype=BF16, device=dev)
         xo = torch.empty(M, C, dtype=BF16, device=dev)
         if fp8:
-            yq8, sy = quantize(y2)
+            yq8, sy = quantize(y2, amax=amax_y)
             w8, sw = fp8_weight(shadow_of(wo))
             gemm(yq8, w8, xa, aux=xm, beta=1.0, scale_a=sy, scale_b=sw)
             amax_xn2 = _zeroed_scalar(dev)
@@ -604,7 +609,12 @@ class _LayerFn(Function):
         v = qkv[:, nq + nkv:].view(B, T, n_kv_head, D)
         views = (dqkv[:, :nq].view(B, T, n_head, D), dqkv[:, nq:nq + nkv].view(B, T, n_kv_head, D),
                  dqkv[:, nq + nkv:].view(B, T, n_kv_head, D))
-        attention_backward(dy.view(B, T, n_head, D), q, k, v, y2.view(B, T, n_head, D), lse, window, views)
+        # max|dqkv| for the fp8 scale: dV from the attention kernel, dQ/dK from the rotary/norm backward below
+        amax_dqkv = _zeroed_scalar(dev) if f8 is not None else None
+        filled = attention_backward(dy.view(B, T, n_head, D), q, k, v, y2.view(B, T, n_head, D), lse, window, views,
+                                    amax_dqkv)
+        if not filled:
+            amax_dqkv = None
 
         # ---- rotary / QK-norm / VE gate
         dgate_x = None
@@ -612,10 +622,10 @@ class _LayerFn(Function):
             dgate_x = torch.empty(M, 12, dtype=torch.float32, device=dev)
             wg32 = wgate.detach().float().contiguous()
             _C.qkv_post_bwd(dqkv, qkv, n_head, n_kv_head, cos2, sin2, T, rstd, xn, wg32, ve_w, idx,
-                            _grad_buffer(ve_w), _grad_buffer(wgate), dgate_x)
+                            _grad_buffer(ve_w), _grad_buffer(wgate), dgate_x, amax_dqkv)
         else:
             _C.qkv_post_bwd(dqkv, qkv, n_head, n_kv_head, cos2, sin2, T, rstd, None, None, None, None,
-                            None, None, None)
+                            None, None, None, amax_dqkv)
 
         # ---- QKV projections
         dxn = dy  # reuse again
@@ -623,7 +633,7 @@ class _LayerFn(Function):
         fused_w = _contiguous_rows([sq, sk, sv])
         d8 = None
         if f8 is not None:
-            d8, sd = quantize(dqkv, E5M2)
+            d8, sd = quantize(dqkv, E5M2, amax=amax_dqkv)
             w8, sw = fp8_weight(fused_w)
             gemm(d8, w8, dxn, b_mn=True, scale_a=sd, scale_b=sw)
         elif fused_w is not None:

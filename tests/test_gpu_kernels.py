@@ -346,14 +346,20 @@ def test_flash_attention_backward(nat, B, T, H, Hkv, window):
     y = torch.empty(B, T, H, D, dtype=BF16, device="cuda")
     lse = torch.empty(B, H, T, dtype=torch.float32, device="cuda")
     scale = 1.0 / math.sqrt(D)
-    nat._C.attn_fwd(q, k, v, y, lse, window, scale)
+    amax_y = torch.zeros(1, device="cuda")
+    nat._C.attn_fwd(q, k, v, y, lse, window, scale, amax_y)
+    true_max = y.float().abs().max().item()
+    assert true_max <= amax_y.item() <= 1.01 * true_max, (true_max, amax_y.item())      # the fp8 scale's input
     dqkv = torch.zeros_like(qkv)
     dq = dqkv[..., :H * D].view(B, T, H, D)
     dk = dqkv[..., H * D:(H + Hkv) * D].view(B, T, Hkv, D)
     dv = dqkv[..., (H + Hkv) * D:].view(B, T, Hkv, D)
     delta = torch.empty(B, H, T, dtype=torch.float32, device="cuda")
-    nat._C.attn_bwd(q, k, v, y, lse, dy, dq, dk, dv, delta, window, scale)
+    amax_dv = torch.zeros(1, device="cuda")
+    nat._C.attn_bwd(q, k, v, y, lse, dy, dq, dk, dv, delta, window, scale, amax_dv)
     nat.check_status(y)
+    true_max = dv.float().abs().max().item()
+    assert true_max <= amax_dv.item() <= 1.01 * true_max, (true_max, amax_dv.item())
     qf, kf, vf = (t.float().detach().requires_grad_(True) for t in (q, k, v))
     ref = R.attention(qf, kf, vf, window)
     ref.backward(dy.float())
