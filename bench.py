@@ -219,6 +219,35 @@ def run_ours(args):
                "ms_per_step": e2e_ms / args.steps,
                "h2d_bytes_per_step": accum * 2 * B * T * 8, "d2h_bytes_per_step": 4,
                "last_loss": last_loss[0]}
+    # The optimizer step on its own (sharded Muon + AdamW with its gradient reduction and parameter write-back),
+    # against the roofline of that step: the slower of its Newton-Schulz FLOPs at the measured GEMM rate and
+    # its bytes over NVLink at the measured per-direction peer bandwidth.
+    opt = None
+    if world > 1:
+        reps = 3
+        trainer.optimizer.step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            trainer.optimizer.step()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / reps], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        n_all = sum(p.numel() for p in model.parameters())
+        ns_flops = 0.0
+        for p in model.transformer.h.parameters():
+            if p.dim() == 2 and min(p.shape) >= 8:
+                n, m = min(p.shape), max(p.shape)
+                ns_flops += 5 * (2.0 * n * n * m + 2.0 * n ** 3 + 2.0 * n * n * m)
+        bytes_in = (world - 1) / world * n_all * 4          # fp32 gradient slices pulled from the peers
+        bytes_out = (world - 1) / world * n_all * 2         # bf16 parameters stored to the peers
+        link_ms = max(bytes_in, bytes_out) / 770e9 * 1e3    # measured peer copy: 770 GB/s per direction
+        flop_ms = ns_flops / world / 1405e12 * 1e3          # measured sustained bf16 GEMM rate
+        opt = {"ms": t.item(), "roofline_ms": max(link_ms, flop_ms), "link_ms": link_ms, "newton_schulz_ms": flop_ms,
+               "fraction_of_roofline": max(link_ms, flop_ms) / t.item()}
     tok_s = args.total_batch_size * args.steps / (ms / 1e3)
     peak_mem = torch.cuda.max_memory_allocated() / 2**30
     out = {
@@ -233,6 +262,7 @@ def run_ours(args):
                    "attention": nat.ATTENTION_IMPL},
         "mfu_bf16_nominal": flops_per_token * tok_s / (world * 2.25e15),
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "peak_mem_gib": peak_mem,
+        "optimizer_step": opt,
     }
     if rank == 0:
         print(json.dumps(out))
