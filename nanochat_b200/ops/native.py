@@ -221,17 +221,58 @@ def _rows(x):
     return x2 if x2.stride(-1) == 1 else x2.contiguous()
 
 
+# Weight-gradient GEMMs are off the critical path of the backward pass (nothing reads them before the optimizer),
+# so they are issued on a side stream: they overlap with the memory-bound kernels of the main chain (quantisation,
+# norms, rotary backward), which leave the tensor cores idle. `sync_wgrad_stream()` joins the streams; the
+# embedding backward (the last node of a backward pass) and the optimizer call it.
+_WGRAD_ASYNC = _os.environ.get("NANOCHAT_WGRAD_STREAM", "1") != "0"
+_wgrad_streams = {}
+_wgrad_pending = set()
+
+
+def _wgrad_stream(device):
+    s = _wgrad_streams.get(device)
+    if s is None:
+        s = torch.cuda.Stream(device=device)
+        _wgrad_streams[device] = s
+    return s
+
+
+def sync_wgrad_stream(device=None):
+    """Make the current stream wait for every weight-gradient GEMM issued so far."""
+    for dev in list(_wgrad_pending) if device is None else [device]:
+        if dev in _wgrad_pending:
+            torch.cuda.current_stream(dev).wait_stream(_wgrad_streams[dev])
+            _wgrad_pending.discard(dev)
+
+
+def _wgrad_gemm(A, B, out, **kw):
+    """gemm(A, B, out, ...) on the weight-gradient stream, ordered after everything issued so far on the current one."""
+    dev = out.device
+    if not _WGRAD_ASYNC or torch.cuda.is_current_stream_capturing():
+        return gemm(A, B, out, **kw)
+    side = _wgrad_stream(dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        gemm(A, B, out, **kw)
+    for t in (A, B, kw.get("scale_a"), kw.get("scale_b")):
+        if t is not None:
+            t.record_stream(side)          # the allocator must not hand these blocks out before the GEMM has read them
+    _wgrad_pending.add(dev)
+    return out
+
+
 def _accumulate_wgrad(w, dy2, x2, scale_a=None, scale_b=None):
     """w.grad (fp32) += dy2^T @ x2, fused in the GEMM epilogue (bf16 operands, or fp8 with their scales)."""
     kw = dict(a_mn=True, b_mn=True, scale_a=scale_a, scale_b=scale_b)
     if w.grad is None:
         w.grad = torch.empty_like(w, dtype=w.dtype)
-        gemm(dy2, x2, w.grad, **kw)
+        _wgrad_gemm(dy2, x2, w.grad, **kw)
     elif getattr(w, "_grad_fresh", False):      # persistent arena buffer, first write of this step
-        gemm(dy2, x2, w.grad, **kw)
+        _wgrad_gemm(dy2, x2, w.grad, **kw)
         w._grad_fresh = False
     else:
-        gemm(dy2, x2, w.grad, aux=w.grad, beta=1.0, **kw)
+        _wgrad_gemm(dy2, x2, w.grad, aux=w.grad, beta=1.0, **kw)
 
 
 def _grad_buffer(p, dtype=torch.float32):
@@ -272,6 +313,7 @@ class _LinearFn(Function):
             dx = dx.view(*dy.shape[:-1], x2.shape[-1])
         if w.requires_grad:
             _accumulate_wgrad(w, dy2, x2)
+            sync_wgrad_stream(dy2.device)    # op-level path: no later node is known to join the streams
         return dx, None, None
 
 
@@ -445,6 +487,7 @@ class _EmbedFn(Function):
     @staticmethod
     def backward(ctx, dx, _dlast=None):
         idx, wte, gate_w, lam = ctx.saved_tensors
+        sync_wgrad_stream(dx.device)        # last node of the backward pass: every gradient is complete after it
         dwte = _grad_buffer(wte)
         dgate = _grad_buffer(gate_w)
         dlam = _grad_buffer(lam)
@@ -651,10 +694,10 @@ class _LayerFn(Function):
             wa, wb = (d8, xq8) if d8 is not None else (dqkv, xn)
             kw = dict(a_mn=True, b_mn=True, scale_a=sd, scale_b=sx) if d8 is not None else dict(a_mn=True, b_mn=True)
             if fresh[0]:
-                gemm(wa, wb, fused_g, **kw)
+                _wgrad_gemm(wa, wb, fused_g, **kw)
                 wq._grad_fresh = wk._grad_fresh = wv._grad_fresh = False
             else:
-                gemm(wa, wb, fused_g, aux=fused_g, beta=1.0, **kw)
+                _wgrad_gemm(wa, wb, fused_g, aux=fused_g, beta=1.0, **kw)
         else:
             _accumulate_wgrad(wq, dqkv[:, :nq], xn)
             _accumulate_wgrad(wk, dqkv[:, nq:nq + nkv], xn)

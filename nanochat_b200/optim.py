@@ -183,6 +183,8 @@ class MuonAdamW(torch.optim.Optimizer):
     # ------------------------------------------------------------- step
     @torch.no_grad()
     def step(self):
+        if torch.cuda.is_available() and ops.get_kernel_mode() == "native":
+            ops.native_module().sync_wgrad_stream()     # weight gradients are produced on a side stream
         comm = self.comm if self.comm is not None else default_comm()
         if getattr(comm, "fused", False):
             return comm.fused_step(self)
