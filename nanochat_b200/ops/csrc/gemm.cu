@@ -488,6 +488,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 // ----------------------------------------------------------------------------- host
 
+// M-blocks per group of the tile order (tiles of one group run back to back so their B tiles stay in L2);
+// NANOCHAT_GEMM_GROUP_M overrides the default for tuning.
+static int group_m_override(int dflt) {
+  static const int env = [] { const char* e = getenv("NANOCHAT_GEMM_GROUP_M"); return e ? atoi(e) : 0; }();
+  return env > 0 ? env : dflt;
+}
+
 template <int BN, bool A_MN, bool B_MN, bool FP8>
 static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t stream) {
   using C = Cfg<BN, A_MN, B_MN, FP8>;
@@ -529,7 +536,7 @@ static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t strea
   a.scale_a = d.scale_a; a.scale_b = d.scale_b; a.amax_out = d.amax_out;
   a.m_blocks = (d.M + BM - 1) / BM;
   a.n_blocks = (d.N + BN - 1) / BN;
-  a.group_m = 16;
+  a.group_m = group_m_override(16);
   a.idesc = FP8 ? umma_idesc_f8(BM, BN, A_MN, B_MN, d.a_e5m2, d.b_e5m2) : umma_idesc_bf16(BM, BN, A_MN, B_MN);
   a.status = status;
   const long long tiles = 1ll * a.m_blocks * a.n_blocks * d.batch;
@@ -591,7 +598,7 @@ static cudaError_t launch_pair_cfg(const GemmDesc& d, int* status, cudaStream_t 
   a.scale_a = d.scale_a; a.scale_b = d.scale_b; a.amax_out = d.amax_out;
   a.m_blocks = (d.M + 2 * BM - 1) / (2 * BM);
   a.n_blocks = (d.N + BN - 1) / BN;
-  a.group_m = 8;
+  a.group_m = group_m_override(8);
   a.idesc = FP8 ? umma_idesc_f8(2 * BM, BN, A_MN, B_MN, d.a_e5m2, d.b_e5m2) : umma_idesc_bf16(2 * BM, BN, A_MN, B_MN);
   a.status = status;
   const long long tiles = 1ll * a.m_blocks * a.n_blocks * d.batch;
