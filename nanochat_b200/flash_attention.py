@@ -19,7 +19,6 @@ Two bodies:
 
 from types import SimpleNamespace
 
-import torch
 
 from nanochat_b200 import ops
 from nanochat_b200.ops import reference as ref_ops

@@ -13,7 +13,6 @@ the fraction of that rate.
 """
 import argparse
 import json
-import math
 import os
 
 import torch

@@ -10,7 +10,6 @@ Each op cites the reference lines whose arithmetic it reproduces
 (reference: nanochat/gpt.py unless stated otherwise).
 """
 
-import math
 
 import torch
 import torch.nn.functional as F

@@ -4,7 +4,6 @@ MuonAdamW update, gradient reset. This is the loop body of the pretraining / SFT
 (reference: scripts/base_train.py:510-540) packaged so benchmarks and scripts share it.
 """
 
-import torch
 
 
 class TrainStep:

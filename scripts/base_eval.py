@@ -16,7 +16,6 @@ import zipfile
 import tempfile
 import argparse
 
-import torch
 
 from nanochat_b200.common import (compute_init, compute_cleanup, print0, get_base_dir, autodetect_device_type,
                                   download_file_with_lock)
