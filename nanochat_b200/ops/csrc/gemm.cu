@@ -66,11 +66,12 @@ struct Cfg {
   static constexpr int B_BYTES = B_ROWS_ALLOC * ROW_BYTES;
   static constexpr int B_TX = B_MN ? B_CHUNKS * CHUNK_BYTES : BN * ROW_BYTES;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int MAX_STAGES = (227 * 1024 - 2048) / STAGE_BYTES;
+  static constexpr int EPI_BYTES = 8 * 32 * 128;   // staging tiles of the eight epilogue warps
+  static constexpr int MAX_STAGES = (227 * 1024 - 2048 - EPI_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
   static constexpr int ACC_STRIDE = next_pow2_cols(BN);
   static constexpr int TMEM_COLS = 2 * ACC_STRIDE;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/ + EPI_BYTES;
   static_assert(!B_MN || B_CHUNKS * CHUNK_BYTES <= B_BYTES, "MN-major B boxes must fit the stage");
 };
 
@@ -161,6 +162,92 @@ __device__ __forceinline__ void store_tile_row(const GemmKernelArgs& args, uint3
   }
 }
 
+// bf16 epilogue through a per-warp staging tile in shared memory. A thread owns one accumulator row, so storing it
+// directly makes every warp-wide store touch 32 different rows (32 partial sectors per instruction), and for short
+// reductions that store traffic, not the tensor core, sets the tile time. Here the warp converts 64 columns of its 32
+// rows at a time into a 32 x 128 B tile (16-byte units XOR-swizzled by row, so the row-wise writes and the
+// 4-rows-per-instruction reads are both conflict free) and writes it out as whole 128-byte lines. The auxiliary operand
+// (residual, relu^2 derivative input) comes in the same way, through the same tile.
+constexpr int EPI_STAGE_BYTES = 32 * 128;          // per epilogue warp
+
+template <int BN>
+__device__ __forceinline__ void store_tile_bf16_staged(const GemmKernelArgs& args, uint32_t taddr, int b, int row0, int n0,
+                                                       float alpha, float beta, float& amax, int c_begin, int c_end,
+                                                       uint8_t* stage, int lane) {
+  __nv_bfloat16* cbase = reinterpret_cast<__nv_bfloat16*>(args.C) + b * args.bsc;
+  const __nv_bfloat16* xbase = args.aux ? reinterpret_cast<const __nv_bfloat16*>(args.aux) + b * args.bsaux : nullptr;
+  const bool use_aux = xbase != nullptr && args.epi != EPI_RELU2;
+  const int sub_r = lane >> 3, unit = lane & 7;     // coalesced phase: 4 rows x 8 units (16 B) per instruction
+#pragma unroll 1
+  for (int g = c_begin; g < c_end; g += 4) {
+    const int nch = min(4, c_end - g);              // 16-column chunks in this group
+    const int col0 = n0 + g * 16;
+    if (use_aux) {
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int r = it * 4 + sub_r;
+        const int col = col0 + unit * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row0 + r < args.M && unit < nch * 2 && col + 8 <= args.N)
+          v = *reinterpret_cast<const uint4*>(xbase + static_cast<long long>(row0 + r) * args.ldaux + col);
+        *reinterpret_cast<uint4*>(stage + r * 128 + ((unit ^ (r & 7)) << 4)) = v;
+      }
+      __syncwarp();
+    }
+    uint32_t acc[4][16];
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc)
+      if (cc < nch) tmem_ld16(taddr + (g + cc) * 16, acc[cc]);
+    tmem_wait_ld();
+#pragma unroll
+    for (int cc = 0; cc < 4; ++cc) {
+      if (cc < nch) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float vv[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) vv[j] = __uint_as_float(acc[cc][h * 8 + j]) * alpha;
+          uint8_t* slot = stage + lane * 128 + (((cc * 2 + h) ^ (lane & 7)) << 4);
+          if (args.epi == EPI_RELU2) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { const float tpos = fmaxf(vv[j], 0.f); vv[j] = tpos * tpos; }
+          } else if (use_aux) {
+            const uint4 xa = *reinterpret_cast<const uint4*>(slot);
+            const uint32_t xs[4] = {xa.x, xa.y, xa.z, xa.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack_bf16(xs[j]);
+              if (args.epi == EPI_MUL2SQRT) {
+                vv[2 * j] *= 2.f * sqrtf(f.x);
+                vv[2 * j + 1] *= 2.f * sqrtf(f.y);
+              } else {
+                vv[2 * j] += beta * f.x;
+                vv[2 * j + 1] += beta * f.y;
+              }
+            }
+          }
+          if (row0 + lane < args.M && col0 + (cc * 2 + h) * 8 + 8 <= args.N) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(vv[j]));
+          }
+          *reinterpret_cast<uint4*>(slot) = make_uint4(pack_bf16(vv[0], vv[1]), pack_bf16(vv[2], vv[3]),
+                                                       pack_bf16(vv[4], vv[5]), pack_bf16(vv[6], vv[7]));
+        }
+      }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int r = it * 4 + sub_r;
+      const int col = col0 + unit * 8;
+      if (row0 + r < args.M && unit < nch * 2 && col + 8 <= args.N)
+        *reinterpret_cast<uint4*>(cbase + static_cast<long long>(row0 + r) * args.ldc + col) =
+            *reinterpret_cast<const uint4*>(stage + r * 128 + ((unit ^ (r & 7)) << 4));
+    }
+    __syncwarp();                                   // the tile is reused by the next group
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN, bool FP8>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -176,6 +263,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES + 512;      // 8 x 4 KB, 128-byte aligned
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -277,7 +365,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int row = mb * BM + quad * 32 + lane;
       const int n0 = nb * BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC_STRIDE;
-      store_tile_row<BN>(args, taddr, b, row, n0, alpha, beta, amax, c_begin, c_end);
+      if (args.c_f32)
+        store_tile_row<BN>(args, taddr, b, row, n0, alpha, beta, amax, c_begin, c_end);
+      else
+        store_tile_bf16_staged<BN>(args, taddr, b, mb * BM + quad * 32, n0, alpha, beta, amax, c_begin, c_end,
+                                   epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -329,11 +421,12 @@ struct PairCfg {
   static constexpr int B_TX = B_MN ? B_CHUNKS * CHUNK_BYTES : BNH * ROW_BYTES;
   static constexpr int B_BYTES = (B_TX + 1023) / 1024 * 1024;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int MAX_STAGES = (227 * 1024 - 2048) / STAGE_BYTES;
+  static constexpr int EPI_BYTES = Base::EPI_BYTES;
+  static constexpr int MAX_STAGES = (227 * 1024 - 2048 - EPI_BYTES) / STAGE_BYTES;
   static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
   static constexpr int ACC_STRIDE = next_pow2_cols(BN);
   static constexpr int TMEM_COLS = 2 * ACC_STRIDE;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/ + EPI_BYTES;
   static_assert(BN % 32 == 0 || BN == 208, "pair tiles: N/2 must stay a multiple of 8");
 };
 
@@ -352,6 +445,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES + 512;      // 8 x 4 KB, 128-byte aligned
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -459,7 +553,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int row = mb * (2 * BM) + rank * BM + quad * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC_STRIDE;
-      store_tile_row<BN>(args, taddr, b, row, nb * BN, alpha, beta, amax, c_begin, c_end);
+      if (args.c_f32)
+        store_tile_row<BN>(args, taddr, b, row, nb * BN, alpha, beta, amax, c_begin, c_end);
+      else
+        store_tile_bf16_staged<BN>(args, taddr, b, mb * (2 * BM) + rank * BM + quad * 32, nb * BN, alpha, beta, amax,
+                                   c_begin, c_end, epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
