@@ -1,0 +1,65 @@
+"""
+The whole pipeline on CPU at toy size, through the entry points a user runs: synthetic corpus shards -> tokenizer
+training -> pretraining (with validation bpb and a checkpoint) -> resume from that checkpoint -> base evaluation ->
+one-shot chat -> SFT on synthetic conversations. Every stage is a subprocess with its own interpreter, as in the
+run scripts.
+"""
+import os
+import random
+import re
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.slow
+
+
+def _run(base_dir, *args, timeout=600):
+    env = dict(os.environ, NANOCHAT_BASE_DIR=base_dir, OMP_NUM_THREADS="4", WANDB_MODE="disabled")
+    r = subprocess.run([sys.executable, "-m", *args], cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0, (args, r.stdout[-1500:], r.stderr[-3000:])
+    return r.stdout + r.stderr
+
+
+def test_toy_pipeline_end_to_end(tmp_path):
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+    base = str(tmp_path / "nanochat")
+    data = os.path.join(base, "base_data_climbmix")
+    os.makedirs(data)
+    rnd = random.Random(0)
+    words = ("the quick brown fox jumps over lazy dog and then runs far away from home while it rains hard on every "
+             "street of town").split()
+    for i in range(3):                                       # the last shard is the validation split
+        docs = [" ".join(rnd.choice(words) for _ in range(rnd.randint(30, 200))) + "." for _ in range(600)]
+        pq.write_table(pa.table({"text": docs}), os.path.join(data, f"shard_{i:05d}.parquet"), row_group_size=100)
+
+    out = _run(base, "scripts.tok_train", "--max-chars=300000", "--vocab-size=512")
+    assert os.path.exists(os.path.join(base, "tokenizer", "tokenizer.pkl"))
+    assert os.path.exists(os.path.join(base, "tokenizer", "token_bytes.pt"))
+
+    train_args = ["scripts.base_train", "--depth=2", "--head-dim=64", "--window-pattern=L", "--max-seq-len=64",
+                  "--device-batch-size=4", "--total-batch-size=512", "--eval-tokens=1024", "--core-metric-every=-1",
+                  "--sample-every=-1", "--device-type=cpu"]
+    out = _run(base, *train_args, "--num-iterations=4", "--eval-every=2")
+    bpbs = [float(x) for x in re.findall(r"Validation bpb: ([0-9.]+)", out)]
+    assert len(bpbs) == 3 and bpbs[-1] < bpbs[0], bpbs       # it learns, even in four steps
+    ck = os.path.join(base, "base_checkpoints", "d2")
+    assert sorted(os.listdir(ck)) == ["meta_000004.json", "model_000004.pt", "optim_000004_rank0.pt"]
+
+    out = _run(base, *train_args, "--num-iterations=6", "--eval-every=-1", "--resume-from-step=4")
+    assert "Resuming optimization from step 4" in out and "step 00005/00006" in out and "step 00003/" not in out
+
+    out = _run(base, "scripts.base_eval", "--eval", "bpb,sample", "--device-batch-size=2", "--split-tokens=1024",
+               "--device-type=cpu")
+    assert re.search(r"val bpb: [0-9.]+", out)
+
+    out = _run(base, "scripts.chat_cli", "-i", "base", "-p", "the quick", "-t", "0.0", "--device-type=cpu")
+    assert "Assistant:" in out
+
+    out = _run(base, "scripts.chat_sft", "--synthetic-data", "--depth=2", "--num-iterations=3", "--max-seq-len=64",
+               "--device-batch-size=2", "--total-batch-size=256", "--eval-every=-1", "--chatcore-every=-1",
+               "--device-type=cpu")
+    assert re.search(r"step 0000\d .*loss: [0-9.]+", out)
