@@ -332,6 +332,21 @@ def test_flash_attention_forward(nat, B, T, H, Hkv, window):
     assert (lse - torch.logsumexp(s, dim=-1)).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("Tq,Tk,window", [(128, 384, -1), (1, 300, -1), (72, 1000, 256), (300, 556, 128)])
+def test_flash_attention_forward_queries_at_the_end_of_longer_keys(nat, Tq, Tk, window):
+    """Chunked inference: Tq new queries attend to Tk cached keys, aligned to their end."""
+    from nanochat_b200.ops import reference as R
+    B, H, Hkv, D = 2, 4, 2, 128
+    q = _mk((B, Tq, H, D), seed=50)
+    k = _mk((B, Tk, Hkv, D), seed=51)
+    v = _mk((B, Tk, Hkv, D), seed=52)
+    y, lse = nat.attention_forward(q, k, v, window)
+    assert lse is not None
+    nat.check_status(y)
+    ref = R.attention(q.float(), k.float(), v.float(), window)
+    assert _rel_err(y, ref) < 2e-2, (Tq, Tk, window)
+
+
 @pytest.mark.parametrize("B,T,H,Hkv,window", [
     (2, 256, 2, 2, -1), (1, 512, 4, 4, 128), (2, 384, 4, 2, 256), (1, 200, 2, 1, 64), (1, 1024, 2, 2, 512),
 ])
