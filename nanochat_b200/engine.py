@@ -217,7 +217,7 @@ class Engine:
         None when the graph path does not apply or the pooled cache is busy (nested generations)."""
         cfg = self.model.config
         device = geometry["device"]
-        if (device.type != "cuda" or ops.get_kernel_mode() != "native" or rows > 8
+        if (device.type != "cuda" or ops.get_kernel_mode() != "native" or rows > 64
                 or capacity > cfg.sequence_len or geometry["head_dim"] != 128):
             return None
         cache = self._cache_pool.get(rows)

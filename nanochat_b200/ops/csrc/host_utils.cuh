@@ -28,8 +28,13 @@ inline bool make_tmap(CUtensorMap* out, CUtensorMapDataType dtype, int rank, con
                       const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
                       CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   // Driver entry points need a current context on the calling thread; autograd's worker threads have
-  // none until their first runtime call, so make the primary context current here.
-  cudaFree(nullptr);
+  // none until their first runtime call, so make the primary context current here. Once per thread: the call
+  // is not allowed while a stream capture is in progress, and a thread that captures has launched eagerly before.
+  static thread_local bool context_ready = false;
+  if (!context_ready) {
+    cudaFree(nullptr);
+    context_ready = true;
+  }
   auto enc = tensor_map_encoder();
   if (!enc) return false;
   cuuint64_t gdim[5];

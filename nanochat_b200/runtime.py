@@ -10,7 +10,7 @@ position-dependent quantity is read from device memory (`KVCache.cache_seqlens`)
 step is captured once per (engine, cache) and replayed with a single launch per token.
 
 `decode_graph_for(engine, kv_cache)` returns the `DecodeGraph` of a cache, or None when the
-fast path does not apply (CPU, kernels disabled, more than 8 rows, head dim != 128).
+fast path does not apply (CPU, kernels disabled, more than 64 rows, head dim != 128).
 """
 
 import torch
@@ -19,7 +19,8 @@ import torch.nn.functional as F
 from nanochat_b200 import common, ops
 from nanochat_b200.ops import reference as ref_ops
 
-MAX_ROWS = 8
+MAX_ROWS = 64          # rows of one decode graph; up to GEMV_ROWS of them use the weight-streaming GEMV
+GEMV_ROWS = 8
 
 
 class DecodeGraph:
@@ -46,6 +47,7 @@ class DecodeGraph:
         self.scratch = torch.zeros(self.C_.decode_attn_scratch(B, self.H), dtype=torch.float32, device=dev)
         self.cos = model.cos.reshape(-1, 64).contiguous()
         self.sin = model.sin.reshape(-1, 64).contiguous()
+        self.use_gemv = B <= GEMV_ROWS     # more rows: the tcgen05 GEMM (rows padded to a 128-row tile) inside the graph
         self.weights_epoch = None
         self.w = None
         self.graph = None
@@ -86,6 +88,18 @@ class DecodeGraph:
         self.weights_epoch = epoch
 
     # --------------------------------------------------------------------- step
+    def _linear(self, x, w, out, aux=None, relu2=False, norm_input=False):
+        """out = epi(norm?(x) @ w^T) (+ aux): GEMV for a few rows, tensor-core GEMM otherwise."""
+        if self.use_gemv:
+            self.C_.gemv_rows(x, w, out, aux, 1 if relu2 else 0, norm_input)
+            return
+        nat = self.nat
+        if norm_input:
+            self.C_.norm_fwd(x, self.xn2, None)
+            x = self.xn2
+        nat.gemm(x, w, out, aux=aux, beta=1.0 if aux is not None else 0.0,
+                 epi=nat.EPI_RELU2 if relu2 else nat.EPI_LINEAR)
+
     def _forward(self):
         m, C_ = self.model, self.C_
         B, H, Hkv = self.B, self.H, self.Hkv
@@ -103,7 +117,7 @@ class DecodeGraph:
         scale = 1.0 / (128 ** 0.5)
         for i, w in enumerate(self.w):
             C_.mixnorm_fwd(x, x0, m.resid_lambdas, m.x0_lambdas, i, self.xm, self.xn, None)
-            C_.gemv_rows(self.xn, w["qkv"], self.qkv, None, 0, False)
+            self._linear(self.xn, w["qkv"], self.qkv)
             ve = m.value_embeds[str(i)].weight if str(i) in m.value_embeds else None
             kc, vc = cache.get_layer_cache(i)
             C_.decode_qkv_post(self.qkv, H, Hkv, self.cos, self.sin, cache.cache_seqlens,
@@ -112,13 +126,13 @@ class DecodeGraph:
             window = m.window_sizes[i][0]
             window = window if 0 <= window < cache.max_seq_len else -1
             C_.decode_attn(self.qkv[:, :nq], kc, vc, cache.cache_seqlens, H, Hkv, window, scale, self.scratch, self.y)
-            C_.gemv_rows(self.y, w["o"], self.xa, self.xm, 0, False)
-            C_.gemv_rows(self.xa, w["fc"], self.h, None, 1, True)          # norm(xa) folded into the GEMV
+            self._linear(self.y, w["o"], self.xa, aux=self.xm)
+            self._linear(self.xa, w["fc"], self.h, relu2=True, norm_input=True)   # GEMV: norm(xa) folded in
             out = self.x_backout if i == backout_layer else self.xs[i & 1]
-            C_.gemv_rows(self.h, w["pr"], out, self.xa, 0, False)
+            self._linear(self.h, w["pr"], out, aux=self.xa)
             x = out
         C_.backout_norm_fwd(x, self.x_backout, m.backout_lambda.detach().float(), self.xn)
-        C_.gemv_rows(self.xn, self.lm_head, self.logits_bf16, None, 0, False)
+        self._linear(self.xn, self.lm_head, self.logits_bf16)
         C_.softcap_logits(self.logits_bf16, self.logits, m.config.vocab_size, ref_ops.SOFTCAP)
         cache.cache_seqlens.add_(1)
 

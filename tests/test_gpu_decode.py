@@ -115,6 +115,17 @@ def test_decode_graph_matches_cached_forward_and_engine_is_greedy_consistent():
     # a second generation reuses the captured graph and gives the same tokens
     again = [c for c, _ in eng.generate(prompt, num_samples=2, max_tokens=40, temperature=0.0)]
     assert again == fast
+    # more than 8 rows: the same graph with tensor-core GEMMs instead of the GEMV; every row is the same greedy sequence
+    wide = [c for c, _ in eng.generate(prompt, num_samples=12, max_tokens=24, temperature=0.0)]
+    assert any(g.graph is not None and g.B == 12 for g in eng._decode_graphs.values())
+    assert all(len(set(col)) == 1 for col in wide[:8])
+    agree = 0
+    for a, b in zip(wide, fast):
+        if a[0] != b[0]:
+            break
+        agree += 1
+    assert agree >= 8, (agree, [c[0] for c in wide[:12]], [c[0] for c in fast[:12]])
+    ops.native_module().check_status()
 
 
 def test_sampling_kernel_semantics():
