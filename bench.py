@@ -204,10 +204,13 @@ def run_ours(args):
     nat = ops.native_module()
     nat.check_status()
     launches0 = nat.launch_count()
+    trainer.timers.collect()               # NANOCHAT_TRACE=1: drop the warm-up intervals
     sampler = ClockSampler(local_rank)
     sampler.start()
     ms = timed_region(torch, dist, world, args.steps, step_device)
     clocks = sampler.stop()
+    # device time per phase and step (max over ranks); empty unless NANOCHAT_TRACE=1
+    phases = {k: v / args.steps for k, v in trainer.timers.collect().items()}
     launches = nat.launch_count() - launches0
     nat.check_status()
 
@@ -264,6 +267,8 @@ def run_ours(args):
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "peak_mem_gib": peak_mem,
         "optimizer_step": opt,
     }
+    if phases:
+        out["phases_ms_per_step"] = phases
     if rank == 0:
         print(json.dumps(out))
     common.compute_cleanup()

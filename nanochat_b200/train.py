@@ -4,11 +4,15 @@ MuonAdamW update, gradient reset. This is the loop body of the pretraining / SFT
 (reference: scripts/base_train.py:510-540) packaged so benchmarks and scripts share it.
 """
 
+from nanochat_b200.utils.trace import PhaseTimers
 
 
 class TrainStep:
-    def __init__(self, model, grad_accum=1, comm=None, optimizer=None, use_arena=None, **optimizer_kwargs):
+    def __init__(self, model, grad_accum=1, comm=None, optimizer=None, use_arena=None, timers=None,
+                 **optimizer_kwargs):
         self.model = model
+        # phase timers are inert (no events, no extra launches) unless NANOCHAT_TRACE=1 or one is passed in
+        self.timers = timers if timers is not None else PhaseTimers(device_type=model.get_device().type)
         if use_arena is None:
             use_arena = model.get_device().type == "cuda"
         if use_arena and getattr(model, "_arena", None) is None:
@@ -24,9 +28,12 @@ class TrainStep:
         loss = None
         for i in range(self.grad_accum):
             x, y = fetch(i)
-            loss = self.model(x, y)
-            (loss * scale).backward()
-        self.optimizer.step()
+            with self.timers.phase("forward"):
+                loss = self.model(x, y)
+            with self.timers.phase("backward"):
+                (loss * scale).backward()
+        with self.timers.phase("optimizer"):
+            self.optimizer.step()
         arena = getattr(self.model, "_arena", None)
         if arena is not None:
             arena.zero_grads()      # persistent gradient buffers: re-arm "first write overwrites"

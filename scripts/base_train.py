@@ -33,6 +33,7 @@ from nanochat_b200 import schedules
 from nanochat_b200.checkpoint_manager import save_checkpoint, load_checkpoint
 from nanochat_b200.loss_eval import evaluate_bpb
 from nanochat_b200.engine import Engine
+from nanochat_b200.utils.trace import MetricsLog, PhaseTimers
 
 print_banner()
 
@@ -66,6 +67,9 @@ parser.add_argument("--core-metric-every", type=int, default=2000)
 parser.add_argument("--core-metric-max-per-task", type=int, default=500)
 parser.add_argument("--sample-every", type=int, default=2000)
 parser.add_argument("--save-every", type=int, default=-1)
+parser.add_argument("--log-every", type=int, default=100, help="steps between metric records (wandb and the metrics file)")
+parser.add_argument("--metrics-file", type=str, default=None,
+                    help="JSONL metrics file (default: <base_dir>/metrics/base_train_<model tag>.jsonl; '' disables)")
 parser.add_argument("--model-tag", type=str, default=None)
 # additions of this framework
 parser.add_argument("--synthetic-data", action="store_true", help="uniform-random tokens instead of the corpus")
@@ -124,6 +128,13 @@ model.init_weights()
 
 base_dir = get_base_dir()
 checkpoint_dir = os.path.join(base_dir, "base_checkpoints", args.model_tag if args.model_tag else f"d{args.depth}")
+# every metric record also goes to a JSONL file on the master rank (one object per line, flushed per line)
+metrics_path = args.metrics_file
+if metrics_path is None:
+    metrics_path = os.path.join(base_dir, "metrics", f"base_train_{args.model_tag if args.model_tag else f'd{args.depth}'}.jsonl")
+wandb_run = MetricsLog(metrics_path if (master_process and metrics_path) else None, forward_to=wandb_run,
+                       header={"script": "base_train", "config": user_config, "world_size": ddp_world_size})
+timers = PhaseTimers(device_type=device_type)
 resuming = args.resume_from_step != -1
 if resuming:
     print0(f"Resuming optimization from step {args.resume_from_step}")
@@ -303,13 +314,15 @@ while True:
     synchronize()
     t0 = time.time()
     for micro_step in range(grad_accum_steps):
-        loss = model(x, y)
+        with timers.phase("forward"):
+            loss = model(x, y)
         train_loss = loss.detach()
         loss = loss / grad_accum_steps
-        if scaler is not None:
-            scaler.scale(loss).backward()
-        else:
-            loss.backward()
+        with timers.phase("backward"):
+            if scaler is not None:
+                scaler.scale(loss).backward()
+            else:
+                loss.backward()
         x, y, dataloader_state_dict = next(train_loader)   # host-side packing overlaps the GPU work
     lrm = schedules.pretrain_lr_multiplier(step, num_iterations, args.warmup_steps, args.warmdown_ratio,
                                            args.final_lr_frac)
@@ -328,11 +341,13 @@ while True:
         scaler.step(optimizer)
         scaler.update()
     else:
-        optimizer.step()
+        with timers.phase("optimizer"):
+            optimizer.step()
     model.zero_grad(set_to_none=True)
     train_loss_f = train_loss.item()
     synchronize()
     dt = time.time() - t0
+    phase_ms = timers.collect()            # {} unless NANOCHAT_TRACE=1; device time per phase, max over ranks
 
     ema_beta = 0.9
     smooth_train_loss = ema_beta * smooth_train_loss + (1 - ema_beta) * train_loss_f
@@ -350,11 +365,13 @@ while True:
     print0(f"step {step:05d}/{num_iterations:05d} ({pct_done:.2f}%) | loss: {debiased_smooth_loss:.6f} | lrm: {lrm:.2f} | "
            f"dt: {dt * 1000:.2f}ms | tok/sec: {tok_per_sec:,} | bf16_mfu: {mfu:.2f} | epoch: {epoch} | "
            f"total time: {total_training_time/60:.2f}m{eta_str}")
-    if step % 100 == 0:
+    if phase_ms:
+        print0("    phases (device ms, max over ranks): " + " | ".join(f"{k}: {v:.2f}" for k, v in phase_ms.items()))
+    if step % args.log_every == 0:
         wandb_run.log({"step": step, "total_training_flops": flops_so_far,
                        "total_training_time": total_training_time, "train/loss": debiased_smooth_loss,
                        "train/lrm": lrm, "train/dt": dt, "train/tok_per_sec": tok_per_sec, "train/mfu": mfu,
-                       "train/epoch": epoch})
+                       "train/epoch": epoch, **{f"train/{k}_ms": v for k, v in phase_ms.items()}})
 
     first_step_of_run = (step == 0) or (resuming and step == args.resume_from_step)
     step += 1

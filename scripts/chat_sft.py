@@ -45,6 +45,8 @@ parser.add_argument("--warmup-ratio", type=float, default=0.0)
 parser.add_argument("--warmdown-ratio", type=float, default=0.5)
 parser.add_argument("--final-lr-frac", type=float, default=0.0)
 parser.add_argument("--eval-every", type=int, default=200)
+parser.add_argument("--metrics-file", type=str, default=None,
+                    help="JSONL metrics file (default: <base_dir>/metrics/chat_sft.jsonl; '' disables)")
 parser.add_argument("--eval-tokens", type=int, default=40 * 524288)
 parser.add_argument("--chatcore-every", type=int, default=200)
 parser.add_argument("--chatcore-max-cat", type=int, default=-1)
@@ -68,6 +70,11 @@ if args.run == "dummy" or not master_process:
 else:
     import wandb
     wandb_run = wandb.init(project="nanochat-sft", name=args.run, config=user_config)
+# metric records also go to a JSONL file on the master rank
+from nanochat_b200.utils.trace import MetricsLog
+metrics_path = os.path.join(get_base_dir(), "metrics", "chat_sft.jsonl") if args.metrics_file is None else args.metrics_file
+wandb_run = MetricsLog(metrics_path if (master_process and metrics_path) else None, forward_to=wandb_run,
+                       header={"script": "chat_sft", "config": user_config, "world_size": ddp_world_size})
 
 if args.synthetic_data:
     from nanochat_b200.models.gpt import GPT, GPTConfig

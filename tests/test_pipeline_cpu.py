@@ -16,8 +16,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 pytestmark = pytest.mark.slow
 
 
-def _run(base_dir, *args, timeout=600):
+def _run(base_dir, *args, timeout=600, extra_env=None):
     env = dict(os.environ, NANOCHAT_BASE_DIR=base_dir, OMP_NUM_THREADS="4", WANDB_MODE="disabled")
+    env.update(extra_env or {})
     r = subprocess.run([sys.executable, "-m", *args], cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
     assert r.returncode == 0, (args, r.stdout[-1500:], r.stderr[-3000:])
     return r.stdout + r.stderr
@@ -43,9 +44,17 @@ def test_toy_pipeline_end_to_end(tmp_path):
     train_args = ["scripts.base_train", "--depth=2", "--head-dim=64", "--window-pattern=L", "--max-seq-len=64",
                   "--device-batch-size=4", "--total-batch-size=512", "--eval-tokens=1024", "--core-metric-every=-1",
                   "--sample-every=-1", "--device-type=cpu"]
-    out = _run(base, *train_args, "--num-iterations=4", "--eval-every=2")
+    out = _run(base, *train_args, "--num-iterations=4", "--eval-every=2", "--log-every=2",
+               extra_env={"NANOCHAT_TRACE": "1"})
     bpbs = [float(x) for x in re.findall(r"Validation bpb: ([0-9.]+)", out)]
     assert len(bpbs) == 3 and bpbs[-1] < bpbs[0], bpbs       # it learns, even in four steps
+    assert re.search(r"phases \(device ms, max over ranks\): forward: [0-9.]+ \| backward: [0-9.]+ \| optimizer:", out)
+    from nanochat_b200.utils.trace import read_metrics
+    recs = read_metrics(os.path.join(base, "metrics", "base_train_d2.jsonl"))
+    assert recs[0]["event"] == "run_start" and recs[0]["config"]["depth"] == 2
+    train = [r for r in recs if "train/loss" in r]
+    assert [r["step"] for r in train] == [0, 2] and all(r["train/forward_ms"] > 0 for r in train)
+    assert any("val/bpb" in r for r in recs)
     ck = os.path.join(base, "base_checkpoints", "d2")
     assert sorted(os.listdir(ck)) == ["meta_000004.json", "model_000004.pt", "optim_000004_rank0.pt"]
 
