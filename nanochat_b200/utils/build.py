@@ -134,10 +134,17 @@ def load_cuda_extension():
 
 # -------------------------------------------------------------------------- tokenizer
 
-def build_tokenizer_extension(force=False):
+def build_tokenizer_extension(force=False, sanitize=False):
+    """Build `_tok`. `sanitize=True` builds a second copy under `_build/sanitize/` with AddressSanitizer and
+    UndefinedBehaviorSanitizer (run it in a process started with libasan preloaded; see tests/test_tok_sanitize.py)."""
     import pybind11
     name = "_tok"
     so_path = os.path.join(PKG_DIR, name + EXT_SUFFIX)
+    opt = ["-O3"]
+    if sanitize:
+        os.makedirs(os.path.join(BUILD_DIR, "sanitize"), exist_ok=True)
+        so_path = os.path.join(BUILD_DIR, "sanitize", name + EXT_SUFFIX)
+        opt = ["-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"]
     srcs = sorted(glob.glob(os.path.join(TOK_SRC, "*.cpp")))
     if not srcs:
         raise FileNotFoundError("tokenizer sources not found")
@@ -145,7 +152,7 @@ def build_tokenizer_extension(force=False):
     digest = _hash_files(srcs + headers)
     if not force and not _stale(so_path, digest):
         return so_path
-    cmd = ["g++", "-O3", "-std=c++17", "-fPIC", "-shared", "-pthread", "-I", pybind11.get_include(),
+    cmd = ["g++", *opt, "-std=c++17", "-fPIC", "-shared", "-pthread", "-I", pybind11.get_include(),
            "-I", sysconfig.get_paths()["include"], "-I", TOK_SRC, *srcs, "-o", so_path]
     _run(cmd)
     with open(so_path + ".hash", "w") as f:
@@ -159,8 +166,21 @@ _tok_ext = None
 def load_tokenizer_extension():
     global _tok_ext
     if _tok_ext is None:
-        _tok_ext = _load("nanochat_b200._tok", build_tokenizer_extension())
+        sanitize = os.environ.get("NANOCHAT_TOK_SANITIZE", "0") == "1"      # ASan/UBSan copy, for the sanitizer test
+        _tok_ext = _load("nanochat_b200._tok", build_tokenizer_extension(sanitize=sanitize))
     return _tok_ext
+
+
+def sanitizer_runtime_libs():
+    """Paths of the ASan and UBSan runtimes of the host compiler (for LD_PRELOAD), or None if either is missing."""
+    out = []
+    for lib in ("libasan.so", "libubsan.so"):
+        r = subprocess.run(["gcc", f"-print-file-name={lib}"], capture_output=True, text=True)
+        path = r.stdout.strip()
+        if r.returncode != 0 or not os.path.isabs(path) or not os.path.exists(path):
+            return None
+        out.append(os.path.realpath(path))
+    return out
 
 
 def build_all(verbose=False, force=False):
