@@ -68,6 +68,10 @@ parser.add_argument("--core-metric-max-per-task", type=int, default=500)
 parser.add_argument("--sample-every", type=int, default=2000)
 parser.add_argument("--save-every", type=int, default=-1)
 parser.add_argument("--log-every", type=int, default=100, help="steps between metric records (wandb and the metrics file)")
+parser.add_argument("--heartbeat-timeout", type=float, default=0.0,
+                    help="seconds without a peer's heartbeat before the run stops with an error (0 = no heartbeat)")
+parser.add_argument("--abort-on-divergence", action="store_true",
+                    help="stop when the loss is non-finite or stays above 3x its running average")
 parser.add_argument("--metrics-file", type=str, default=None,
                     help="JSONL metrics file (default: <base_dir>/metrics/base_train_<model tag>.jsonl; '' disables)")
 parser.add_argument("--model-tag", type=str, default=None)
@@ -135,6 +139,14 @@ if metrics_path is None:
 wandb_run = MetricsLog(metrics_path if (master_process and metrics_path) else None, forward_to=wandb_run,
                        header={"script": "base_train", "config": user_config, "world_size": ddp_world_size})
 timers = PhaseTimers(device_type=device_type)
+# host-side failure detection (both off by default): a lost rank is reported before the next step is launched
+from nanochat_b200.parallel.heartbeat import Heartbeat, LossWatch, default_store
+heartbeat = None
+if args.heartbeat_timeout > 0 and ddp_world_size > 1:
+    heartbeat = Heartbeat(default_store(), ddp_rank, ddp_world_size, interval=min(1.0, args.heartbeat_timeout / 4),
+                          timeout=args.heartbeat_timeout)
+    heartbeat.wait_for_peers()
+loss_watch = LossWatch() if args.abort_on_divergence else None
 resuming = args.resume_from_step != -1
 if resuming:
     print0(f"Resuming optimization from step {args.resume_from_step}")
@@ -261,6 +273,8 @@ print0(f"Total batch size {total_batch_size:,} => gradient accumulation steps: {
 # ---------------------------------------------------------------------------------- loop
 while True:
     last_step = step == num_iterations
+    if heartbeat is not None:
+        heartbeat.check()                  # raises RankLostError: no collective is started against a dead peer
     flops_so_far = num_flops_per_token * total_batch_size * step
 
     if build_val_loader is not None and args.eval_every > 0 and (last_step or step % args.eval_every == 0):
@@ -348,6 +362,10 @@ while True:
     synchronize()
     dt = time.time() - t0
     phase_ms = timers.collect()            # {} unless NANOCHAT_TRACE=1; device time per phase, max over ranks
+    if loss_watch is not None:
+        why = loss_watch.update(train_loss_f)
+        if why is not None:                # every rank sees its own shard's loss; any rank may raise
+            raise RuntimeError(f"training diverged at step {step}: {why}")
 
     ema_beta = 0.9
     smooth_train_loss = ema_beta * smooth_train_loss + (1 - ema_beta) * train_loss_f
@@ -388,4 +406,6 @@ print0(f"Total training time: {total_training_time/60:.2f}m")
 if val_bpb is not None:
     print0(f"Minimum validation bpb: {min_val_bpb:.6f}")
 wandb_run.finish()
+if heartbeat is not None:
+    heartbeat.leave()
 compute_cleanup()
