@@ -52,6 +52,16 @@ def test_truncated_or_missing_checkpoint_files_raise_checkpoint_error(tmp_path):
     with pytest.raises(cm.CheckpointError, match="missing"):
         cm.load_checkpoint(d, 3, "cpu")
     assert not [f for f in os.listdir(d) if f.endswith(".tmp")]     # saves are atomic: no temp files left behind
+    # optimizer shards: a resume on more ranks than the run that saved has no shard for the new rank; a torn one is unreadable
+    cm.save_checkpoint(d, 5, {"w": torch.randn(4)}, {"state": {"0": torch.zeros(2)}}, {"model_config": {}}, rank=0)
+    with pytest.raises(cm.CheckpointError, match="missing"):
+        cm.load_checkpoint(d, 5, "cpu", load_optimizer=True, rank=1)
+    shard = os.path.join(d, "optim_000005_rank0.pt")
+    with open(shard, "r+b") as f:
+        f.truncate(os.path.getsize(shard) // 3)
+    with pytest.raises(cm.CheckpointError, match="unreadable"):
+        cm.load_checkpoint(d, 5, "cpu", load_optimizer=True, rank=0)
+    assert cm.load_checkpoint(d, 5, "cpu", load_optimizer=False)[1] is None      # the model alone still loads
 
 
 def test_largest_model_tag_is_the_deepest(tmp_path):
