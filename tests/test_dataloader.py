@@ -69,3 +69,37 @@ def test_loader_shapes_shift_and_resume_state(tmp_path, monkeypatch):
     resumed = dl._document_batches("train", {"pq_idx": 1, "rg_idx": 1, "epoch": 3}, 8)
     _, (pq_idx, rg_idx, epoch) = next(resumed)
     assert (pq_idx, rg_idx, epoch) == (1, 2, 3)
+
+
+def test_repackaged_corpus_is_read_back_by_the_loader(tmp_path, monkeypatch):
+    """Local files -> shards -> the loader's row-group iterator: nothing lost, last shard is validation."""
+    import json
+    import pyarrow.parquet as pq
+    from scripts import repackage_data as rp
+    from nanochat_b200 import dataset
+    src = tmp_path / "src"
+    src.mkdir()
+    docs_txt = [f"line document {i} " + "x" * (i % 50) for i in range(700)]
+    (src / "a.txt").write_text("\n".join(docs_txt) + "\n\n")
+    docs_jsonl = [f"json document {i}\nwith a second line" for i in range(300)]
+    (src / "b.jsonl").write_text("\n".join(json.dumps({"text": d, "other": i}) for i, d in enumerate(docs_jsonl)))
+    base = tmp_path / "base"
+    monkeypatch.setenv("NANOCHAT_BASE_DIR", str(base))
+    out = dataset.data_dir()
+    m = rp.repackage([str(src)], out, chars_per_shard=6000, row_group_size=64, seed=1, shuffle_buffer=256, log=lambda s: None)
+    assert m["documents"] == 1000 and len(m["shards"]) >= 3 and m["validation_shard"] == m["shards"][-1]["file"]
+    for s in m["shards"][:-1]:
+        assert s["documents"] % 64 == 0 and s["characters"] >= 6000
+    assert pq.ParquetFile(os.path.join(out, "shard_00000.parquet")).metadata.row_group(0).num_rows == 64
+    train = [d for batch in dataset.parquets_iter_batched("train") for d in batch]
+    val = [d for batch in dataset.parquets_iter_batched("val") for d in batch]
+    assert sorted(train + val) == sorted(docs_txt + docs_jsonl) and len(val) == m["shards"][-1]["documents"]
+    assert train[:50] != (docs_txt + docs_jsonl)[:50]                      # shuffled
+    two = [d for r in range(2) for batch in dataset.parquets_iter_batched("train", start=r, step=2) for d in batch]
+    assert sorted(two) == sorted(train)                                    # rank striding covers every row group once
+    again = tmp_path / "again"
+    m2 = rp.repackage([str(src)], str(again), chars_per_shard=6000, row_group_size=64, seed=1, shuffle_buffer=256,
+                      log=lambda s: None)
+    assert m2["shards"] == m["shards"]                                     # same seed, same shards
+    with pytest.raises(FileExistsError):
+        rp.repackage([str(src)], out, log=lambda s: None)
