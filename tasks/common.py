@@ -90,7 +90,8 @@ class Task:
         raise NotImplementedError
 
     def __len__(self):
-        stop = self.num_examples() if self.stop is None else self.stop
+        # a stop beyond the data (a fixed evaluation budget on a smaller dataset) ends at the data
+        stop = self.num_examples() if self.stop is None else min(self.stop, self.num_examples())
         n = -(-(stop - self.start) // self.step)
         assert n >= 0, f"Negative number of examples???: {n}"
         return n

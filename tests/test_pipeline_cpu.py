@@ -72,3 +72,63 @@ def test_toy_pipeline_end_to_end(tmp_path):
                "--device-batch-size=2", "--total-batch-size=256", "--eval-every=-1", "--chatcore-every=-1",
                "--device-type=cpu")
     assert re.search(r"step 0000\d .*loss: [0-9.]+", out)
+
+    # the real finetuning path: base checkpoint + optimizer warm start + task mixture, with the task datasets
+    # placed in the local cache (no network); then task evaluation and RL on the finetuned model
+    _write_task_data(base)
+    out = _run(base, "scripts.chat_sft", "--num-iterations=3", "--device-batch-size=2", "--total-batch-size=256",
+               "--eval-every=2", "--eval-tokens=256", "--chatcore-every=-1", "--device-type=cpu")
+    assert "Inherited max_seq_len=64" in out and "Loaded optimizer state from pretrained checkpoint" in out
+    assert re.search(r"Training mixture: \d+ rows", out) and re.search(r"step 0000\d .*loss: [0-9.]+", out)
+    assert os.path.isdir(os.path.join(base, "chatsft_checkpoints", "d2"))
+    out = _run(base, "scripts.chat_eval", "-i", "sft", "-a", "ARC-Easy|GSM8K", "-x", "4", "-m", "8", "-b", "2",
+               "--device-type=cpu")
+    assert re.search(r"ARC-Easy accuracy: [0-9.]+%", out) and re.search(r"GSM8K accuracy: [0-9.]+%", out)
+    out = _run(base, "scripts.chat_rl", "--num-samples=2", "--device-batch-size=2", "--examples-per-step=2",
+               "--max-new-tokens=8", "--eval-examples=2", "--eval-every=2", "--save-every=2", "--device-type=cpu")
+    assert "Calculated number of steps: 4" in out and re.search(r"Step 0 \| Pass@1: [0-9.]+, Pass@2: [0-9.]+", out)
+    assert re.search(r"Step 3/4 \|", out) or re.search(r"[Ss]tep 3", out)
+    rl = os.path.join(base, "chatrl_checkpoints", "d2")
+    assert any(f.startswith("model_") for f in os.listdir(rl))
+    out = _run(base, "scripts.chat_cli", "-i", "rl", "-p", "2+2?", "-t", "0.0", "--device-type=cpu")
+    assert "Assistant:" in out
+
+
+def _write_task_data(base):
+    """Tiny stand-ins for the hub datasets, in the cache layout `tasks.common.load_hub_dataset` reads."""
+    import json
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    def put(repo, subset, split, table):
+        d = os.path.join(base, "task_data", repo.replace("/", "--"), subset, split)
+        os.makedirs(d, exist_ok=True)
+        pq.write_table(table, os.path.join(d, "00000.parquet"))
+        with open(os.path.join(d, "manifest.json"), "w") as f:
+            json.dump(["00000.parquet"], f)
+
+    def gsm(n, off):
+        return pa.Table.from_pydict({
+            "question": [f"What is {i + off} plus {i}?" for i in range(n)],
+            "answer": [f"Add them: <<{i + off}+{i}={2 * i + off}>>{2 * i + off}\n#### {2 * i + off}" for i in range(n)]})
+    talk = pa.Table.from_pylist([
+        {"messages": ([{"role": "system", "content": "Be brief."}] if i % 3 == 0 else []) + [
+            {"role": "user", "content": f"Say the number {i}."}, {"role": "assistant", "content": f"The number is {i}."},
+            {"role": "user", "content": "Again?"}, {"role": "assistant", "content": f"{i}"}]}
+        for i in range(40)])
+    put("HuggingFaceTB/smol-smoltalk", "default", "train", talk)
+    put("HuggingFaceTB/smol-smoltalk", "default", "test", talk.slice(0, 12))
+    mmlu = pa.Table.from_pylist([
+        {"question": f"Pick option {i % 4}.", "subject": "toy", "choices": ["zero", "one", "two", "three"], "answer": i % 4}
+        for i in range(24)])
+    put("cais/mmlu", "all", "auxiliary_train", mmlu)
+    put("cais/mmlu", "all", "test", mmlu.slice(0, 8))
+    put("openai/gsm8k", "main", "train", gsm(8, 1))
+    put("openai/gsm8k", "main", "test", gsm(4, 3))
+    arc = pa.Table.from_pylist([
+        {"id": str(i), "question": f"Which is letter {'ABCD'[i % 4]}?",
+         "choices": {"text": ["a", "b", "c", "d"], "label": ["A", "B", "C", "D"]}, "answerKey": "ABCD"[i % 4]}
+        for i in range(6)])
+    for split in ("train", "validation", "test"):
+        put("allenai/ai2_arc", "ARC-Easy", split, arc)
+

@@ -23,6 +23,7 @@ def test_full_and_sliced_views():
     assert len(t) == 5 and t[0]["i"] == 5
     t = Toy(10, start=0, stop=10, step=3)
     assert len(t) == 4 and [t[i]["i"] for i in range(4)] == [0, 3, 6, 9]
+    assert len(Toy(10, stop=5200)) == 10 and len(Toy(10, start=4, stop=5200, step=2)) == 3      # stop ends at the data
 
 
 def test_mixture_is_a_deterministic_interleaved_permutation():
