@@ -40,6 +40,8 @@ def test_toy_pipeline_end_to_end(tmp_path):
     out = _run(base, "scripts.tok_train", "--max-chars=300000", "--vocab-size=512")
     assert os.path.exists(os.path.join(base, "tokenizer", "tokenizer.pkl"))
     assert os.path.exists(os.path.join(base, "tokenizer", "token_bytes.pt"))
+    out = _run(base, "scripts.tok_eval")           # the comparison vocabularies need a network: reported, not fatal
+    assert re.search(r"Ours: \d+", out) and "GPT-2" in out
 
     train_args = ["scripts.base_train", "--depth=2", "--head-dim=64", "--window-pattern=L", "--max-seq-len=64",
                   "--device-batch-size=4", "--total-batch-size=512", "--eval-tokens=1024", "--core-metric-every=-1",
