@@ -210,6 +210,39 @@ def test_model_loss_and_grads_match_torch_path(nat):
     assert logits.shape == (B, T, 2048) and logits.dtype == torch.float32
 
 
+def test_weighted_per_token_loss_backward_matches_torch_path(nat):
+    """The policy-gradient objective: per-token losses times per-token advantages, summed (reduction 'none')."""
+    from nanochat_b200 import ops
+    m = _tiny_model(n_layer=2, window="SL")
+    B, T = 2, 256
+    idx = torch.randint(0, 2048, (B, T), device="cuda")
+    tgt = torch.randint(0, 2048, (B, T), device="cuda")
+    tgt[1, 100:] = -1                                          # padding carries no loss and no gradient
+    adv = torch.randn(B, 1, device="cuda").expand(B, T).contiguous()
+
+    def run():
+        for p in m.parameters():
+            p.grad = None
+            if hasattr(p, "grad32"):
+                p.grad32.zero_()
+        per_tok = m(idx, tgt, loss_reduction="none").view(B, T)
+        obj = (per_tok * adv).sum() / (tgt >= 0).sum()
+        obj.backward()
+        nat.check_status(obj)
+        return obj.item(), {n: (getattr(p, "grad32", None) if p.grad is None else p.grad).float().clone()
+                            for n, p in m.named_parameters()}
+    obj, got = run()
+    ops.set_kernel_mode("torch")
+    try:
+        ref_obj, ref = run()
+    finally:
+        ops.set_kernel_mode("native")
+    assert abs(obj - ref_obj) < 2e-2, (obj, ref_obj)
+    bad = [(n, _rel_err(got[n], ref[n])) for n in ref
+           if n != "backout_lambda" and ref[n].numel() >= 64 and _rel_err(got[n], ref[n]) > 8e-2]
+    assert not bad, bad
+
+
 def test_quantize_kernels_match_torch(nat):
     x = (_mk((384, 512), seed=11).float() * 3).to(BF16)
     for dt in (torch.float8_e4m3fn, torch.float8_e5m2):
