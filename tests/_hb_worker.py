@@ -16,7 +16,7 @@ def main():
     mode, out_dir = sys.argv[1], sys.argv[2]
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
-    hb = Heartbeat(default_store(), rank, world, interval=0.2, timeout=1.5)
+    hb = Heartbeat(default_store(), rank, world, interval=0.2, timeout=3.0)
     hb.wait_for_peers()
     victim = world - 1
     outcome = {"rank": rank, "steps": 0}

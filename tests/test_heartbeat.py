@@ -48,7 +48,7 @@ def test_killed_rank_is_named_by_every_survivor_within_the_deadline(tmp_path):
         assert procs[r].returncode == 0 and "TIMEOUT" not in outs[r], outs[r][-2000:]
         got = json.load(open(tmp_path / f"rank{r}.json"))
         assert got["outcome"].startswith("error: lost rank(s) [2]") and got["lost"] == [2], got
-        assert got["steps"] == 3 and got["seconds"] < 10, got
+        assert got["steps"] == 3 and got["seconds"] < 30, got
     assert not (tmp_path / "rank2.json").exists()
 
 
@@ -85,8 +85,8 @@ class _FakeStore:
 
 def test_silent_peer_and_broken_store_are_losses():
     store = _FakeStore()
-    a = Heartbeat(store, 0, 2, interval=0.05, timeout=0.4)
-    b = Heartbeat(store, 1, 2, interval=0.05, timeout=0.4)
+    a = Heartbeat(store, 0, 2, interval=0.05, timeout=1.0)
+    b = Heartbeat(store, 1, 2, interval=0.05, timeout=1.0)
     a.wait_for_peers(deadline=5)
     time.sleep(0.3)
     a.check(); b.check()                                 # both beating: healthy
@@ -98,7 +98,7 @@ def test_silent_peer_and_broken_store_are_losses():
             time.sleep(0.05)
     a.stop()
     store2 = _FakeStore()
-    c = Heartbeat(store2, 1, 3, interval=0.05, timeout=0.4)
+    c = Heartbeat(store2, 1, 3, interval=0.05, timeout=1.0)
     store2.broken = True
     t0 = time.time()
     with pytest.raises(RankLostError, match="store unreachable") as e:
@@ -108,7 +108,7 @@ def test_silent_peer_and_broken_store_are_losses():
     assert e.value.ranks == [0, 2]
     c.stop()
     with pytest.raises(RankLostError, match="never started"):
-        Heartbeat(_FakeStore(), 0, 2, interval=0.05, timeout=0.4).wait_for_peers(deadline=0.3)
+        Heartbeat(_FakeStore(), 0, 2, interval=0.05, timeout=1.0).wait_for_peers(deadline=0.3)
 
 
 def test_loss_watch():
