@@ -343,6 +343,12 @@ class GPT(nn.Module):
         if kv_cache is None and common.COMPUTE_DTYPE == torch.bfloat16 and ops.use_native(self.transformer.wte.weight):
             return self._forward_native(idx, targets, cos_sin, loss_reduction)
 
+        if (kv_cache is not None and T > 1 and T0 == 0 and kv_cache.prev_embedding is None
+                and not torch.is_grad_enabled() and common.COMPUTE_DTYPE == torch.bfloat16
+                and self.config.n_embd // self.config.n_head == 128 and T <= kv_cache.max_seq_len
+                and ops.use_native(self.transformer.wte.weight)):
+            return self._prefill_native(idx, cos_sin, kv_cache)
+
         x = self._embed(idx, kv_cache)
         x0 = x
         backout_layer = self.config.n_layer // 2
@@ -383,6 +389,27 @@ class GPT(nn.Module):
             loss = nat.head_loss(x, x_backout, self.backout_lambda, self.lm_head.weight, targets,
                                  self.config.vocab_size, loss_reduction)
             return loss.view(-1) if loss_reduction == "none" else loss
+        x = ops.backout_norm(x, x_backout, self.backout_lambda)
+        return nat.softcap_logits(x, self.lm_head.weight, self.config.vocab_size)
+
+    def _prefill_native(self, idx, cos_sin, kv_cache):
+        """Prompt into an empty cache on the fused per-layer path of training (one QKV GEMM, rotary / QK-norm / VE
+        gate in place, the whole-sequence attention kernel), each layer's keys and values copied into its cache.
+        The op-by-op cached forward launches about twice as many kernels and is bound by their launch cost."""
+        nat = ops.native_module()
+        T = idx.size(1)
+        x, last = nat.embed_norm_smear(idx, self.transformer.wte.weight, self.smear_gate.weight, self.smear_lambda)
+        kv_cache.prev_embedding = last
+        x0 = x
+        backout_layer = self.config.n_layer // 2
+        x_backout = None
+        for i, block in enumerate(self.transformer.h):
+            ve_w = self.value_embeds[str(i)].weight if str(i) in self.value_embeds else None
+            x = nat.layer_forward(block, x, x0, idx, ve_w, cos_sin, self.window_sizes[i],
+                                  self.resid_lambdas, self.x0_lambdas, i, kv_sink=kv_cache.get_layer_cache(i))
+            if i == backout_layer:
+                x_backout = x
+        kv_cache.advance(T)
         x = ops.backout_norm(x, x_backout, self.backout_lambda)
         return nat.softcap_logits(x, self.lm_head.weight, self.config.vocab_size)
 

@@ -518,7 +518,7 @@ class _LayerFn(Function):
 
     @staticmethod
     def forward(ctx, x, x0, idx, cos, sin, resid_lambdas, x0_lambdas, layer, wq, wk, wv, wo, wfc, wpr,
-                wgate, ve_w, window, n_head, n_kv_head):
+                wgate, ve_w, window, n_head, n_kv_head, kv_sink=None):
         B, T, C = x.shape
         M = B * T
         D = C // n_head
@@ -529,7 +529,8 @@ class _LayerFn(Function):
         nq, nkv = n_head * D, n_kv_head * D
         sq, sk, sv = shadow_of(wq), shadow_of(wk), shadow_of(wv)
         fused_w = _contiguous_rows([sq, sk, sv])
-        fp8 = fused_w is not None and _fp8_ok(C, nq, nkv, wfc.shape[0])
+        # kv_sink: (k_cache, v_cache) of this layer, (B, Tmax, Hkv, D): prefill of an empty cache (inference, bf16)
+        fp8 = kv_sink is None and fused_w is not None and _fp8_ok(C, nq, nkv, wfc.shape[0])
         # producers that hold whole rows report max|output| themselves: no separate pass for the fp8 scale
         amax_xn = _zeroed_scalar(dev) if fp8 else None
         _C.mixnorm_fwd(x2, x02, resid_lambdas, x0_lambdas, layer, xm, xn, amax_xn)
@@ -556,6 +557,9 @@ class _LayerFn(Function):
         q = qkv[:, :nq].view(B, T, n_head, D)
         k = qkv[:, nq:nq + nkv].view(B, T, n_kv_head, D)
         v = qkv[:, nq + nkv:].view(B, T, n_kv_head, D)
+        if kv_sink is not None:
+            kv_sink[0][:, :T].copy_(k)
+            kv_sink[1][:, :T].copy_(v)
         amax_y = _zeroed_scalar(dev) if fp8 else None
         y, lse = attention_forward(q, k, v, window, amax_y)
         if lse is None:
@@ -711,17 +715,17 @@ class _LayerFn(Function):
                        _grad_buffer(resid_lambdas), _grad_buffer(x0_lambdas), amax_dx)
         if amax_dx is not None:
             _amax_hints[dx.data_ptr()] = amax_dx
-        return (dx.view(B, T, C), dx0.view(B, T, C)) + (None,) * 17
+        return (dx.view(B, T, C), dx0.view(B, T, C)) + (None,) * 18
 
 
-def layer_forward(block, x, x0, idx, ve_weight, cos_sin, window_size, resid_lambdas, x0_lambdas, layer):
+def layer_forward(block, x, x0, idx, ve_weight, cos_sin, window_size, resid_lambdas, x0_lambdas, layer, kv_sink=None):
     attn, mlp = block.attn, block.mlp
     return _LayerFn.apply(
         x, x0, idx, cos_sin[0], cos_sin[1], resid_lambdas, x0_lambdas, layer,
         attn.c_q.weight, attn.c_k.weight, attn.c_v.weight, attn.c_proj.weight,
         mlp.c_fc.weight, mlp.c_proj.weight,
         attn.ve_gate.weight if ve_weight is not None else None, ve_weight,
-        window_size[0], attn.n_head, attn.n_kv_head)
+        window_size[0], attn.n_head, attn.n_kv_head, kv_sink)
 
 
 # ------------------------------------------------------------------------ head function

@@ -128,6 +128,50 @@ def test_decode_graph_matches_cached_forward_and_engine_is_greedy_consistent():
     ops.native_module().check_status()
 
 
+@pytest.mark.parametrize("T", [8, 77, 200])
+def test_fused_prefill_matches_op_level_cached_forward(T):
+    """Prompt into an empty cache: the fused per-layer path against the plain-PyTorch cached forward (logits, the
+    cache contents, the smear state), then one decode step on top of each cache."""
+    from nanochat_b200 import ops
+    from nanochat_b200.engine import KVCache
+    model = _model()
+    cfg = model.config
+    g = torch.Generator(device="cuda").manual_seed(T)
+    ids = torch.randint(0, 2040, (1, T), device="cuda", generator=g)
+    nxt = torch.randint(0, 2040, (1, 1), device="cuda", generator=g)
+
+    def run():
+        cache = KVCache(1, cfg.n_kv_head, 256, 128, cfg.n_layer, "cuda", BF16)
+        with torch.inference_mode():
+            logits = model(ids, kv_cache=cache)
+            step = model(nxt, kv_cache=cache)
+        return logits.float(), step.float(), cache
+
+    calls = []
+    orig = model._prefill_native
+    model._prefill_native = lambda *a, **k: (calls.append(1), orig(*a, **k))[1]
+    logits, step, cache = run()
+    assert calls, "the fused prefill path was not taken"
+    ops.native_module().check_status()
+    ops.set_kernel_mode("torch")
+    try:
+        ref_logits, ref_step, ref_cache = run()
+    finally:
+        ops.set_kernel_mode("native")
+    assert len(calls) == 1
+    assert cache.get_pos() == ref_cache.get_pos() == T + 1
+    assert cache.cache_seqlens.tolist() == ref_cache.cache_seqlens.tolist() == [T + 1]
+    assert (logits - ref_logits).abs().max().item() < 0.25, (logits - ref_logits).abs().max().item()
+    assert (logits[0, -1].argmax() == ref_logits[0, -1].argmax()) or (logits[0, -1] - ref_logits[0, -1]).abs().max() < 0.1
+    k, rk = cache.k_cache[:, :, :T + 1].float(), ref_cache.k_cache[:, :, :T + 1].float()
+    v, rv = cache.v_cache[:, :, :T + 1].float(), ref_cache.v_cache[:, :, :T + 1].float()
+    for got, want in ((k, rk), (v, rv)):
+        assert (got - want).abs().max().item() < 0.05 + 0.03 * want.abs().max().item()
+        assert (got - want).abs().mean().item() < 0.01 * want.abs().mean().item() + 1e-3
+    assert cache.k_cache[:, :, T + 1:].abs().sum().item() == 0           # nothing written past the prompt
+    assert (step - ref_step).abs().max().item() < 0.25
+
+
 def test_sampling_kernel_semantics():
     from nanochat_b200.ops import native as nat
     g = torch.Generator(device="cuda").manual_seed(7)
