@@ -24,7 +24,6 @@ import os
 import subprocess
 import sys
 import threading
-import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 
@@ -286,7 +285,7 @@ def run_reference(args):
         import torch
         import torch.distributed as dist
         import torch.nn as nn
-        from nanochat.common import compute_init, compute_cleanup, COMPUTE_DTYPE
+        from nanochat.common import compute_init, compute_cleanup
         from nanochat.gpt import GPT, GPTConfig
     except Exception as e:  # dependency missing on this box
         print(json.dumps({"impl": "reference", "unavailable": f"import failed: {type(e).__name__}: {e}"}))

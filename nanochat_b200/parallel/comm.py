@@ -25,7 +25,6 @@ Reference for the call sites being served: nanochat/optim.py:274-318 (reduces) a
 
 import threading
 
-import torch
 import torch.distributed as dist
 
 
