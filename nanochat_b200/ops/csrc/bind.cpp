@@ -263,6 +263,21 @@ void gemv_rows(const Tensor& x, const Tensor& W, Tensor& out, const optional<Ten
                          (int)x.size(0), (int)W.size(0), (int)x.size(1), (int)epi, norm_input ? 1 : 0, cur_stream()));
 }
 
+// ids: int64 (B) or (B, 1); wte: (V, C) bf16; gate_w: fp32 (n_gate); lam: fp32 (1); prev, out: (B, C) bf16.
+void decode_embed(const Tensor& ids, const Tensor& wte, const Tensor& gate_w, const Tensor& lam, Tensor& prev, Tensor& out) {
+  check_bf16(wte, "wte"); check_bf16(prev, "prev"); check_bf16(out, "out");
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == at::kLong && ids.is_contiguous() && ids.numel() == out.size(0), "ids int64 (B)");
+  TORCH_CHECK(wte.dim() == 2 && wte.stride(1) == 1 && out.dim() == 2 && out.stride(1) == 1 && prev.dim() == 2 &&
+              prev.stride(1) == 1 && out.size(1) == wte.size(1) && prev.sizes() == out.sizes(), "embedding shapes");
+  TORCH_CHECK(gate_w.is_cuda() && gate_w.scalar_type() == at::kFloat && gate_w.is_contiguous() && lam.is_cuda() &&
+              lam.scalar_type() == at::kFloat && lam.numel() == 1, "gate weights fp32, lambda fp32 (1)");
+  const c10::cuda::CUDAGuard guard(out.device());
+  NC_CHECK(nc::decode_embed(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), wte.data_ptr(), wte.stride(0),
+                            (int)wte.size(0), gate_w.data_ptr<float>(), (int)gate_w.numel(), lam.data_ptr<float>(),
+                            prev.data_ptr(), prev.stride(0), out.data_ptr(), out.stride(0), (int)out.size(0),
+                            (int)out.size(1), cur_stream()));
+}
+
 // qkv: (B, (H+2Hkv)*128); cos/sin: (Tmax, 64); seqlens: int32 (B); k_cache/v_cache: (B, Tmax, Hkv, 128) of one layer.
 void decode_qkv_post(Tensor& qkv, int64_t H, int64_t Hkv, const Tensor& cos_t, const Tensor& sin_t, const Tensor& seqlens,
                      const optional<Tensor>& xn, const optional<Tensor>& wg, const optional<Tensor>& ve,
@@ -454,6 +469,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_pick_bn", &gemm_pick_bn);
   m.def("sample_next_token", &sample_next_token);
   m.def("gemv_rows", &gemv_rows);
+  m.def("decode_embed", &decode_embed);
   m.def("decode_qkv_post", &decode_qkv_post);
   m.def("decode_attn", &decode_attn);
   m.def("decode_attn_scratch", &decode_attn_scratch);

@@ -6,6 +6,7 @@
 //                    loads; the handful of activation rows stay in L1. Decode is bound by reading every
 //                    weight once per token, so the kernel is a bandwidth kernel: no tensor cores, many
 //                    loads in flight on every SM whatever the shape.
+//   decode_embed     token embedding, RMS norm and the smear with the previous token's embedding: one CTA per row.
 //   decode_qkv_post  rotary at position seqlens[b], RMS norm and scale of q and k, value-embedding gate
 //                    on v, and the append of k and v to the (B, T, Hkv, D) cache: one warp per head.
 //   decode_attn      flash-decoding: grid (splits, heads, rows), each CTA reduces a slice of the visible
@@ -138,6 +139,67 @@ gemv_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_
       if (aux) v += __bfloat162float(aux[b * ldaux + n]);
       out[b * ldo + n] = __float2bfloat16(v);
     }
+  }
+}
+
+// One CTA per row: token embedding -> RMS norm -> smear with the previous token's normed embedding
+//   e = norm(wte[id]);  out = e + lam * sigmoid(e[:n_gate] . gate_w) * prev;  prev <- e
+// (reference: nanochat/gpt.py:471-492, the single-token branch). `prev` holds zeros at the start of a generation
+// whose prefill left no state, which makes the smear term vanish.
+__global__ void __launch_bounds__(256)
+decode_embed_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ wte, long long ldw, int vocab,
+                    const float* __restrict__ gate_w, int n_gate, const float* __restrict__ lam,
+                    __nv_bfloat16* __restrict__ prev, long long ldp, __nv_bfloat16* __restrict__ out, long long ldo,
+                    int C) {
+  __shared__ float s_red[8];
+  __shared__ float s_head[32];
+  __shared__ float s_bcast[2];
+  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  long long id = ids[b];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);          // an out-of-range id must not become a wild read
+  const __nv_bfloat16* row = wte + id * ldw;
+  float ss = 0.f;
+  for (int c = tid * 8; c < C; c += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + c);
+    const float2 a0 = unpack_bf16(v.x), a1 = unpack_bf16(v.y), a2 = unpack_bf16(v.z), a3 = unpack_bf16(v.w);
+    ss += a0.x * a0.x + a0.y * a0.y + a1.x * a1.x + a1.y * a1.y + a2.x * a2.x + a2.y * a2.y + a3.x * a3.x + a3.y * a3.y;
+  }
+  ss = warp_sum(ss);
+  if (lane == 0) s_red[warp] = ss;
+  __syncthreads();
+  if (tid == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) t += s_red[w];
+    s_bcast[0] = rsqrtf(t / C + kRmsEps);
+  }
+  __syncthreads();
+  const float rstd = s_bcast[0];
+  if (tid < n_gate) s_head[tid] = __bfloat162float(__float2bfloat16(__bfloat162float(row[tid]) * rstd)) * gate_w[tid];
+  __syncthreads();
+  if (tid == 0) {
+    float dot = 0.f;
+    for (int i = 0; i < n_gate; ++i) dot += s_head[i];
+    s_bcast[1] = lam[0] / (1.f + __expf(-dot));
+  }
+  __syncthreads();
+  const float gate = s_bcast[1];
+  for (int c = tid * 8; c < C; c += 256 * 8) {
+    const uint4 v = *reinterpret_cast<const uint4*>(row + c);
+    const uint4 pv = *reinterpret_cast<const uint4*>(prev + b * ldp + c);
+    const uint32_t in[4] = {v.x, v.y, v.z, v.w}, pin[4] = {pv.x, pv.y, pv.z, pv.w};
+    uint32_t e_out[4], x_out[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 a = unpack_bf16(in[j]), p = unpack_bf16(pin[j]);
+      const __nv_bfloat162 e = __floats2bfloat162_rn(a.x * rstd, a.y * rstd);          // the normed embedding, as stored
+      const float2 ef = __bfloat1622float2(e);
+      const __nv_bfloat162 x = __floats2bfloat162_rn(ef.x + gate * p.x, ef.y + gate * p.y);
+      e_out[j] = *reinterpret_cast<const uint32_t*>(&e);
+      x_out[j] = *reinterpret_cast<const uint32_t*>(&x);
+    }
+    *reinterpret_cast<uint4*>(prev + b * ldp + c) = make_uint4(e_out[0], e_out[1], e_out[2], e_out[3]);
+    *reinterpret_cast<uint4*>(out + b * ldo + c) = make_uint4(x_out[0], x_out[1], x_out[2], x_out[3]);
   }
 }
 
@@ -316,6 +378,17 @@ cudaError_t gemv_rows(const void* x, long long ldx, const void* W, long long ldw
   }
 #undef NC_GEMV
   return e;
+}
+
+cudaError_t decode_embed(const long long* ids, const void* wte, long long ldw, int vocab, const float* gate_w, int n_gate,
+                         const float* lam, void* prev, long long ldp, void* out, long long ldo, int B, int C,
+                         cudaStream_t s) {
+  if (B <= 0 || C % 8 != 0 || ldw % 8 != 0 || ldp % 8 != 0 || ldo % 8 != 0 || n_gate < 0 || n_gate > 32 || n_gate > C)
+    return cudaErrorInvalidValue;
+  decode_embed_kernel<<<B, 256, 0, s>>>(ids, reinterpret_cast<const __nv_bfloat16*>(wte), ldw, vocab, gate_w, n_gate, lam,
+                                        reinterpret_cast<__nv_bfloat16*>(prev), ldp,
+                                        reinterpret_cast<__nv_bfloat16*>(out), ldo, C);
+  return cudaGetLastError();
 }
 
 cudaError_t decode_qkv_post(void* qkv, long long ld, int H, int Hkv, const void* cos_t, const void* sin_t,

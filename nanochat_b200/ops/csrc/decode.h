@@ -13,6 +13,12 @@ enum DecodeEpilogue : int { DEC_EPI_NONE = 0, DEC_EPI_RELU2 = 1 };
 cudaError_t gemv_rows(const void* x, long long ldx, const void* W, long long ldw, void* out, long long ldo,
                       const void* aux, long long ldaux, int B, int N, int K, int epi, int norm_input, cudaStream_t s);
 
+// out[b] = e + lam * sigmoid(e[:n_gate] . gate_w) * prev[b], e = rmsnorm(wte[ids[b]]); prev[b] <- e. C, ldw, ldp, ldo
+// multiples of 8; n_gate <= 32; ids outside [0, vocab) are clamped.
+cudaError_t decode_embed(const long long* ids, const void* wte, long long ldw, int vocab, const float* gate_w, int n_gate,
+                         const float* lam, void* prev, long long ldp, void* out, long long ldo, int B, int C,
+                         cudaStream_t s);
+
 // In place on qkv (B rows of [q heads | k heads | v heads]): rotary at position seqlens[b] + RMS norm + 1.2 on
 // q and k; v += 3*sigmoid(xn[:12] . wg[hkv]) * ve[idx[b]] when ve != nullptr; k and v are appended to the
 // caches at (b, seqlens[b]) (cache strides c_bat / c_tok in elements, heads contiguous). A row whose position

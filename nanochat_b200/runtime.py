@@ -14,7 +14,6 @@ fast path does not apply (CPU, kernels disabled, more than 64 rows, head dim != 
 """
 
 import torch
-import torch.nn.functional as F
 
 from nanochat_b200 import common, ops
 from nanochat_b200.ops import reference as ref_ops
@@ -40,6 +39,7 @@ class DecodeGraph:
         self.prev = torch.zeros(B, C, dtype=bf16, device=dev)
         self.xm, self.xn, self.xa, self.xn2 = e(B, C), e(B, C), e(B, C), e(B, C)
         self.xs = [e(B, C), e(B, C)]                       # residual stream ping-pong
+        self.x_in = e(B, C)                                # embedding + smear: the stream's input and the x0 of every layer
         self.x_backout = e(B, C)
         self.qkv, self.y, self.h = e(B, nq + 2 * nkv), e(B, nq), e(B, 4 * C)
         self.logits_bf16 = e(B, model.lm_head.weight.shape[0])
@@ -106,13 +106,10 @@ class DecodeGraph:
         nq = H * 128
         cache = self.cache
         idx = self.ids[:, 0]
-        x = ref_ops.rms_norm(F.embedding(idx, m.transformer.wte.weight).to(torch.bfloat16))
-        gate = m.smear_lambda.to(x.dtype) * torch.sigmoid(
-            F.linear(x[:, :ref_ops.SMEAR_CHANNELS], m.smear_gate.weight.to(x.dtype)))
-        x_in = x + gate * self.prev
-        self.prev.copy_(x)
-        x0 = x_in
-        x = x_in
+        # embedding gather, norm, smear with the previous token's embedding and the update of that state: one kernel
+        C_.decode_embed(self.ids, m.transformer.wte.weight, m.smear_gate.weight.detach().float().contiguous().view(-1),
+                        m.smear_lambda.detach().float().view(1), self.prev, self.x_in)
+        x0 = x = self.x_in
         backout_layer = m.config.n_layer // 2
         scale = 1.0 / (128 ** 0.5)
         for i, w in enumerate(self.w):
@@ -176,6 +173,7 @@ def decode_graph_for(engine, kv_cache):
         return None
     cfg = model.config
     if (cfg.n_embd // cfg.n_head != 128 or kv_cache.batch_size > MAX_ROWS or common.COMPUTE_DTYPE != torch.bfloat16
+            or model.transformer.wte.weight.dtype != torch.bfloat16 or cfg.n_embd % 8 != 0
             or not getattr(kv_cache, "pooled", False)):
         return None
     graphs = engine._decode_graphs

@@ -66,6 +66,29 @@ def test_gemv_rows_matches_fp32():
         assert ((out.float() - ref3).norm() / ref3.norm()).item() < 1e-2
 
 
+def test_decode_embed_matches_fp32():
+    from nanochat_b200.ops import native as nat
+    g = torch.Generator(device="cuda").manual_seed(11)
+    V, C, B = 300, 1664, 5
+    wte = torch.randn(V, C, device="cuda", generator=g).to(BF16)
+    gate_w = torch.randn(24, device="cuda", generator=g) * 0.3
+    lam = torch.tensor([0.7], device="cuda")
+    prev = torch.randn(B, C, device="cuda", generator=g).to(BF16)
+    ids = torch.tensor([[3], [299], [0], [17], [3]], device="cuda")
+    out = torch.empty(B, C, dtype=BF16, device="cuda")
+    prev_in = prev.clone()
+    nat._C.decode_embed(ids, wte, gate_w, lam, prev, out)
+    e = wte[ids[:, 0]].float()
+    e = (e * torch.rsqrt(e.pow(2).mean(-1, keepdim=True) + 1.1920929e-07)).to(BF16).float()
+    gate = lam * torch.sigmoid(e[:, :24] @ gate_w)
+    want = e + gate[:, None] * prev_in.float()
+    assert torch.equal(prev.float(), e)                                  # the state becomes the normed embedding
+    assert (out.float() - want).abs().max().item() < 0.02 * want.abs().max().item()
+    zero = torch.zeros_like(prev)                                        # no previous token: the smear term vanishes
+    nat._C.decode_embed(ids, wte, gate_w, lam, zero, out)
+    assert torch.equal(out.float(), e) and torch.equal(zero.float(), e)
+
+
 def test_decode_attention_matches_fp32():
     from nanochat_b200.ops import native as nat
     g = torch.Generator(device="cuda").manual_seed(1)
