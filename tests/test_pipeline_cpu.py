@@ -50,6 +50,10 @@ def test_toy_pipeline_end_to_end(tmp_path):
                extra_env={"NANOCHAT_TRACE": "1"})
     bpbs = [float(x) for x in re.findall(r"Validation bpb: ([0-9.]+)", out)]
     assert len(bpbs) == 3 and bpbs[-1] < bpbs[0], bpbs       # it learns, even in four steps
+    # the lines the sweep scripts (runs/miniseries.sh, runs/scaling_laws.sh) scrape out of the log
+    for pattern in (r"^total +: [\d,]+$", r"^transformer_matrices +: [\d,]+$", r"^lm_head +: [\d,]+$",
+                    r"number of iterations.*: [\d,]+$", r"Total batch size [\d,]+", r"Validation bpb: [\d.]+$"):
+        assert re.search(pattern, out, re.M), pattern
     assert re.search(r"phases \(device ms, max over ranks\): forward: [0-9.]+ \| backward: [0-9.]+ \| optimizer:", out)
     from nanochat_b200.utils.trace import read_metrics
     recs = read_metrics(os.path.join(base, "metrics", "base_train_d2.jsonl"))
