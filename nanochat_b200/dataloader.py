@@ -16,6 +16,7 @@ kernels; the consumer only waits on an event.
 """
 
 import threading
+import atexit
 import queue
 
 import torch
@@ -137,6 +138,14 @@ def tokenizing_distributed_data_loader_with_state_bos_bestfit(
         free.put(s)
     stop = threading.Event()
 
+    def hand_over(item):
+        while not stop.is_set():
+            try:
+                ready.put(item, timeout=0.2)
+                return
+            except queue.Full:
+                continue
+
     def worker():
         try:
             while not stop.is_set():
@@ -144,12 +153,26 @@ def tokenizing_distributed_data_loader_with_state_bos_bestfit(
                 if slot is None:
                     return
                 snapshot = build(slot)
-                ready.put((slot, snapshot, None))
+                hand_over((slot, snapshot, None))
         except BaseException as e:   # surface loader failures in the training thread
-            ready.put((None, None, e))
+            hand_over((None, None, e))
 
     thread = threading.Thread(target=worker, daemon=True)
     thread.start()
+
+    def shutdown():
+        """Stop the producer and wait for it: a daemon thread that is inside the C++ tokenizer when the interpreter
+        finalises is unwound through frames that own running std::threads, which aborts the process."""
+        if stop.is_set():
+            return
+        stop.set()
+        free.put(None)
+        thread.join(timeout=30)
+        live = _live_loaders              # None once the module has been torn down at interpreter exit
+        if live is not None and shutdown in live:
+            live.remove(shutdown)
+
+    _live_loaders.append(shutdown)
     try:
         previous = None
         while True:
@@ -171,8 +194,16 @@ def tokenizing_distributed_data_loader_with_state_bos_bestfit(
             previous = slot
             yield dst[:B * T].view(B, T), dst[B * T:].view(B, T), snapshot
     finally:
-        stop.set()
-        free.put(None)
+        shutdown()
+
+
+_live_loaders = []
+
+
+@atexit.register
+def _stop_loaders_at_exit():
+    for shutdown in list(_live_loaders):
+        shutdown()
 
 
 def tokenizing_distributed_data_loader_bos_bestfit(*args, **kwargs):

@@ -103,3 +103,39 @@ def test_repackaged_corpus_is_read_back_by_the_loader(tmp_path, monkeypatch):
     assert m2["shards"] == m["shards"]                                     # same seed, same shards
     with pytest.raises(FileExistsError):
         rp.repackage([str(src)], out, log=lambda s: None)
+
+
+_EXIT_WORKER = r"""
+import os, random, sys
+sys.path.insert(0, sys.argv[1])
+os.environ["NANOCHAT_BASE_DIR"] = sys.argv[2]
+import pyarrow as pa, pyarrow.parquet as pq
+from nanochat_b200 import dataset, dataloader as dl
+from nanochat_b200.tokenizer import BPETokenizer
+rnd = random.Random(0)
+words = [("w%d" % i) * rnd.randint(1, 3) for i in range(400)]
+os.makedirs(dataset.data_dir())
+for s in range(2):
+    docs = [" ".join(rnd.choice(words) for _ in range(rnd.randint(200, 900))) for _ in range(800)]
+    pq.write_table(pa.table({"text": docs}), os.path.join(dataset.data_dir(), "shard_%05d.parquet" % s), row_group_size=128)
+tok = BPETokenizer.train_from_iterator((d for b in dataset.parquets_iter_batched("train") for d in b), 600)
+loader = dl.tokenizing_distributed_data_loader_with_state_bos_bestfit(tok, 8, 512, "train", device="cpu")
+for _ in range(int(sys.argv[3])):
+    x, y, state = next(loader)
+assert x.shape == (8, 512)
+print("leaving with the loader alive")
+# no close(), no del: the interpreter exits while the producer thread is busy tokenising
+"""
+
+
+@pytest.mark.parametrize("batches", [1, 7, 20])
+def test_process_exits_cleanly_with_a_live_loader(tmp_path, batches):
+    import subprocess
+    import sys
+    script = tmp_path / "w.py"
+    script.write_text(_EXIT_WORKER)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, str(script), root, str(tmp_path / "base"), str(batches)], capture_output=True,
+                       text=True, timeout=300)
+    assert r.returncode == 0 and "leaving with the loader alive" in r.stdout, (r.returncode, r.stderr[-2000:])
+    assert "terminate called" not in r.stderr, r.stderr[-2000:]
