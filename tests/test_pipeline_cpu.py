@@ -64,12 +64,19 @@ def test_toy_pipeline_end_to_end(tmp_path):
     ck = os.path.join(base, "base_checkpoints", "d2")
     assert sorted(os.listdir(ck)) == ["meta_000004.json", "model_000004.pt", "optim_000004_rank0.pt"]
 
-    out = _run(base, *train_args, "--num-iterations=6", "--eval-every=-1", "--resume-from-step=4")
+    _write_eval_bundle(base)
+    resume_args = [a for a in train_args if not a.startswith("--core-metric-every")]
+    out = _run(base, *resume_args, "--num-iterations=6", "--eval-every=-1", "--resume-from-step=4",
+               "--core-metric-every=5", "--core-metric-max-per-task=4")
     assert "Resuming optimization from step 4" in out and "step 00005/00006" in out and "step 00003/" not in out
+    assert len(re.findall(r"CORE metric: -?[0-9.]+", out)) == 2          # at step 5 and at the last step
 
-    out = _run(base, "scripts.base_eval", "--eval", "bpb,sample", "--device-batch-size=2", "--split-tokens=1024",
-               "--device-type=cpu")
+    out = _run(base, "scripts.base_eval", "--eval", "core,bpb,sample", "--device-batch-size=2", "--split-tokens=1024",
+               "--max-per-task=5", "--device-type=cpu")
     assert re.search(r"val bpb: [0-9.]+", out)
+    assert len(re.findall(r"accuracy: [0-9.]+ \| centered: -?[0-9.]+", out)) == 3
+    assert re.search(r"CORE metric: -?[0-9.]+$", out, re.M)          # the line the sweep scripts scrape
+    assert os.path.exists(os.path.join(base, "base_eval", "base_model_000006.csv"))
 
     out = _run(base, "scripts.chat_cli", "-i", "base", "-p", "the quick", "-t", "0.0", "--device-type=cpu")
     assert "Assistant:" in out
@@ -98,6 +105,34 @@ def test_toy_pipeline_end_to_end(tmp_path):
     assert any(f.startswith("model_") for f in os.listdir(rl))
     out = _run(base, "scripts.chat_cli", "-i", "rl", "-p", "2+2?", "-t", "0.0", "--device-type=cpu")
     assert "Assistant:" in out
+
+
+def _write_eval_bundle(base):
+    """A three-task stand-in for the CORE bundle (one task of each type), where `scripts.base_eval` looks for it."""
+    import json
+    d = os.path.join(base, "eval_bundle")
+    os.makedirs(os.path.join(d, "eval_data"), exist_ok=True)
+    tasks = [("toy_mc", "multiple_choice", 2, 25.0), ("toy_schema", "schema", 0, 50.0), ("toy_lm", "language_modeling", 1, 0.0)]
+    with open(os.path.join(d, "core.yaml"), "w") as f:
+        f.write("icl_tasks:\n")
+        for label, kind, shots, _ in tasks:
+            f.write(f"- label: {label}\n  dataset_uri: {label}.jsonl\n  num_fewshot: [{shots}]\n  icl_task_type: {kind}\n")
+            if kind == "language_modeling":
+                f.write("  continuation_delimiter: ' '\n")
+    with open(os.path.join(d, "eval_meta_data.csv"), "w") as f:
+        f.write("Eval Task,Task Category,Task Type,#shots,#datapoints,Random baseline,Centered Metric?\n")
+        for label, kind, shots, base_acc in tasks:
+            f.write(f"{label},toy,{kind},{shots},8,{base_acc},\n")
+    rows = {
+        "toy_mc": [{"query": f"the quick fox number {i} jumps", "choices": ["over", "far", "home", "rains"], "gold": i % 4}
+                   for i in range(8)],
+        "toy_schema": [{"context_options": [f"the dog {i}", f"the fox {i}"], "continuation": "runs far away", "gold": i % 2}
+                       for i in range(8)],
+        "toy_lm": [{"context": f"it rains hard on every street {i}", "continuation": "of town"} for i in range(8)],
+    }
+    for label, items in rows.items():
+        with open(os.path.join(d, "eval_data", f"{label}.jsonl"), "w") as f:
+            f.write("\n".join(json.dumps(r) for r in items) + "\n")
 
 
 def _write_task_data(base):
