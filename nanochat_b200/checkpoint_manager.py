@@ -172,8 +172,16 @@ def load_model(source, *args, **kwargs):
     return load_model_from_dir(checkpoints_dir, *args, **kwargs)
 
 
-def load_optimizer_state(source, device, rank, model_tag=None, step=None):
-    """This rank's optimizer shard only, or None when the file does not exist."""
+def optimizer_shard_count(checkpoint_dir, step):
+    """How many ranks saved optimizer shards at `step` (the world size of the run that wrote the checkpoint)."""
+    prefix = f"optim_{step:06d}_rank"
+    return sum(1 for f in os.listdir(checkpoint_dir) if f.startswith(prefix) and f.endswith(".pt"))
+
+
+def load_optimizer_state(source, device, rank, model_tag=None, step=None, world_size=None):
+    """This rank's optimizer shard only, or None when the file does not exist. The state is sharded by rank, so
+    shards written by a run of another world size do not fit: with `world_size` given, every rank sees the same
+    mismatch in the directory listing and gets None (a fresh optimizer) instead of a shape error on some ranks."""
     checkpoints_dir = os.path.join(get_base_dir(), _SOURCE_DIRS[source])
     if model_tag is None:
         model_tag = find_largest_model(checkpoints_dir)
@@ -181,6 +189,12 @@ def load_optimizer_state(source, device, rank, model_tag=None, step=None):
     if step is None:
         step = find_last_step(checkpoint_dir)
     path = os.path.join(checkpoint_dir, f"optim_{step:06d}_rank{rank:d}.pt")
+    if world_size is not None:
+        saved = optimizer_shard_count(checkpoint_dir, step)
+        if saved != world_size and saved > 0:
+            log0(f"Optimizer checkpoint at {checkpoint_dir} step {step} was written by {saved} rank(s); this run has "
+                 f"{world_size}: not loading it")
+            return None
     if not os.path.exists(path):
         log0(f"Optimizer checkpoint not found: {path}")
         return None

@@ -30,7 +30,8 @@ from nanochat_b200.common import (compute_init, compute_cleanup, print0, DummyWa
                                   autodetect_device_type, get_peak_flops, is_ddp_initialized)
 from nanochat_b200.models.gpt import GPT, GPTConfig
 from nanochat_b200 import schedules
-from nanochat_b200.checkpoint_manager import save_checkpoint, load_checkpoint
+from nanochat_b200.checkpoint_manager import (save_checkpoint, load_checkpoint, optimizer_shard_count,
+                                               CheckpointError)
 from nanochat_b200.loss_eval import evaluate_bpb
 from nanochat_b200.engine import Engine
 from nanochat_b200.utils.trace import MetricsLog, PhaseTimers
@@ -150,6 +151,10 @@ loss_watch = LossWatch() if args.abort_on_divergence else None
 resuming = args.resume_from_step != -1
 if resuming:
     print0(f"Resuming optimization from step {args.resume_from_step}")
+    saved_ranks = optimizer_shard_count(checkpoint_dir, args.resume_from_step)
+    if saved_ranks not in (0, ddp_world_size):
+        raise CheckpointError(f"{checkpoint_dir} step {args.resume_from_step} was written by {saved_ranks} rank(s); the "
+                              f"optimizer state is sharded by rank, so resume with {saved_ranks} rank(s), not {ddp_world_size}")
     model_data, optimizer_data, meta_data = load_checkpoint(checkpoint_dir, args.resume_from_step, device,
                                                             load_optimizer=True, rank=ddp_rank)
     model.load_state_dict(model_data, strict=True, assign=True)

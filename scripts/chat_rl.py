@@ -168,5 +168,6 @@ for step in range(num_steps):
         save_checkpoint(out_dir, step, model.state_dict(), None, {"model_config": dict(model.config.__dict__)})
         print(f"Saved model checkpoint to {out_dir}")
 
+batches.close()          # the rollout generator holds a no_grad context: close it before the interpreter tears torch down
 wandb_run.finish()
 compute_cleanup()

@@ -118,7 +118,8 @@ print0(f"Total batch size {args.total_batch_size:,} => gradient accumulation ste
 optimizer = model.setup_optimizer(unembedding_lr=args.unembedding_lr, embedding_lr=args.embedding_lr,
                                   matrix_lr=args.matrix_lr, weight_decay=0.0)
 if args.load_optimizer and not args.synthetic_data:
-    shard = load_optimizer_state("base", device, rank=ddp_rank, model_tag=args.model_tag, step=args.model_step)
+    shard = load_optimizer_state("base", device, rank=ddp_rank, model_tag=args.model_tag, step=args.model_step,
+                                 world_size=ddp_world_size)
     if shard is not None:
         fresh_lrs = [g["lr"] for g in optimizer.param_groups]
         optimizer.load_state_dict(shard)      # also brings back the (annealed) pretraining LRs ...
