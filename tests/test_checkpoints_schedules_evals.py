@@ -190,3 +190,19 @@ def test_fp8_conversion_filter_and_disable_context():
     ref = nn.functional.linear(ref, net[3].weight)
     assert torch.allclose(exact, ref, atol=1e-5)
     json.dumps({"n_fp8": sum(isinstance(m, Float8Linear) for m in net.modules())})
+
+
+def test_optimizer_shards_of_another_world_size_are_not_loaded(tmp_path, monkeypatch):
+    monkeypatch.setenv("NANOCHAT_BASE_DIR", str(tmp_path))
+    d = str(tmp_path / "base_checkpoints" / "d2")
+    for rank in range(2):                                       # a two-rank run saved step 9
+        cm.save_checkpoint(d, 9, {"w": torch.zeros(2)} if rank == 0 else None, {"state": {"0": torch.full((3,), float(rank))}},
+                           {"model_config": {}} if rank == 0 else None, rank=rank)
+    assert cm.optimizer_shard_count(d, 9) == 2 and cm.optimizer_shard_count(d, 8) == 0
+    got = cm.load_optimizer_state("base", "cpu", rank=1, world_size=2)
+    assert torch.equal(got["state"]["0"], torch.ones(3))
+    for world in (1, 4):                                        # every rank of a run of another size gets None
+        for rank in range(world):
+            assert cm.load_optimizer_state("base", "cpu", rank=rank, world_size=world) is None
+    assert cm.load_optimizer_state("base", "cpu", rank=0) is not None          # no world size given: as before
+    assert cm.load_optimizer_state("base", "cpu", rank=5) is None
