@@ -263,6 +263,24 @@ void gemv_rows(const Tensor& x, const Tensor& W, Tensor& out, const optional<Ten
                          (int)x.size(0), (int)W.size(0), (int)x.size(1), (int)epi, norm_input ? 1 : 0, cur_stream()));
 }
 
+// x, x0, xm, xn: (B, K) bf16 (xn: only its first 16 channels are written); lam_r, lam_0: fp32 (layers); W: (N, K); out: (B, N).
+void gemv_rows_mix(const Tensor& x, const Tensor& x0, const Tensor& lam_r, const Tensor& lam_0, int64_t layer,
+                   const Tensor& W, Tensor& out, Tensor& xm, Tensor& xn) {
+  check_bf16(x, "x"); check_bf16(x0, "x0"); check_bf16(W, "W"); check_bf16(out, "out"); check_bf16(xm, "xm"); check_bf16(xn, "xn");
+  TORCH_CHECK(x.dim() == 2 && W.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && x0.stride(1) == 1 && W.stride(1) == 1 &&
+              out.stride(1) == 1 && xm.stride(1) == 1 && xn.stride(1) == 1, "gemv_rows_mix: 2-D row-major tensors");
+  TORCH_CHECK(x.size(1) == W.size(1) && out.size(0) == x.size(0) && out.size(1) == W.size(0) && x0.sizes() == x.sizes() &&
+              xm.sizes() == x.sizes() && xn.sizes() == x.sizes() && x.size(1) >= 16, "gemv_rows_mix shapes");
+  TORCH_CHECK(lam_r.is_cuda() && lam_0.is_cuda() && lam_r.scalar_type() == at::kFloat && lam_0.scalar_type() == at::kFloat &&
+              lam_r.is_contiguous() && lam_0.is_contiguous() && layer >= 0 && layer < lam_r.numel() && layer < lam_0.numel(),
+              "lambdas: fp32 (layers)");
+  const c10::cuda::CUDAGuard guard(x.device());
+  NC_CHECK(nc::gemv_rows_mix(x.data_ptr(), x.stride(0), x0.data_ptr(), x0.stride(0), lam_r.data_ptr<float>(),
+                             lam_0.data_ptr<float>(), (int)layer, W.data_ptr(), W.stride(0), out.data_ptr(), out.stride(0),
+                             xm.data_ptr(), xm.stride(0), xn.data_ptr(), xn.stride(0), 16, (int)x.size(0), (int)W.size(0),
+                             (int)x.size(1), cur_stream()));
+}
+
 // ids: int64 (B) or (B, 1); wte: (V, C) bf16; gate_w: fp32 (n_gate); lam: fp32 (1); prev, out: (B, C) bf16.
 void decode_embed(const Tensor& ids, const Tensor& wte, const Tensor& gate_w, const Tensor& lam, Tensor& prev, Tensor& out) {
   check_bf16(wte, "wte"); check_bf16(prev, "prev"); check_bf16(out, "out");
@@ -469,6 +487,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm_pick_bn", &gemm_pick_bn);
   m.def("sample_next_token", &sample_next_token);
   m.def("gemv_rows", &gemv_rows);
+  m.def("gemv_rows_mix", &gemv_rows_mix);
   m.def("decode_embed", &decode_embed);
   m.def("decode_qkv_post", &decode_qkv_post);
   m.def("decode_attn", &decode_attn);

@@ -56,11 +56,24 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 constexpr int GEMV_ROWS = 4;       // output columns per CTA: all 256 threads split K for each of them
 
-template <int B>
+// MIX: the input row is the layer's mixed residual stream, built on the fly: xm = bf16(lam_r[layer] * x + lam_0[layer] * x0),
+// fed to the dot products as rmsnorm(xm) (norm_input semantics). The first CTA also writes xm (the residual the
+// attention projection adds back) and the first `head_cols` channels of rmsnorm(xm) (the value-embedding gate's input),
+// so no separate mix+norm kernel runs in the decode step.
+struct GemvMix {
+  const __nv_bfloat16* x0; long long ldx0;
+  const float* lam_r; const float* lam_0; int layer;
+  __nv_bfloat16* xm; long long ldxm;
+  __nv_bfloat16* xn_head; long long ldxn; int head_cols;
+};
+
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16(v)); }
+
+template <int B, bool MIX>
 __global__ void __launch_bounds__(256)
 gemv_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ W, long long ldw,
                  __nv_bfloat16* __restrict__ out, long long ldo, const __nv_bfloat16* __restrict__ aux, long long ldaux,
-                 int N, int K, int epi, int norm_input) {
+                 int N, int K, int epi, int norm_input, GemvMix mix) {
   __shared__ float s_acc[8][GEMV_ROWS][B];
   __shared__ float s_ss[8][B];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -82,6 +95,8 @@ gemv_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_
   }
   pdl_wait();
   pdl_trigger();
+  float lam_r = 1.f, lam_0 = 0.f;
+  if (MIX) { lam_r = mix.lam_r[mix.layer]; lam_0 = mix.lam_0[mix.layer]; }
   auto fma_chunk = [&](const uint4 (&wv)[GEMV_ROWS], int k) {
     float wf[GEMV_ROWS][8];
 #pragma unroll
@@ -93,10 +108,26 @@ gemv_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_
 #pragma unroll
     for (int b = 0; b < B; ++b) {
       const uint4 xv = *reinterpret_cast<const uint4*>(x + b * ldx + k);
-      const float2 x0 = unpack_bf16(xv.x), x1 = unpack_bf16(xv.y), x2 = unpack_bf16(xv.z), x3 = unpack_bf16(xv.w);
-      const float xf[8] = {x0.x, x0.y, x1.x, x1.y, x2.x, x2.y, x3.x, x3.y};
+      const float2 xa = unpack_bf16(xv.x), xb = unpack_bf16(xv.y), xc = unpack_bf16(xv.z), xd = unpack_bf16(xv.w);
+      float xf[8] = {xa.x, xa.y, xb.x, xb.y, xc.x, xc.y, xd.x, xd.y};
+      if (MIX) {
+        const uint4 zv = *reinterpret_cast<const uint4*>(mix.x0 + b * mix.ldx0 + k);
+        const float2 za = unpack_bf16(zv.x), zb = unpack_bf16(zv.y), zc = unpack_bf16(zv.z), zd = unpack_bf16(zv.w);
+        const float zf[8] = {za.x, za.y, zb.x, zb.y, zc.x, zc.y, zd.x, zd.y};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) xf[j] = round_bf16(lam_r * xf[j] + lam_0 * zf[j]);
+        if (blockIdx.x == 0) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(xf[2 * j], xf[2 * j + 1]);
+            pk[j] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+          *reinterpret_cast<uint4*>(mix.xm + b * mix.ldxm + k) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+      }
       // rmsnorm(x) . w = rstd * (x . w): the row's sum of squares rides along
-      if (norm_input) {
+      if (MIX || norm_input) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) ss[b] += xf[j] * xf[j];
       }
@@ -121,20 +152,28 @@ gemv_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_
       const float v = warp_sum(acc[r][b]);
       if (lane == 0) s_acc[warp][r][b] = v;
     }
-    if (norm_input) {
+    if (MIX || norm_input) {
       const float v = warp_sum(ss[b]);
       if (lane == 0) s_ss[warp][b] = v;
     }
   }
   __syncthreads();
+  if (MIX && blockIdx.x == 0 && tid < mix.head_cols * B) {
+    const int b = tid / mix.head_cols, c = tid - b * mix.head_cols;
+    float q = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) q += s_ss[w][b];
+    const float xm = round_bf16(lam_r * __bfloat162float(x[b * ldx + c]) + lam_0 * __bfloat162float(mix.x0[b * mix.ldx0 + c]));
+    mix.xn_head[b * mix.ldxn + c] = __float2bfloat16(xm * rsqrtf(q / K + kRmsEps));
+  }
   if (tid < GEMV_ROWS * B) {
     const int r = tid / B, b = tid - r * B;
     const int n = n0 + r;
     if (n < N) {
       float v = 0.f, q = 0.f;
 #pragma unroll
-      for (int w = 0; w < 8; ++w) { v += s_acc[w][r][b]; if (norm_input) q += s_ss[w][b]; }
-      if (norm_input) v *= rsqrtf(q / K + kRmsEps);
+      for (int w = 0; w < 8; ++w) { v += s_acc[w][r][b]; if (MIX || norm_input) q += s_ss[w][b]; }
+      if (MIX || norm_input) v *= rsqrtf(q / K + kRmsEps);
       if (epi == DEC_EPI_RELU2) { v = fmaxf(v, 0.f); v *= v; }
       if (aux) v += __bfloat162float(aux[b * ldaux + n]);
       out[b * ldo + n] = __float2bfloat16(v);
@@ -372,7 +411,31 @@ cudaError_t gemv_rows(const void* x, long long ldx, const void* W, long long ldw
   auto op = reinterpret_cast<__nv_bfloat16*>(out);
   auto ap = reinterpret_cast<const __nv_bfloat16*>(aux);
   cudaError_t e = cudaSuccess;
-#define NC_GEMV(BB) case BB: e = launch_pdl(gemv_rows_kernel<BB>, dim3(grid), dim3(256), s, xp, ldx, wp, ldw, op, ldo, ap, ldaux, N, K, epi, norm_input); break;
+  const GemvMix none = {};
+#define NC_GEMV(BB) case BB: e = launch_pdl(gemv_rows_kernel<BB, false>, dim3(grid), dim3(256), s, xp, ldx, wp, ldw, op, ldo, ap, ldaux, N, K, epi, norm_input, none); break;
+  switch (B) {
+    NC_GEMV(1) NC_GEMV(2) NC_GEMV(3) NC_GEMV(4) NC_GEMV(5) NC_GEMV(6) NC_GEMV(7) NC_GEMV(8)
+  }
+#undef NC_GEMV
+  return e;
+}
+
+cudaError_t gemv_rows_mix(const void* x, long long ldx, const void* x0, long long ldx0, const float* lam_r,
+                          const float* lam_0, int layer, const void* W, long long ldw, void* out, long long ldo,
+                          void* xm, long long ldxm, void* xn_head, long long ldxn, int head_cols, int B, int N, int K,
+                          cudaStream_t s) {
+  if (B < 1 || B > 8 || (K & 7) || (ldx & 7) || (ldx0 & 7) || (ldw & 7) || (ldxm & 7) || head_cols < 0 ||
+      head_cols * B > 256 || head_cols > K)
+    return cudaErrorInvalidValue;
+  const int grid = (N + GEMV_ROWS - 1) / GEMV_ROWS;
+  auto xp = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto wp = reinterpret_cast<const __nv_bfloat16*>(W);
+  auto op = reinterpret_cast<__nv_bfloat16*>(out);
+  const __nv_bfloat16* no_aux = nullptr;
+  GemvMix mix = {reinterpret_cast<const __nv_bfloat16*>(x0), ldx0, lam_r, lam_0, layer,
+                 reinterpret_cast<__nv_bfloat16*>(xm), ldxm, reinterpret_cast<__nv_bfloat16*>(xn_head), ldxn, head_cols};
+  cudaError_t e = cudaSuccess;
+#define NC_GEMV(BB) case BB: e = launch_pdl(gemv_rows_kernel<BB, true>, dim3(grid), dim3(256), s, xp, ldx, wp, ldw, op, ldo, no_aux, 0LL, N, K, (int)DEC_EPI_NONE, 1, mix); break;
   switch (B) {
     NC_GEMV(1) NC_GEMV(2) NC_GEMV(3) NC_GEMV(4) NC_GEMV(5) NC_GEMV(6) NC_GEMV(7) NC_GEMV(8)
   }

@@ -13,6 +13,14 @@ enum DecodeEpilogue : int { DEC_EPI_NONE = 0, DEC_EPI_RELU2 = 1 };
 cudaError_t gemv_rows(const void* x, long long ldx, const void* W, long long ldw, void* out, long long ldo,
                       const void* aux, long long ldaux, int B, int N, int K, int epi, int norm_input, cudaStream_t s);
 
+// The layer's first GEMV with the residual mix and the norm folded in: xm = bf16(lam_r[layer] * x + lam_0[layer] * x0),
+// out[b, n] = sum_k rmsnorm(xm)[b, k] * W[n, k]. Also writes xm (B x K) and the first head_cols channels of
+// rmsnorm(xm) to xn_head (the value-embedding gate reads them). head_cols * B <= 256.
+cudaError_t gemv_rows_mix(const void* x, long long ldx, const void* x0, long long ldx0, const float* lam_r,
+                          const float* lam_0, int layer, const void* W, long long ldw, void* out, long long ldo,
+                          void* xm, long long ldxm, void* xn_head, long long ldxn, int head_cols, int B, int N, int K,
+                          cudaStream_t s);
+
 // out[b] = e + lam * sigmoid(e[:n_gate] . gate_w) * prev[b], e = rmsnorm(wte[ids[b]]); prev[b] <- e. C, ldw, ldp, ldo
 // multiples of 8; n_gate <= 32; ids outside [0, vocab) are clamped.
 cudaError_t decode_embed(const long long* ids, const void* wte, long long ldw, int vocab, const float* gate_w, int n_gate,

@@ -66,6 +66,32 @@ def test_gemv_rows_matches_fp32():
         assert ((out.float() - ref3).norm() / ref3.norm()).item() < 1e-2
 
 
+def test_gemv_with_folded_mix_and_norm_matches_the_separate_kernels():
+    from nanochat_b200.ops import native as nat
+    g = torch.Generator(device="cuda").manual_seed(5)
+    lam_r = torch.tensor([1.0, 0.9, 1.1], device="cuda")
+    lam_0 = torch.tensor([0.0, 0.2, -0.1], device="cuda")
+    for B, N, K, layer in ((1, 4992, 1664, 1), (5, 1000, 256, 2), (8, 768, 2048, 0)):
+        x = torch.randn(B, K, device="cuda", generator=g).to(BF16)
+        x0 = torch.randn(B, K, device="cuda", generator=g).to(BF16)
+        W = (torch.randn(N, K, device="cuda", generator=g) * 0.05).to(BF16)
+        out = torch.empty(B, N, dtype=BF16, device="cuda")
+        xm = torch.zeros(B, K, dtype=BF16, device="cuda")
+        xn = torch.zeros(B, K, dtype=BF16, device="cuda")
+        nat._C.gemv_rows_mix(x, x0, lam_r, lam_0, layer, W, out, xm, xn)
+        # oracle: the stand-alone mix + norm kernel, then fp32 matmul
+        xm_ref = torch.empty_like(xm)
+        xn_ref = torch.empty_like(xn)
+        nat._C.mixnorm_fwd(x, x0, lam_r, lam_0, layer, xm_ref, xn_ref, None)
+        assert torch.equal(xm, xm_ref)                                        # same rounding, bit for bit
+        assert (xn[:, :16].float() - xn_ref[:, :16].float()).abs().max().item() <= 0.02 * xn_ref.float().abs().max().item()
+        assert xn[:, 16:].abs().sum().item() == 0                             # only the gate's slice is written
+        xmf = xm_ref.float()
+        ref = (xmf * torch.rsqrt(xmf.pow(2).mean(-1, keepdim=True) + 1.1920929e-07)) @ W.float().t()
+        assert ((out.float() - ref).norm() / ref.norm()).item() < 1e-2
+    nat.check_status()
+
+
 def test_decode_embed_matches_fp32():
     from nanochat_b200.ops import native as nat
     g = torch.Generator(device="cuda").manual_seed(11)
