@@ -56,6 +56,34 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 constexpr int GEMV_ROWS = 4;       // output columns per CTA: all 256 threads split K for each of them
 
+__host__ __device__ constexpr int pow2_ceil(int n) { int p = 1; while (p < n) p <<= 1; return p; }
+__host__ __device__ constexpr int ilog2(int n) { int l = 0; while ((1 << l) < n) ++l; return l; }
+
+// Warp-wide sums of NV values per lane (NV a power of two <= 32). Step s pairs lanes 16 >> s apart: the lower lane keeps
+// the first half of its list and the upper lane the second half, each adding the partner's copy of the half it keeps,
+// so after log2(NV) steps lane l holds one value, index l >> (5 - log2 NV), summed over the lanes that share l's low
+// bits; plain butterfly steps over those low bits finish it. NV - 1 + (5 - log2 NV) shuffles instead of 5 NV.
+template <int NV>
+__device__ __forceinline__ float warp_sum_many(float (&v)[NV], int lane) {
+  constexpr int LOG = ilog2(NV);
+  static_assert((1 << LOG) == NV && NV <= 32, "NV must be a power of two <= 32");
+#pragma unroll
+  for (int s = 0; s < LOG; ++s) {
+    const int off = 16 >> s, half = NV >> (s + 1);
+    const bool upper = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < half; ++i) {
+      const float send = upper ? v[i] : v[i + half];
+      const float keep = upper ? v[i + half] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
+  }
+  float r = v[0];
+#pragma unroll
+  for (int off = 16 >> LOG; off >= 1; off >>= 1) r += __shfl_xor_sync(0xffffffffu, r, off);
+  return r;
+}
+
 // MIX: the input row is the layer's mixed residual stream, built on the fly: xm = bf16(lam_r[layer] * x + lam_0[layer] * x0),
 // fed to the dot products as rmsnorm(xm) (norm_input semantics). The first CTA also writes xm (the residual the
 // attention projection adds back) and the first `head_cols` channels of rmsnorm(xm) (the value-embedding gate's input),
@@ -145,17 +173,25 @@ gemv_rows_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_
     for (int r = 0; r < GEMV_ROWS; ++r) wv[r] = ld_stream(W + (long long)min(n0 + r, N - 1) * ldw + k);
     fma_chunk(wv, k);
   }
+  // 4 x B partial dot products per lane: a transposing reduction (the value list halves as the lane distance halves)
+  // sums them with ~4B shuffles instead of 5 per value
+  {
+    constexpr int NV = pow2_ceil(GEMV_ROWS * B), LOW = 5 - ilog2(NV);
+    float flat[NV];
 #pragma unroll
-  for (int b = 0; b < B; ++b) {
+    for (int i = 0; i < NV; ++i) flat[i] = i < GEMV_ROWS * B ? acc[i / B][i % B] : 0.f;
+    const float total = warp_sum_many<NV>(flat, lane);
+    const int idx = lane >> LOW;                                 // the value this lane ends up owning
+    if ((lane & ((1 << LOW) - 1)) == 0 && idx < GEMV_ROWS * B) s_acc[warp][idx / B][idx % B] = total;
+  }
+  if (MIX || norm_input) {
+    constexpr int NB = pow2_ceil(B), LOW = 5 - ilog2(NB);
+    float flat[NB];
 #pragma unroll
-    for (int r = 0; r < GEMV_ROWS; ++r) {
-      const float v = warp_sum(acc[r][b]);
-      if (lane == 0) s_acc[warp][r][b] = v;
-    }
-    if (MIX || norm_input) {
-      const float v = warp_sum(ss[b]);
-      if (lane == 0) s_ss[warp][b] = v;
-    }
+    for (int i = 0; i < NB; ++i) flat[i] = i < B ? ss[i] : 0.f;
+    const float total = warp_sum_many<NB>(flat, lane);
+    const int idx = lane >> LOW;
+    if ((lane & ((1 << LOW) - 1)) == 0 && idx < B) s_ss[warp][idx] = total;
   }
   __syncthreads();
   if (MIX && blockIdx.x == 0 && tid < mix.head_cols * B) {
