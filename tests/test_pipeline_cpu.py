@@ -94,9 +94,10 @@ def test_toy_pipeline_end_to_end(tmp_path):
     assert "Inherited max_seq_len=64" in out and "Loaded optimizer state from pretrained checkpoint" in out
     assert re.search(r"Training mixture: \d+ rows", out) and re.search(r"step 0000\d .*loss: [0-9.]+", out)
     assert os.path.isdir(os.path.join(base, "chatsft_checkpoints", "d2"))
-    out = _run(base, "scripts.chat_eval", "-i", "sft", "-a", "ARC-Easy|GSM8K", "-x", "4", "-m", "8", "-b", "2",
-               "--device-type=cpu")
-    assert re.search(r"ARC-Easy accuracy: [0-9.]+%", out) and re.search(r"GSM8K accuracy: [0-9.]+%", out)
+    out = _run(base, "scripts.chat_eval", "-i", "sft", "-x", "4", "-m", "8", "-b", "2", "--device-type=cpu")   # all tasks
+    for name in ("ARC-Easy", "ARC-Challenge", "MMLU", "GSM8K", "HumanEval"):
+        assert re.search(name + r" accuracy: [0-9.]+%", out), name
+    assert re.search(r"ChatCORE metric: -?[0-9.]+", out)
     out = _run(base, "scripts.chat_rl", "--num-samples=2", "--device-batch-size=2", "--examples-per-step=2",
                "--max-new-tokens=8", "--eval-examples=2", "--eval-every=2", "--save-every=2", "--device-type=cpu")
     assert "Calculated number of steps: 4" in out and re.search(r"Step 0 \| Pass@1: [0-9.]+, Pass@2: [0-9.]+", out)
@@ -172,4 +173,10 @@ def _write_task_data(base):
         for i in range(6)])
     for split in ("train", "validation", "test"):
         put("allenai/ai2_arc", "ARC-Easy", split, arc)
+        put("allenai/ai2_arc", "ARC-Challenge", split, arc)
+    he = pa.Table.from_pylist([
+        {"task_id": f"Toy/{i}", "prompt": f"def add{i}(a, b):\n    \"\"\"Return a + b + {i}.\"\"\"\n",
+         "canonical_solution": f"    return a + b + {i}\n", "entry_point": f"add{i}",
+         "test": f"def check(f):\n    assert f(1, 2) == {3 + i}\n"} for i in range(4)])
+    put("openai/openai_humaneval", "openai_humaneval", "test", he)
 
