@@ -20,6 +20,7 @@
 #include <queue>
 #include <set>
 #include <string>
+#include <string_view>
 #include <thread>
 #include <unordered_map>
 #include <unordered_set>
@@ -55,19 +56,39 @@ void parallel_for(size_t n, int threads, const std::function<void(size_t, size_t
 // ------------------------------------------------------------------------------ trainer
 using WordCounts = std::unordered_map<std::string, long long>;
 
+// Counts the pre-split words of a batch. Threads take texts from a shared counter (documents differ in length by
+// orders of magnitude, so a static split leaves most threads idle), count into private maps keyed by views into the
+// batch (no allocation per occurrence), and the maps are folded into `total`, copying a key only when it is new.
 void count_words(const std::vector<std::string>& texts, int threads, WordCounts& total) {
   const int nt = std::max(1, std::min<int>(threads, static_cast<int>(texts.size())));
-  std::vector<WordCounts> partial(nt);
-  parallel_for(texts.size(), nt, [&](size_t lo, size_t hi, int t) {
+  using ViewCounts = std::unordered_map<std::string_view, long long>;
+  std::vector<ViewCounts> partial(nt);
+  std::atomic<size_t> next{0};
+  auto work = [&](int t) {
     std::vector<std::pair<uint32_t, uint32_t>> pieces;
-    for (size_t i = lo; i < hi; ++i) {
+    ViewCounts& mine = partial[t];
+    for (;;) {
+      const size_t i = next.fetch_add(1);
+      if (i >= texts.size()) return;
       pieces.clear();
       tok::split(texts[i], pieces);
-      for (auto& pc : pieces) partial[t][texts[i].substr(pc.first, pc.second - pc.first)] += 1;
+      const char* base = texts[i].data();
+      for (auto& pc : pieces) mine[std::string_view(base + pc.first, pc.second - pc.first)] += 1;
     }
-  });
+  };
+  if (nt == 1) {
+    work(0);
+  } else {
+    std::vector<std::thread> pool;
+    for (int t = 0; t < nt; ++t) pool.emplace_back(work, t);
+    for (auto& th : pool) th.join();
+  }
   for (auto& m : partial)
-    for (auto& kv : m) total[kv.first] += kv.second;
+    for (auto& kv : m) {
+      auto f = total.find(std::string(kv.first));
+      if (f == total.end()) total.emplace(std::string(kv.first), kv.second);
+      else f->second += kv.second;
+    }
 }
 
 std::vector<std::pair<py::bytes, int>> train_bpe(py::iterator it, int vocab_size, int threads) {
