@@ -111,3 +111,45 @@ def test_save_load_round_trip_and_tiktoken_parity(tok, tmp_path):
                             special_tokens=tok.enc.special_tokens)
     for t in CORPUS[:4] + [text, "  multiple   spaces  \n\n and\ttabs "]:
         assert enc.encode_ordinary(t) == tok.encode(t)
+
+
+# ------------------------------------------------------------- the C++ pieces against independent oracles
+
+def _random_text(rng, n):
+    alphabet = ["a", "b", "Z", "é", "ß", "中", "文", "\U0001f600", " ", "  ", "\n", "\r\n", "\t", "'s", "'T", "'ll", "'x", "1",
+                "23", "4567", "!", "?!", "...", "_", "-", "́", " ", " ", "x" * 9, "I'm", "don't", "WE'VE"]
+    return "".join(rng.choice(alphabet) for _ in range(n))
+
+
+def test_cpp_scanner_splits_like_the_regex_engine():
+    import random
+    import regex
+    from nanochat_b200.tokenizer import SPLIT_PATTERN, _load_cpp
+    cpp = _load_cpp()
+    if cpp is None:
+        pytest.skip("C++ tokenizer extension not available")
+    splitter = regex.compile(SPLIT_PATTERN)
+    rng = random.Random(0)
+    cases = ["", " ", "\n\n", "a  b", "it's  12345 abc", "  leading", "trailing  ", "x\n \ny", "１２３４"]     # incl. full-width digits
+    cases += [_random_text(rng, rng.randint(1, 60)) for _ in range(3000)]
+    for text in cases:
+        got = [p if isinstance(p, bytes) else p.encode("utf-8") for p in cpp.split(text)]
+        want = [m.encode("utf-8") for m in splitter.findall(text)]
+        assert got == want, (text, got, want)
+
+
+@pytest.mark.parametrize("threads", [1, 4])
+def test_cpp_trainer_learns_the_same_merges_as_the_python_oracle(threads):
+    import random
+    from nanochat_b200.tokenizer import SPLIT_PATTERN, _PyBPE, _load_cpp
+    cpp = _load_cpp()
+    if cpp is None:
+        pytest.skip("C++ tokenizer extension not available")
+    rng = random.Random(1)
+    words = ["the", "quick", "brown", "fox", "jumps", "over", "lazy", "dog", "naïve", "中文", "don't", "1234", "x_y", "..."]
+    corpus = [" ".join(rng.choice(words) for _ in range(rng.randint(5, 60))) + rng.choice(["", "\n", "!"]) for _ in range(300)]
+    corpus += ["", " "]
+    vocab = 256 + 120
+    want = _PyBPE.train(iter(corpus), vocab, SPLIT_PATTERN)
+    got = {bytes(b): r for b, r in cpp.train_bpe(iter(corpus), vocab, threads)}
+    assert got == want
