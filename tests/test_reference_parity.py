@@ -88,3 +88,24 @@ def test_checkpoints_load_in_both_directions(tmp_path):
     blob = torch.load(path)
     losses, _, _ = _ours(blob)
     assert all(l == l for l in losses)
+
+
+def _cli_flags(path):
+    import re
+    out = set()
+    with open(path, encoding="utf-8") as f:
+        src = f.read()
+    for m in re.finditer(r"add_argument\(([^)]*)", src):
+        out |= set(re.findall(r"""["'](--?[a-zA-Z][a-zA-Z0-9-]*)["']""", m.group(1)))
+    return out
+
+
+@pytest.mark.parametrize("script", ["base_train", "base_eval", "chat_sft", "chat_rl", "chat_eval", "chat_cli", "tok_train",
+                                    "infer_bench"])
+def test_entry_points_accept_every_flag_of_the_reference(script):
+    ref_path = os.path.join(REF, "scripts", script + ".py")
+    if not os.path.exists(ref_path):
+        pytest.skip("the reference copy carries no scripts")
+    ref = _cli_flags(ref_path)
+    ours = _cli_flags(os.path.join(ROOT, "scripts", script + ".py"))
+    assert ref and not (ref - ours), sorted(ref - ours)
