@@ -57,6 +57,9 @@ class _ColorFormatter(logging.Formatter):
         return out
 
 
+ColoredFormatter = _ColorFormatter     # name used by code written against the reference
+
+
 _logging_ready = False
 
 

@@ -20,6 +20,16 @@ BASE_URL = "https://huggingface.co/datasets/karpathy/climbmix-400b-shuffle/resol
 MAX_SHARD = 6542   # index of the last shard (the validation shard)
 
 
+def __getattr__(name):
+    """`DATA_DIR` and `base_dir` of the reference's module, resolved on access so that NANOCHAT_BASE_DIR set after the
+    import is honoured."""
+    if name == "DATA_DIR":
+        return data_dir()
+    if name == "base_dir":
+        return get_base_dir()
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")
+
+
 def index_to_filename(index):
     return f"shard_{index:05d}.parquet"
 

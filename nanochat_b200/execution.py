@@ -60,6 +60,8 @@ del _lockdown
 exec(compile(%s, "<llm>", "exec"), {"__name__": "__main__"})
 """
 
+GUARD = _PRELUDE        # name used by code written against the reference: the source run in the child before the program
+
 
 def _limit_memory(nbytes):
     """Returns a callable that runs in the child after fork and before exec."""

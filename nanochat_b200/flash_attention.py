@@ -24,6 +24,9 @@ from nanochat_b200 import ops
 from nanochat_b200.ops import reference as ref_ops
 
 _override_impl = None  # 'native' | 'sdpa' | None (auto)
+# The reference's flags for its prebuilt Hopper library; this package never loads it (the sm_100a kernels take its place).
+HAS_FA3 = False
+USE_FA3 = False
 
 
 def _want_native(q):

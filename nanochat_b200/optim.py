@@ -57,6 +57,35 @@ def _use_native(t):
     return t.is_cuda and ops.get_kernel_mode() == "native"
 
 
+def _scalar(v):
+    return float(v.item()) if isinstance(v, torch.Tensor) else float(v)
+
+
+def adamw_step_fused(p, grad, exp_avg, exp_avg_sq, step_t, lr_t, beta1_t, beta2_t, eps_t, wd_t):
+    """One AdamW step in place on `p` and its moments, with the reference's functional signature
+    (reference: nanochat/optim.py:24-63; hyper-parameters as 0-D tensors or numbers). On a B200 this is the fused
+    kernel of `ops/csrc/optim.cu`, elsewhere the plain-PyTorch body."""
+    args = (p, grad, exp_avg, exp_avg_sq, int(_scalar(step_t)), _scalar(lr_t), _scalar(beta1_t), _scalar(beta2_t),
+            _scalar(eps_t), _scalar(wd_t))
+    if _use_native(p):
+        ops.native_module().adamw_update(*args)
+    else:
+        ref_ops.adamw_update(*args)
+
+
+def muon_step_fused(stacked_grads, stacked_params, momentum_buffer, second_momentum_buffer, momentum_t, lr_t, wd_t,
+                    beta2_t, ns_steps, red_dim):
+    """One Muon step on stacked (k, r, c) tensors, in place on the parameters and both buffers, with the reference's
+    functional signature (reference: nanochat/optim.py:112-180). `stacked_grads` is clobbered."""
+    from nanochat_b200 import common
+    args = (stacked_grads, stacked_params, momentum_buffer, second_momentum_buffer, _scalar(momentum_t), _scalar(lr_t),
+            _scalar(wd_t), _scalar(beta2_t), int(ns_steps), int(red_dim))
+    if _use_native(stacked_params):
+        ops.native_module().muon_update(*args)
+    else:
+        ref_ops.muon_update(*args, use_bf16=(common.COMPUTE_DTYPE == torch.bfloat16))
+
+
 class MuonAdamW(torch.optim.Optimizer):
     """param_groups: dicts with 'params', 'kind' ('adamw' | 'muon') and the kind's hyper-parameters
     (adamw: lr, betas, eps, weight_decay; muon: lr, momentum, ns_steps, beta2, weight_decay)."""

@@ -11,6 +11,7 @@ from tasks.common import Task, load_hub_dataset
 
 _FINAL = re.compile(r"#### (\-?[0-9\.\,]+)")
 _CALL = re.compile(r"(<<[^>]+>>)")
+GSM_RE = _FINAL                         # name used by code written against the reference
 
 
 def extract_answer(completion):

@@ -151,3 +151,30 @@ def test_state_dict_round_trip_resumes_identically():
         ob.step()
     for pa, pb in zip(_flat(a), _flat(b)):
         assert torch.equal(pa, pb)
+
+
+def test_functional_steps_with_the_reference_signatures():
+    """`adamw_step_fused` / `muon_step_fused` take the reference's arguments (0-D tensors for the hyper-parameters)."""
+    import torch
+    from nanochat_b200.optim import adamw_step_fused, muon_step_fused
+    torch.manual_seed(0)
+    p = torch.randn(16, 8)
+    q = p.clone().requires_grad_(True)
+    oracle = torch.optim.AdamW([q], lr=0.01, betas=(0.8, 0.95), eps=1e-10, weight_decay=0.1)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    t = lambda x: torch.tensor(float(x))
+    for step in range(1, 6):
+        g = torch.randn(16, 8)
+        q.grad = g.clone()
+        oracle.step()
+        adamw_step_fused(p, g, m, v, t(step), t(0.01), t(0.8), t(0.95), t(1e-10), t(0.1))
+    assert torch.allclose(p, q.detach(), rtol=1e-5, atol=1e-6)
+
+    grads = torch.randn(3, 32, 64)
+    params = torch.randn(3, 32, 64)
+    before = params.clone()
+    mom, second = torch.zeros(3, 32, 64), torch.zeros(3, 32, 1)
+    muon_step_fused(grads.clone(), params, mom, second, t(0.95), t(0.02), t(0.0), t(0.9), 5, -1)
+    update = before - params
+    s = torch.linalg.svdvals(update[0])
+    assert s.max() / s.min() < 4 and mom.abs().sum() > 0 and second.abs().sum() > 0      # near semi-orthogonal step

@@ -109,3 +109,37 @@ def test_entry_points_accept_every_flag_of_the_reference(script):
     ref = _cli_flags(ref_path)
     ours = _cli_flags(os.path.join(ROOT, "scripts", script + ".py"))
     assert ref and not (ref - ours), sorted(ref - ours)
+
+
+def _public_names(path):
+    import ast
+    with open(path, encoding="utf-8") as f:
+        tree = ast.parse(f.read())
+    out = set()
+    for node in tree.body:
+        if isinstance(node, (ast.FunctionDef, ast.ClassDef)):
+            out.add(node.name)
+        elif isinstance(node, ast.Assign):
+            out |= {t.id for t in node.targets if isinstance(t, ast.Name)}
+    return {n for n in out if not n.startswith("_")}
+
+
+@pytest.mark.parametrize("ref_mod,our_mod", [
+    ("nanochat/common.py", "nanochat_b200.common"), ("nanochat/gpt.py", "nanochat_b200.models.gpt"),
+    ("nanochat/flash_attention.py", "nanochat_b200.flash_attention"), ("nanochat/fp8.py", "nanochat_b200.fp8"),
+    ("nanochat/optim.py", "nanochat_b200.optim"), ("nanochat/engine.py", "nanochat_b200.engine"),
+    ("nanochat/execution.py", "nanochat_b200.execution"), ("nanochat/tokenizer.py", "nanochat_b200.tokenizer"),
+    ("nanochat/dataset.py", "nanochat_b200.dataset"), ("nanochat/dataloader.py", "nanochat_b200.dataloader"),
+    ("nanochat/core_eval.py", "nanochat_b200.core_eval"), ("nanochat/loss_eval.py", "nanochat_b200.loss_eval"),
+    ("nanochat/checkpoint_manager.py", "nanochat_b200.checkpoint_manager"), ("tasks/common.py", "tasks.common"),
+    ("tasks/arc.py", "tasks.arc"), ("tasks/mmlu.py", "tasks.mmlu"), ("tasks/gsm8k.py", "tasks.gsm8k"),
+    ("tasks/humaneval.py", "tasks.humaneval"), ("tasks/smoltalk.py", "tasks.smoltalk")])
+def test_every_public_name_of_the_reference_exists_here(ref_mod, our_mod, tmp_path, monkeypatch):
+    import importlib
+    path = os.path.join(REF, ref_mod)
+    if not os.path.exists(path):
+        pytest.skip("module not in the reference copy")
+    monkeypatch.setenv("NANOCHAT_BASE_DIR", str(tmp_path))          # names resolved on access may touch the base dir
+    ours = importlib.import_module(our_mod)
+    missing = sorted(n for n in _public_names(path) if not hasattr(ours, n))
+    assert not missing, missing
