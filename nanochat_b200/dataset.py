@@ -38,10 +38,13 @@ def data_dir():
     return os.path.join(get_base_dir(), "base_data_climbmix")
 
 
-def list_parquet_files(data_dir_override=None, warn_on_legacy=False):
+_default_data_dir = data_dir
+
+
+def list_parquet_files(data_dir=None, warn_on_legacy=False):
     """Sorted full paths of the shards on disk. Falls back to the older `base_data` directory when the
     ClimbMix directory does not exist."""
-    d = data_dir() if data_dir_override is None else data_dir_override
+    d = _default_data_dir() if data_dir is None else data_dir      # the parameter keeps the reference's name
     if not os.path.exists(d):
         if warn_on_legacy:
             print(f"WARNING: {d} not found; run `python -m nanochat_b200.dataset -n 170` and re-train the "
