@@ -42,6 +42,9 @@ def parse_args():
     ap.add_argument("--total-batch-size", type=int, default=1048576)
     ap.add_argument("--window-pattern", type=str, default="SSSL")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end region (debugging)")
+    ap.add_argument("--no-decode", action="store_true",
+                    help="skip the Engine decode sweep that is appended to the 1-GPU record")
+    ap.add_argument("--decode-tokens", type=int, default=256)
     ap.add_argument("--comm", type=str, default="auto", choices=["auto", "fused", "nccl"],
                     help="optimizer collectives for N>1: fused peer-to-peer kernels or NCCL")
     ap.add_argument("--precision", type=str, default="fp8", choices=["fp8", "bf16"],
@@ -130,6 +133,45 @@ def timed_region(torch, dist, world, steps, run_step):
     return ms.item()
 
 
+def shared_config(args, world, accum):
+    """The benchmark configuration: the same keys and values in both arms."""
+    return {"model": f"d{args.depth}", "global_batch": args.total_batch_size, "seq_len": args.seq_len,
+            "device_batch": args.device_batch_size, "grad_accum": accum, "window_pattern": args.window_pattern,
+            "parallelism": f"dp{world}",
+            "l2": "inputs larger than L2 (activations of one micro-batch exceed 126 MB)"}
+
+
+def losses_of(loss_log, args):
+    """Last-micro-batch training loss of every step this process ran, in order: warm-up, timed, end-to-end
+    (one extra untimed step opens the end-to-end region). Same seeds and data in both arms."""
+    vals = [float(v) for v in loss_log]
+    w, k = args.warmup, args.steps
+    return {"warmup": vals[:w], "timed": vals[w:w + k], "e2e": vals[w + k:]}
+
+
+def decode_sweep(args, impl):
+    """Engine decode at the benchmark depth (bf16 random-init weights, 512-token prompt, temperature 1.0, top-k 50,
+    batch 1/8/32/64) through scripts/infer_bench.py in a child process; returns its JSON record."""
+    cmd = [sys.executable, "-m", "scripts.infer_bench", "--random-init", "--depth", str(args.depth),
+           "--prompt-tokens", "512", "--decode-tokens", str(args.decode_tokens), "--batch-sizes", "1,8,32,64",
+           "-t", "1.0", "-k", "50", "--impl", impl]
+    env = dict(os.environ)
+    for k in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT"):
+        env.pop(k, None)
+    try:
+        r = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=900)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "decode sweep timed out"}
+    lines = [ln for ln in r.stdout.strip().splitlines() if ln.startswith("{")]
+    if r.returncode != 0 or not lines:
+        return {"unavailable": f"decode sweep failed (exit {r.returncode}): {r.stderr.strip()[-300:]}"}
+    rec = json.loads(lines[-1])
+    keep = ("impl", "prompt_tokens", "decode_tokens", "temperature", "top_k", "prefill", "sweep", "unavailable")
+    out = {k: rec[k] for k in keep if k in rec}
+    out["command"] = " ".join(cmd[1:])
+    return out
+
+
 def build_ours(args, device):
     import torch
     from nanochat_b200.models.gpt import GPT, GPTConfig
@@ -162,20 +204,10 @@ def run_ours(args):
     B, T = args.device_batch_size, args.seq_len
     assert args.total_batch_size % (B * T * world) == 0
     accum = args.total_batch_size // (B * T * world)
-    comm, comm_name = None, "none (1 GPU)"
-    if world > 1:
-        comm_name = "nccl"
-        if args.comm in ("auto", "fused"):
-            try:
-                from nanochat_b200.parallel.symm import SymmComm
-                comm = SymmComm.create(model)
-                comm_name = "fused peer-to-peer kernels (symmetric memory over NVLink)"
-            except Exception as e:
-                if args.comm == "fused":
-                    raise
-                print(f"[bench] fused optimizer path unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
-                comm = None
-    trainer = TrainStep(model, grad_accum=accum, comm=comm, matrix_lr=0.02, weight_decay=0.1)
+    # the object the training scripts drive (scripts/base_train.py, chat_sft.py, chat_rl.py): arena, collectives, step
+    trainer = TrainStep(model, grad_accum=accum, comm=args.comm if world > 1 else None, matrix_lr=0.02, weight_decay=0.1,
+                        log=lambda m: print(f"[bench] {m}", file=sys.stderr))
+    comm_name = trainer.comm_name or "none (1 GPU)"
     flops_per_token = model.estimate_flops()
 
     gen = torch.Generator(device="cpu").manual_seed(1234 + rank)
@@ -185,8 +217,10 @@ def run_ours(args):
     dev = [h.to(device) for h in host]
     staging = [torch.empty_like(dev[0]) for _ in range(2)]
 
+    loss_log = []                     # device scalars; read back after the timed regions
+
     def step_device():
-        trainer.step(lambda i: (dev[i % n_buf][0], dev[i % n_buf][1]))
+        loss_log.append(trainer.step(lambda i: (dev[i % n_buf][0], dev[i % n_buf][1])))
 
     last_loss = [None]
 
@@ -197,6 +231,7 @@ def run_ours(args):
             return buf[0], buf[1]
         loss = trainer.step(fetch)
         last_loss[0] = loss.item()                           # D2H read of the step's loss
+        loss_log.append(last_loss[0])
 
     for _ in range(args.warmup):
         step_device()
@@ -257,20 +292,26 @@ def run_ours(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": tok_s / PUBLISHED_TOK_PER_SEC, "dtype": dtype, "data": "synthetic",
         "impl": "ours",
-        "config": {"model": f"d{args.depth}", "global_batch": args.total_batch_size, "seq_len": T,
-                   "device_batch": B, "grad_accum": accum, "window_pattern": args.window_pattern,
-                   "parallelism": f"dp{world}", "optimizer": "MuonAdamW (ZeRO-2 sharded)", "optimizer_comm": comm_name,
-                   "l2": "inputs larger than L2 (activations of one micro-batch exceed 126 MB)",
-                   "attention": nat.ATTENTION_IMPL},
+        "config": shared_config(args, world, accum),
+        "arm": {"optimizer": "MuonAdamW (ZeRO-2 sharded)", "optimizer_comm": comm_name, "attention": nat.ATTENTION_IMPL,
+                "step": "nanochat_b200.train.TrainStep (the loop body of scripts/base_train.py)",
+                "fp8_layer_passes": nat.stats["fp8_layer_forward"], "bf16_layer_passes": nat.stats["bf16_layer_forward"]},
+        "losses": losses_of(loss_log, args),
         "mfu_bf16_nominal": flops_per_token * tok_s / (world * 2.25e15),
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches, "peak_mem_gib": peak_mem,
         "optimizer_step": opt,
     }
     if phases:
         out["phases_ms_per_step"] = phases
-    if rank == 0:
-        print(json.dumps(out))
     common.compute_cleanup()
+    if rank == 0:
+        if world == 1 and not args.no_decode:
+            del trainer, model, dev, staging, host
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+            out["decode"] = decode_sweep(args, "ours")
+        print(json.dumps(out))
 
 
 def run_reference(args):
@@ -335,8 +376,10 @@ def run_reference(args):
         model.zero_grad(set_to_none=True)
         return loss.detach()
 
+    loss_log = []
+
     def step_device():
-        train_step(lambda i: (dev[i % n_buf][0], dev[i % n_buf][1]))
+        loss_log.append(train_step(lambda i: (dev[i % n_buf][0], dev[i % n_buf][1])))
 
     last_loss = [None]
 
@@ -346,6 +389,7 @@ def run_reference(args):
             buf.copy_(host[i % n_buf], non_blocking=True)
             return buf[0], buf[1]
         last_loss[0] = train_step(fetch).item()
+        loss_log.append(last_loss[0])
 
     try:
         for _ in range(args.warmup):
@@ -362,6 +406,7 @@ def run_reference(args):
         model = orig_model
         compiled = False
         model.zero_grad(set_to_none=True)
+        del loss_log[:]
         for _ in range(args.warmup):
             step_device()
     sampler = ClockSampler(local_rank)
@@ -381,16 +426,22 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": tok_s / PUBLISHED_TOK_PER_SEC, "dtype": dtype, "data": "synthetic",
         "impl": "reference",
-        "config": {"model": f"d{args.depth}", "global_batch": args.total_batch_size, "seq_len": T,
-                   "device_batch": B, "grad_accum": accum, "window_pattern": args.window_pattern,
-                   "parallelism": f"dp{world}", "torch_compile": compiled,
-                   "l2": "inputs larger than L2 (activations of one micro-batch exceed 126 MB)"},
+        "config": shared_config(args, world, accum),
+        "arm": {"optimizer": "the reference's MuonAdamW / DistMuonAdamW", "optimizer_comm": "nccl" if world > 1 else "none (1 GPU)",
+                "attention": "torch SDPA (the reference's path on a non-Hopper GPU)", "torch_compile": compiled},
+        "losses": losses_of(loss_log, args),
         "mfu_bf16_nominal": orig_model.estimate_flops() * tok_s / (world * 2.25e15),
         "clocks": clocks, "e2e": e2e, "peak_mem_gib": torch.cuda.max_memory_allocated() / 2**30,
     }
-    if rank == 0:
-        print(json.dumps(out))
     compute_cleanup()
+    if rank == 0:
+        if world == 1 and not args.no_decode:
+            del model, orig_model, optimizer, dev, staging, host
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()
+            out["decode"] = decode_sweep(args, "reference")
+        print(json.dumps(out))
 
 
 if __name__ == "__main__":

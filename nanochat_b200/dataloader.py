@@ -119,6 +119,10 @@ def tokenizing_distributed_data_loader_with_state_bos_bestfit(
     pinned = [torch.empty(2 * B * T, dtype=torch.long, pin_memory=use_cuda) for _ in range(n_slots)]
     on_dev = [torch.empty(2 * B * T, dtype=torch.long, device=device) for _ in range(n_slots)]
     copy_stream = torch.cuda.Stream() if use_cuda else None
+    # released[slot]: recorded on the consumer's stream when it is done issuing work on that slot's batch. Host-side
+    # queue order alone does not stop a later copy from overwriting a batch whose kernels are still queued (the
+    # embedding backward reads the token ids last), so the copy stream waits for this event before it refills a slot.
+    released = [None] * n_slots
 
     def build(slot):
         if packer is not None:
@@ -181,6 +185,8 @@ def tokenizing_distributed_data_loader_with_state_bos_bestfit(
                 raise err
             dst = on_dev[slot]
             if use_cuda:
+                if released[slot] is not None:
+                    copy_stream.wait_event(released[slot])
                 with torch.cuda.stream(copy_stream):
                     dst.copy_(pinned[slot], non_blocking=True)
                     done = torch.cuda.Event()
@@ -190,6 +196,9 @@ def tokenizing_distributed_data_loader_with_state_bos_bestfit(
             else:
                 dst.copy_(pinned[slot])
             if previous is not None:
+                if use_cuda:                # everything the consumer queued on the previous batch is ahead of this mark
+                    released[previous] = torch.cuda.Event()
+                    released[previous].record(torch.cuda.current_stream())
                 free.put(previous)          # the consumer is done with the batch handed out before this one
             previous = slot
             yield dst[:B * T].view(B, T), dst[B * T:].view(B, T), snapshot
@@ -211,15 +220,24 @@ def tokenizing_distributed_data_loader_bos_bestfit(*args, **kwargs):
         yield inputs, targets
 
 
-def synthetic_token_loader(B, T, vocab_size, device="cuda", seed=0):
-    """Uniform-random token batches of the training shape (for benchmarks without a corpus)."""
+def synthetic_token_loader(B, T, vocab_size, device="cuda", seed=0, cycle=0):
+    """Uniform-random token batches of the training shape (for benchmarks without a corpus). `cycle` > 0 repeats
+    the first `cycle` batches forever (a memorisable stream: tests use it to see the loss fall)."""
     _, rank, _, _ = get_dist_info()
     gen = torch.Generator(device="cpu").manual_seed(seed + rank)
     state = {"pq_idx": 0, "rg_idx": 0, "epoch": 1}
     use_cuda = torch.device(device).type == "cuda"
+    kept = []
+    i = 0
     while True:
-        rows = torch.randint(0, vocab_size, (B, T + 1), generator=gen, dtype=torch.long)
-        if use_cuda:
-            rows = rows.pin_memory()
-        rows = rows.to(device, non_blocking=use_cuda)
-        yield rows[:, :-1].contiguous(), rows[:, 1:].contiguous(), state
+        if cycle > 0 and len(kept) == cycle:
+            rows = kept[i % cycle]
+        else:
+            rows = torch.randint(0, vocab_size, (B, T + 1), generator=gen, dtype=torch.long)
+            if use_cuda:
+                rows = rows.pin_memory()
+            if cycle > 0:
+                kept.append(rows)
+        i += 1
+        dev_rows = rows.to(device, non_blocking=use_cuda)
+        yield dev_rows[:, :-1].contiguous(), dev_rows[:, 1:].contiguous(), state

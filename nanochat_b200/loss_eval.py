@@ -34,3 +34,23 @@ def evaluate_bpb(model, batches, steps, token_bytes):
     if total_bytes == 0:
         return float("inf")
     return nats.item() / (math.log(2) * total_bytes)
+
+
+@torch.no_grad()
+def evaluate_mean_loss(model, batches, steps):
+    """Mean cross entropy per target token over `steps` batches of every rank (nats). The loaders' third item
+    (their state), if present, is ignored."""
+    device = model.get_device()
+    total = torch.zeros((), dtype=torch.float64, device=device)
+    count = torch.zeros((), dtype=torch.float64, device=device)
+    it = iter(batches)
+    for _ in range(steps):
+        x, y = next(it)[:2]
+        loss = model(x, y, loss_reduction="none").view(-1)
+        valid = y.view(-1) >= 0
+        total += (loss.double() * valid).sum()
+        count += valid.sum()
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        dist.all_reduce(total, op=dist.ReduceOp.SUM)
+        dist.all_reduce(count, op=dist.ReduceOp.SUM)
+    return (total / count.clamp_min(1)).item()

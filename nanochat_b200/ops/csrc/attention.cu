@@ -344,12 +344,11 @@ static bool make_qkv_map(CUtensorMap* m, const void* base, int T, int Hn, int B,
 
 cudaError_t attention_fwd(const AttnDesc& d, int* status, cudaStream_t stream) {
   if (d.D != 128 || d.H % d.Hkv != 0 || d.Tq > d.Tk) return cudaErrorInvalidValue;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  static PerDeviceOnce configured;
+  cudaError_t ce = configured.once([] {
+    return cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, attn::SMEM_BYTES);
+  });
+  if (ce != cudaSuccess) return ce;
   CUtensorMap tmQ, tmK, tmV;
   if (!make_qkv_map(&tmQ, d.q, d.Tq, d.H, d.B, d.q_tok, d.q_head, d.q_bat)) return cudaErrorInvalidValue;
   if (!make_qkv_map(&tmK, d.k, d.Tk, d.Hkv, d.B, d.k_tok, d.k_head, d.k_bat)) return cudaErrorInvalidValue;

@@ -434,21 +434,15 @@ static bool map4(CUtensorMap* m, const void* base, int T, int Hn, int B, long lo
 cudaError_t attention_bwd(const AttnBwdDesc& d, int* status, cudaStream_t stream) {
   const AttnDesc& f = d.fwd;
   if (f.D != 128 || f.H % f.Hkv != 0 || f.Tq > f.Tk) return cudaErrorInvalidValue;
-  static bool configured = false;
-  if (!configured) {
+  static PerDeviceOnce configured;
+  cudaError_t ce = configured.once([] {
     cudaError_t e = cudaFuncSetAttribute(attn_bwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ab::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    e = cudaFuncSetAttribute(attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ab::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
-  {
-    const long long rows = (long long)f.B * f.Tq * f.H;
-    const int grid = (int)((rows + 3) / 4 < 148 * 16 ? (rows + 3) / 4 : 148 * 16);
-    attn_delta_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)f.o, (const __nv_bfloat16*)d.d_o, f.o_bat,
-                                                f.o_tok, f.o_head, d.do_bat, d.do_tok, d.do_head, d.delta, f.B,
-                                                f.Tq, f.H);
-  }
+    return cudaFuncSetAttribute(attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ab::SMEM_BYTES);
+  });
+  if (ce != cudaSuccess) return ce;
+  // The tensor maps are encoded before anything is launched: the encoder rejects misaligned bases and strides,
+  // so a bad layout is an error return here, not a fault in the pre-pass below.
   CUtensorMap q128, do128, k128, v128, q64, do64, k64, v64;
   bool okm = map4(&q128, f.q, f.Tq, f.H, f.B, f.q_tok, f.q_head, f.q_bat, 128) &&
              map4(&do128, d.d_o, f.Tq, f.H, f.B, d.do_tok, d.do_head, d.do_bat, 128) &&
@@ -459,6 +453,13 @@ cudaError_t attention_bwd(const AttnBwdDesc& d, int* status, cudaStream_t stream
              map4(&k64, f.k, f.Tk, f.Hkv, f.B, f.k_tok, f.k_head, f.k_bat, 64) &&
              map4(&v64, f.v, f.Tk, f.Hkv, f.B, f.v_tok, f.v_head, f.v_bat, 64);
   if (!okm) return cudaErrorInvalidValue;
+  {
+    const long long rows = (long long)f.B * f.Tq * f.H;
+    const int grid = (int)((rows + 3) / 4 < 148 * 16 ? (rows + 3) / 4 : 148 * 16);
+    attn_delta_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)f.o, (const __nv_bfloat16*)d.d_o, f.o_bat,
+                                                f.o_tok, f.o_head, d.do_bat, d.do_tok, d.do_head, d.delta, f.B,
+                                                f.Tq, f.H);
+  }
   AttnBwdArgs a;
   a.lse = f.lse; a.delta = d.delta;
   a.Tq = f.Tq; a.Tk = f.Tk; a.H = f.H; a.Hkv = f.Hkv; a.window = f.window;

@@ -4,7 +4,11 @@
 #include "attention.h"
 #include "attention_noalloc.h"
 
+#include <stdint.h>
 #include <stdio.h>
+
+#include <atomic>
+#include <mutex>
 
 namespace {
 
@@ -16,7 +20,10 @@ static __device__ __align__(256) int g_noalloc_status[4];
 constexpr int kMaxDevices = 64;
 float* g_delta_ptr[kMaxDevices];
 int* g_status_ptr[kMaxDevices];
-bool g_ready[kMaxDevices];
+// Set last, with release order, after both addresses above are written; readers load it with acquire order. The
+// mutex makes the first call on a device from several host threads resolve the addresses exactly once.
+std::atomic<bool> g_ready[kMaxDevices];
+std::mutex g_setup_mutex;
 thread_local char g_last_error[256] = "";
 
 int fail(int code, const char* what, cudaError_t e = cudaSuccess) {
@@ -31,15 +38,18 @@ int setup_current_device(int* dev_out) {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(NC_NOALLOC_CUDA_ERROR, "cudaGetDevice", e);
   if (dev < 0 || dev >= kMaxDevices) return fail(NC_NOALLOC_BAD_ARGUMENT, "device index out of range");
-  if (!g_ready[dev]) {
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_noalloc_delta);
-    if (e != cudaSuccess) return fail(NC_NOALLOC_CUDA_ERROR, "cudaGetSymbolAddress(delta scratch)", e);
-    g_delta_ptr[dev] = static_cast<float*>(p);
-    e = cudaGetSymbolAddress(&p, g_noalloc_status);
-    if (e != cudaSuccess) return fail(NC_NOALLOC_CUDA_ERROR, "cudaGetSymbolAddress(status word)", e);
-    g_status_ptr[dev] = static_cast<int*>(p);
-    g_ready[dev] = true;
+  if (!g_ready[dev].load(std::memory_order_acquire)) {
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    if (!g_ready[dev].load(std::memory_order_relaxed)) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_delta);
+      if (e != cudaSuccess) return fail(NC_NOALLOC_CUDA_ERROR, "cudaGetSymbolAddress(delta scratch)", e);
+      g_delta_ptr[dev] = static_cast<float*>(p);
+      e = cudaGetSymbolAddress(&p, g_noalloc_status);
+      if (e != cudaSuccess) return fail(NC_NOALLOC_CUDA_ERROR, "cudaGetSymbolAddress(status word)", e);
+      g_status_ptr[dev] = static_cast<int*>(p);
+      g_ready[dev].store(true, std::memory_order_release);
+    }
   }
   *dev_out = dev;
   return NC_NOALLOC_OK;
@@ -56,6 +66,22 @@ extern "C" int nc_attention_bwd_noalloc(const void* q, const void* k, const void
   g_last_error[0] = 0;
   if (B <= 0 || Tq <= 0 || Tk <= 0 || H <= 0 || Hkv <= 0 || H % Hkv != 0 || Tq > Tk)
     return fail(NC_NOALLOC_BAD_ARGUMENT, "need B,Tq,Tk,H,Hkv > 0, H divisible by Hkv and Tq <= Tk");
+  // Everything the kernels assume about the caller's memory is checked here, before anything is launched: they read
+  // and write 16-byte vectors, so a null or misaligned base, or a stride that is not a whole number of such vectors,
+  // is refused instead of becoming a device fault.
+  const void* ptrs[] = {q, k, v, o, lse, d_o, dq, dk, dv};
+  for (const void* p : ptrs) {
+    if (p == nullptr) return fail(NC_NOALLOC_BAD_ARGUMENT, "null tensor pointer");
+    if (reinterpret_cast<uintptr_t>(p) % 16 != 0)
+      return fail(NC_NOALLOC_BAD_ARGUMENT, "tensor pointers must be 16-byte aligned");
+  }
+  const long long strides[] = {q_bat, q_tok, q_head, kv_bat, kv_tok, kv_head, o_bat, o_tok, o_head};
+  for (long long st : strides) {
+    if (st <= 0 || st % 8 != 0)
+      return fail(NC_NOALLOC_BAD_ARGUMENT, "strides must be positive multiples of 8 elements (16 bytes)");
+  }
+  if (q_head < 128 || kv_head < 128 || o_head < 128)
+    return fail(NC_NOALLOC_BAD_ARGUMENT, "head stride smaller than the head dimension (128)");
   const long long need = 1ll * B * H * Tq;
   if (need > NC_NOALLOC_MAX_DELTA) {
     snprintf(g_last_error, sizeof(g_last_error),

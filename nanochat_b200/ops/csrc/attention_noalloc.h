@@ -20,6 +20,10 @@
 //     in it has to start at zero (the pre-pass overwrites the B*H*Tq entries the kernels read).
 //     Two calls that overlap in time on the same GPU (different streams) race on it: serialise them.
 //   * Inputs and outputs are still the caller's: q, k, v, o, lse, d_o are read; dq, dk, dv written.
+//     Pointers must be non-null and 16-byte aligned, strides positive multiples of 8 elements; anything
+//     else is refused with NC_NOALLOC_BAD_ARGUMENT before a kernel is launched.
+//   * The first call on a device may come from any host thread; concurrent first calls resolve the
+//     address once (the set-up is guarded by a mutex).
 #pragma once
 
 #include <cuda_runtime.h>
@@ -33,7 +37,7 @@ extern "C" {
 enum {
   NC_NOALLOC_OK = 0,
   NC_NOALLOC_TOO_LARGE = 1,      // B*H*Tq > NC_NOALLOC_MAX_DELTA
-  NC_NOALLOC_BAD_ARGUMENT = 2,   // unsupported head dim / head grouping / Tq > Tk
+  NC_NOALLOC_BAD_ARGUMENT = 2,   // unsupported head grouping / Tq > Tk / null or misaligned pointer / bad stride
   NC_NOALLOC_CUDA_ERROR = 3,     // a CUDA call failed; see nc_noalloc_last_error()
   NC_NOALLOC_WAIT_TIMEOUT = 4,   // reported by nc_noalloc_status(): a bounded in-kernel wait gave up
 };
@@ -53,7 +57,9 @@ int nc_attention_bwd_noalloc(const void* q, const void* k, const void* v, const 
                              int window, float scale, cudaStream_t stream);
 
 // Synchronises `stream` and returns NC_NOALLOC_OK, or NC_NOALLOC_WAIT_TIMEOUT if a kernel launched
-// through the entry point above abandoned a wait since the last query (the word is then cleared).
+// through the entry point above abandoned a wait since the last query. The word is then cleared by a
+// memset queued on `stream`: it is ordered before later work on that stream only, so a launch on another
+// stream right after this call may still see (and re-report) the old value.
 int nc_noalloc_status(cudaStream_t stream);
 
 // Text of the last error returned on this thread ("" if none).

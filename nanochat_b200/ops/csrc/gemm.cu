@@ -598,13 +598,11 @@ static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t strea
   using C = Cfg<BN, A_MN, B_MN, FP8>;
   constexpr int BK = C::BK;
   constexpr int ELT = C::ELT;
-  static bool configured = false;
+  static PerDeviceOnce configured;
   auto kern = gemm_kernel<BN, A_MN, B_MN, FP8>;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  cudaError_t ce = configured.once(
+      [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES); });
+  if (ce != cudaSuccess) return ce;
   const CUtensorMapDataType dt = FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tmA, tmB;
   const uint64_t batch = static_cast<uint64_t>(d.batch);
@@ -660,13 +658,11 @@ static cudaError_t launch_pair_cfg(const GemmDesc& d, int* status, cudaStream_t 
   using C = PairCfg<BN, A_MN, B_MN, FP8>;
   constexpr int BK = C::BK;
   constexpr int ELT = Cfg<BN, A_MN, B_MN, FP8>::ELT;
-  static bool configured = false;
+  static PerDeviceOnce configured;
   auto kern = gemm_pair_kernel<BN, A_MN, B_MN, FP8>;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES);
-    if (e != cudaSuccess) return e;
-    configured = true;
-  }
+  cudaError_t ce = configured.once(
+      [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES); });
+  if (ce != cudaSuccess) return ce;
   const CUtensorMapDataType dt = FP8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tmA, tmB;
   const uint64_t batch = static_cast<uint64_t>(d.batch);

@@ -8,7 +8,28 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <atomic>
+
 namespace nc {
+
+// Per-device "configured" flags. A kernel attribute (the raised dynamic shared-memory limit) belongs to one device,
+// so a process that drives several GPUs has to set it on each; `once(f)` runs f for the current device until it has
+// succeeded there once. Two threads racing on the first call both run f, which is idempotent.
+struct PerDeviceOnce {
+  static constexpr int kMax = 64;
+  std::atomic<unsigned char> done[kMax] = {};
+  template <class F>
+  cudaError_t once(F&& f) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMax) return f();
+    if (done[dev].load(std::memory_order_acquire)) return cudaSuccess;
+    e = f();
+    if (e == cudaSuccess) done[dev].store(1, std::memory_order_release);
+    return e;
+  }
+};
 
 inline PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;

@@ -50,6 +50,10 @@ def check_status(like=None):
         raise RuntimeError(f"nanochat_b200 kernel reported a failed wait: code={code} detail={detail}")
 
 
+# host-side counters of which path the fused layer took (drivers print them; tests assert on them)
+stats = {"fp8_layer_forward": 0, "bf16_layer_forward": 0, "fused_qkv_forward": 0}
+
+
 def launch_count():
     """Number of kernels this extension has launched in this process (host-side counter)."""
     return _C.launch_count()
@@ -535,6 +539,8 @@ class _LayerFn(Function):
         amax_xn = _zeroed_scalar(dev) if fp8 else None
         _C.mixnorm_fwd(x2, x02, resid_lambdas, x0_lambdas, layer, xm, xn, amax_xn)
 
+        stats["fp8_layer_forward" if fp8 else "bf16_layer_forward"] += 1
+        stats["fused_qkv_forward"] += fused_w is not None
         qkv = torch.empty(M, nq + 2 * nkv, dtype=BF16, device=dev)
         f8 = None          # fp8 copies of the GEMM inputs, kept for the weight-gradient GEMMs
         if fp8:

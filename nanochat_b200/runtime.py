@@ -93,6 +93,14 @@ class DecodeGraph:
             self.w[i].update(o=f["o"], fc=f["fc"], pr=f["pr"])
         self.lm_head = lm_head
         self.weights_epoch = epoch
+        # tensors the step reads where they live: if any of them was re-homed since the capture (a parameter arena
+        # built later, a checkpoint loaded with assign=True) the captured addresses are stale and the graph is dropped
+        where = tuple(t.data_ptr() for w in self.w for t in (w["o"], w["fc"], w["pr"])) + (
+            lm_head.data_ptr(), m.transformer.wte.weight.data_ptr(),
+            *[ve.weight.data_ptr() for ve in m.value_embeds.values()])
+        if where != getattr(self, "_captured_where", where):
+            self.graph, self.warm = None, False
+        self._captured_where = where
 
     # --------------------------------------------------------------------- step
     def _linear(self, x, w, out, aux=None, relu2=False, norm_input=False):

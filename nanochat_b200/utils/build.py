@@ -13,7 +13,9 @@ command line with `python -m nanochat_b200.utils.build`.
 import os
 import sys
 import glob
+import fcntl
 import hashlib
+import contextlib
 import importlib.util
 import subprocess
 import sysconfig
@@ -58,6 +60,33 @@ def _stale(so_path, digest):
         return f.read().strip() != digest
 
 
+@contextlib.contextmanager
+def _build_lock():
+    """Exclusive lock over check + compile + link + stamp. Every rank of a multi-process job imports the package; on
+    a fresh checkout (or after a source edit) all of them find the build stale, and without the lock they would
+    compile into the same object files and load a library another rank is still writing. The first rank through
+    builds, the others wait here and then find the stamp current."""
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    with open(os.path.join(BUILD_DIR, ".lock"), "w") as f:
+        fcntl.flock(f, fcntl.LOCK_EX)
+        try:
+            yield
+        finally:
+            fcntl.flock(f, fcntl.LOCK_UN)
+
+
+def _write_stamp(so_path, digest):
+    tmp = so_path + ".hash.tmp"
+    with open(tmp, "w") as f:
+        f.write(digest)
+    os.replace(tmp, so_path + ".hash")
+
+
+# Optimizer and collective kernels keep IEEE division / square root and denormals: their state (second moments,
+# running norms) lives for the whole run, and approximate math there shows up as drift, not as noise.
+PRECISE_SOURCES = ("optim.cu", "comm.cu")
+
+
 def _load(name, so_path):
     spec = importlib.util.spec_from_file_location(name, so_path)
     mod = importlib.util.module_from_spec(spec)
@@ -75,16 +104,23 @@ def cuda_sources():
 def build_cuda_extension(verbose=False, force=False):
     """Compile every .cu for sm_100a and link `_C`. Returns the path of the shared object."""
     import torch
-    from torch.utils import cpp_extension as ce
     name = "_C"
     so_path = os.path.join(PKG_DIR, name + EXT_SUFFIX)
     cus, cpps = cuda_sources()
     headers = glob.glob(os.path.join(CSRC, "*.h")) + glob.glob(os.path.join(CSRC, "*.cuh"))
     extra_flags = os.environ.get("NANOCHAT_NVCC_FLAGS", "").split()     # e.g. -DNC_ATTN_TRACE for kernel timelines
-    digest = _hash_files(cus + cpps + headers, extra=torch.__version__ + " ".join(extra_flags))
+    digest = _hash_files(cus + cpps + headers, extra=torch.__version__ + " ".join(extra_flags) + " precise:" + ",".join(PRECISE_SOURCES))
     if not force and not _stale(so_path, digest):
         return so_path
-    os.makedirs(BUILD_DIR, exist_ok=True)
+    with _build_lock():
+        if not force and not _stale(so_path, digest):      # another process built it while this one waited
+            return so_path
+        return _build_cuda_locked(name, so_path, cus, cpps, extra_flags, digest, verbose)
+
+
+def _build_cuda_locked(name, so_path, cus, cpps, extra_flags, digest, verbose):
+    import torch
+    from torch.utils import cpp_extension as ce
     incs = []
     for p in ce.include_paths("cuda"):
         incs += ["-I", p]
@@ -96,7 +132,8 @@ def build_cuda_extension(verbose=False, force=False):
     jobs = []
     for src in cus:
         obj = os.path.join(BUILD_DIR, os.path.basename(src) + ".o")
-        cmd = [nvcc, *NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", "--use_fast_math", "-Xcompiler", "-fPIC",
+        fast = [] if os.path.basename(src) in PRECISE_SOURCES else ["--use_fast_math"]
+        cmd = [nvcc, *NVCC_ARCH, "-lineinfo", "-O3", "-std=c++17", *fast, "-Xcompiler", "-fPIC",
                "-Xptxas", "-v" if verbose else "-O3", *extra_flags, "-I", CSRC, "-c", src, "-o", obj]
         jobs.append((cmd, obj))
     for src in cpps:
@@ -112,11 +149,12 @@ def build_cuda_extension(verbose=False, force=False):
     libs = []
     for p in ce.library_paths("cuda"):
         libs += ["-L", p, f"-Wl,-rpath,{p}"]
-    link = ["g++", "-shared", "-o", so_path, *[j[1] for j in jobs], *libs,
+    tmp_so = so_path + ".tmp"           # link under another name: a process that already mapped the old file keeps it
+    link = ["g++", "-shared", "-o", tmp_so, *[j[1] for j in jobs], *libs,
             "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python", "-lcudart"]
     _run(link)
-    with open(so_path + ".hash", "w") as f:
-        f.write(digest)
+    os.replace(tmp_so, so_path)
+    _write_stamp(so_path, digest)
     return so_path
 
 
@@ -152,11 +190,15 @@ def build_tokenizer_extension(force=False, sanitize=False):
     digest = _hash_files(srcs + headers)
     if not force and not _stale(so_path, digest):
         return so_path
-    cmd = ["g++", *opt, "-std=c++17", "-fPIC", "-shared", "-pthread", "-I", pybind11.get_include(),
-           "-I", sysconfig.get_paths()["include"], "-I", TOK_SRC, *srcs, "-o", so_path]
-    _run(cmd)
-    with open(so_path + ".hash", "w") as f:
-        f.write(digest)
+    with _build_lock():
+        if not force and not _stale(so_path, digest):
+            return so_path
+        tmp_so = so_path + ".tmp"
+        cmd = ["g++", *opt, "-std=c++17", "-fPIC", "-shared", "-pthread", "-I", pybind11.get_include(),
+               "-I", sysconfig.get_paths()["include"], "-I", TOK_SRC, *srcs, "-o", tmp_so]
+        _run(cmd)
+        os.replace(tmp_so, so_path)
+        _write_stamp(so_path, digest)
     return so_path
 
 

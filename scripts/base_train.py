@@ -23,16 +23,15 @@ from dataclasses import asdict
 from contextlib import contextmanager
 
 import torch
-import torch.distributed as dist
 
 from nanochat_b200 import common, ops
 from nanochat_b200.common import (compute_init, compute_cleanup, print0, DummyWandb, print_banner, get_base_dir,
-                                  autodetect_device_type, get_peak_flops, is_ddp_initialized)
+                                  autodetect_device_type, get_peak_flops)
 from nanochat_b200.models.gpt import GPT, GPTConfig
 from nanochat_b200 import schedules
 from nanochat_b200.checkpoint_manager import (save_checkpoint, load_checkpoint, optimizer_shard_count,
                                                CheckpointError)
-from nanochat_b200.loss_eval import evaluate_bpb
+from nanochat_b200.loss_eval import evaluate_bpb, evaluate_mean_loss
 from nanochat_b200.engine import Engine
 from nanochat_b200.utils.trace import MetricsLog, PhaseTimers
 
@@ -79,6 +78,8 @@ parser.add_argument("--model-tag", type=str, default=None)
 # additions of this framework
 parser.add_argument("--synthetic-data", action="store_true", help="uniform-random tokens instead of the corpus")
 parser.add_argument("--vocab-size", type=int, default=32768, help="vocabulary size with --synthetic-data")
+parser.add_argument("--synthetic-cycle", type=int, default=0,
+                    help="with --synthetic-data: repeat the first N batches forever (0 = fresh random batches)")
 parser.add_argument("--comm", type=str, default="auto", choices=["auto", "nccl", "fused"],
                     help="optimizer collectives: torch.distributed or fused peer-to-peer kernels")
 parser.add_argument("--kernels", type=str, default="native", choices=["native", "torch"])
@@ -203,32 +204,35 @@ if hp.weight_decay != args.weight_decay:
     print0(f"Scaling weight decay from {args.weight_decay:.6f} to {hp.weight_decay:.6f} for depth {args.depth}")
 
 # ----------------------------------------------------------------------------- optimizer
-comm = None
-if args.comm == "fused" or (args.comm == "auto" and device_type == "cuda" and ddp_world_size > 1
-                            and ops.get_kernel_mode() == "native"):
-    try:
-        from nanochat_b200.parallel.symm import SymmComm
-        comm = SymmComm.create(model)
-    except Exception as e:   # peer access unavailable: stay on NCCL and say so
-        print0(f"fused peer-to-peer optimizer path unavailable ({type(e).__name__}: {e}); using NCCL")
-        comm = None
-optimizer = model.setup_optimizer(
+# The step itself (micro-batches, sharded update, gradient reset) is train.TrainStep: the same object the
+# benchmark times. It builds the parameter arena on the native path and picks the optimizer collectives.
+from nanochat_b200.train import TrainStep
+scaler = torch.amp.GradScaler() if common.COMPUTE_DTYPE == torch.float16 else None
+if scaler is not None:
+    print0("GradScaler enabled for fp16 training")
+trainer = TrainStep(
+    model, comm=args.comm if ddp_world_size > 1 else None, scaler=scaler, timers=timers, log=print0,
     unembedding_lr=args.unembedding_lr * hp.batch_lr_scale, embedding_lr=args.embedding_lr * hp.batch_lr_scale,
     scalar_lr=args.scalar_lr * hp.batch_lr_scale, matrix_lr=args.matrix_lr * hp.batch_lr_scale,
-    weight_decay=hp.weight_decay, comm=comm)
+    weight_decay=hp.weight_decay)
+optimizer = trainer.optimizer
+if ddp_world_size > 1:
+    print0(f"Optimizer collectives: {trainer.comm_name}")
 if resuming:
     optimizer.load_state_dict(optimizer_data)
     del optimizer_data
 
-scaler = torch.amp.GradScaler() if common.COMPUTE_DTYPE == torch.float16 else None
-if scaler is not None:
-    print0("GradScaler enabled for fp16 training")
-
 # ----------------------------------------------------------------------------------- data
 if args.synthetic_data:
     from nanochat_b200.dataloader import synthetic_token_loader
-    train_loader = synthetic_token_loader(args.device_batch_size, args.max_seq_len, vocab_size, device=device)
+    train_loader = synthetic_token_loader(args.device_batch_size, args.max_seq_len, vocab_size, device=device,
+                                          cycle=args.synthetic_cycle)
     build_val_loader = None
+    # a fixed stream of random tokens whose mean loss a reloaded checkpoint must reproduce: held out for fresh random
+    # batches, the repeated training batches themselves when the stream cycles (then the loss is seen to fall)
+    build_synthetic_val = lambda: synthetic_token_loader(
+        args.device_batch_size, args.max_seq_len, vocab_size, device=device, cycle=args.synthetic_cycle,
+        seed=0 if args.synthetic_cycle > 0 else 4321)
 else:
     from nanochat_b200.dataloader import (tokenizing_distributed_data_loader_bos_bestfit,
                                           tokenizing_distributed_data_loader_with_state_bos_bestfit)
@@ -239,6 +243,17 @@ else:
     build_val_loader = lambda: tokenizing_distributed_data_loader_bos_bestfit(
         tokenizer, args.device_batch_size, args.max_seq_len, split="val", device=device)
 x, y, dataloader_state_dict = next(train_loader)
+
+
+def current_batch(_micro_step):
+    return x, y
+
+
+def advance_batch(_micro_step):
+    """Runs once a micro-batch's backward is queued: host-side packing of the next batch overlaps the GPU work."""
+    global x, y, dataloader_state_dict
+    x, y, dataloader_state_dict = next(train_loader)
+
 
 # ------------------------------------------------------------------------------- horizon
 assert args.num_iterations > 0 or args.target_param_data_ratio > 0 or args.target_flops > 0
@@ -274,6 +289,7 @@ grad_accum_steps = total_batch_size // world_tokens_per_fwdbwd
 print0(f"Tokens / micro-batch / rank: {args.device_batch_size} x {args.max_seq_len} = {tokens_per_fwdbwd:,}")
 print0(f"Tokens / micro-batch: {world_tokens_per_fwdbwd:,}")
 print0(f"Total batch size {total_batch_size:,} => gradient accumulation steps: {grad_accum_steps}")
+trainer.grad_accum = grad_accum_steps
 
 # ---------------------------------------------------------------------------------- loop
 while True:
@@ -291,6 +307,16 @@ while True:
         min_val_bpb = min(min_val_bpb, val_bpb)
         wandb_run.log({"step": step, "total_training_flops": flops_so_far,
                        "total_training_time": total_training_time, "val/bpb": val_bpb})
+        model.train()
+
+    if args.synthetic_data and args.eval_every > 0 and (last_step or step % args.eval_every == 0):
+        model.eval()
+        eval_steps = max(1, min(4, args.eval_tokens // (args.device_batch_size * args.max_seq_len * ddp_world_size)))
+        with disable_fp8(model):
+            val_loss = evaluate_mean_loss(model, build_synthetic_val(), eval_steps)
+        print0(f"Step {step:05d} | Validation loss: {val_loss:.6f}")
+        wandb_run.log({"step": step, "total_training_flops": flops_so_far,
+                       "total_training_time": total_training_time, "val/loss": val_loss})
         model.train()
 
     if tokenizer is not None and args.core_metric_every > 0 and (
@@ -318,7 +344,7 @@ while True:
 
     if last_step or (step > 0 and step != args.resume_from_step and args.save_every > 0
                      and step % args.save_every == 0):
-        save_checkpoint(checkpoint_dir, step, orig_model.state_dict(), optimizer.state_dict(), {
+        save_checkpoint(checkpoint_dir, step, trainer.model_state_dict(), optimizer.state_dict(), {
             "step": step, "val_bpb": val_bpb, "model_config": model_config_kwargs, "user_config": user_config,
             "device_batch_size": args.device_batch_size, "max_seq_len": args.max_seq_len,
             "total_batch_size": total_batch_size, "dataloader_state_dict": dataloader_state_dict,
@@ -332,17 +358,6 @@ while True:
     # ------------------------------------------------------------------ one optimizer step
     synchronize()
     t0 = time.time()
-    for micro_step in range(grad_accum_steps):
-        with timers.phase("forward"):
-            loss = model(x, y)
-        train_loss = loss.detach()
-        loss = loss / grad_accum_steps
-        with timers.phase("backward"):
-            if scaler is not None:
-                scaler.scale(loss).backward()
-            else:
-                loss.backward()
-        x, y, dataloader_state_dict = next(train_loader)   # host-side packing overlaps the GPU work
     lrm = schedules.pretrain_lr_multiplier(step, num_iterations, args.warmup_steps, args.warmdown_ratio,
                                            args.final_lr_frac)
     muon_momentum = schedules.pretrain_muon_momentum(step, num_iterations, args.warmdown_ratio)
@@ -352,17 +367,7 @@ while True:
         if group["kind"] == "muon":
             group["momentum"] = muon_momentum
             group["weight_decay"] = muon_weight_decay
-    if scaler is not None:
-        scaler.unscale_(optimizer)
-        if is_ddp_initialized():   # every rank must agree on skipping the step
-            for v in scaler._found_inf_per_device(optimizer).values():
-                dist.all_reduce(v, op=dist.ReduceOp.MAX)
-        scaler.step(optimizer)
-        scaler.update()
-    else:
-        with timers.phase("optimizer"):
-            optimizer.step()
-    model.zero_grad(set_to_none=True)
+    train_loss = trainer.step(current_batch, after_backward=advance_batch)
     train_loss_f = train_loss.item()
     synchronize()
     dt = time.time() - t0
@@ -406,6 +411,11 @@ while True:
     elif step % 5000 == 0:
         gc.collect()
 
+if device_type == "cuda" and ops.get_kernel_mode() == "native":
+    nat = ops.native_module()
+    nat.check_status()                     # raises if any kernel gave up on a bounded wait during the run
+    print0(f"Native kernels: {nat.launch_count():,} launches | fp8 layer passes: {nat.stats['fp8_layer_forward']:,} | "
+           f"bf16 layer passes: {nat.stats['bf16_layer_forward']:,} | fused QKV: {nat.stats['fused_qkv_forward']:,}")
 print0(f"Peak memory usage: {get_max_memory() / 1024 / 1024:.2f}MiB")
 print0(f"Total training time: {total_training_time/60:.2f}m")
 if val_bpb is not None:

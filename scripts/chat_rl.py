@@ -43,6 +43,8 @@ parser.add_argument("--init-lr-frac", type=float, default=0.05)
 parser.add_argument("--eval-every", type=int, default=60)
 parser.add_argument("--eval-examples", type=int, default=400)
 parser.add_argument("--save-every", type=int, default=60)
+parser.add_argument("--comm", type=str, default="auto", choices=["auto", "nccl", "fused"],
+                    help="optimizer collectives: torch.distributed or fused peer-to-peer kernels")
 args = parser.parse_args()
 user_config = vars(args).copy()
 
@@ -102,8 +104,12 @@ def run_gsm8k_eval(task, max_examples=None, num_samples=1, max_completion_tokens
                                         for s in seqs]}
 
 
-optimizer = model.setup_optimizer(unembedding_lr=args.unembedding_lr, embedding_lr=args.embedding_lr,
-                                  matrix_lr=args.matrix_lr, weight_decay=args.weight_decay)
+# the update (sharded optimizer step, gradient reset, consistent checkpoints) is train.TrainStep, as in pretraining
+from nanochat_b200.train import TrainStep
+trainer = TrainStep(model, comm=args.comm if ddp_world_size > 1 else None, log=print0,
+                    unembedding_lr=args.unembedding_lr, embedding_lr=args.embedding_lr,
+                    matrix_lr=args.matrix_lr, weight_decay=args.weight_decay)
+optimizer = trainer.optimizer
 for g in optimizer.param_groups:
     g["lr"] *= args.init_lr_frac
     g["initial_lr"] = g["lr"]
@@ -140,7 +146,7 @@ for step in range(num_steps):
             logp = -model(inputs, targets, loss_reduction="none").view_as(inputs)
             valid = (targets >= 0).sum().clamp(min=1)
             loss = -(logp * adv.unsqueeze(-1)).sum() / (valid * passes * examples_per_rank)
-            loss.backward()
+            trainer.backward(loss)
             print0(f"Step {step}/{num_steps} | Example step {example_step} | Pass {p} | loss: {loss.item():.6f} | "
                    f"Average reward: {rewards_all[sl].mean().item()}")
         reward_means.append(rewards_all.mean().item())
@@ -158,14 +164,15 @@ for step in range(num_steps):
     lrm = 1.0 - step / num_steps
     for g in optimizer.param_groups:
         g["lr"] = g["initial_lr"] * lrm
-    optimizer.step()
-    model.zero_grad(set_to_none=True)
+    trainer.optimizer_step()
     wandb_run.log({"step": step, "lrm": lrm})
 
-    if master_process and ((step > 0 and step % args.save_every == 0) or step == num_steps - 1):
+    saving = (step > 0 and step % args.save_every == 0) or step == num_steps - 1
+    model_state = trainer.model_state_dict() if saving else None      # collective: every rank takes part
+    if master_process and saving:
         out_dir = os.path.join(get_base_dir(), "chatrl_checkpoints",
                                args.model_tag if args.model_tag else f"d{model.config.n_layer}")
-        save_checkpoint(out_dir, step, model.state_dict(), None, {"model_config": dict(model.config.__dict__)})
+        save_checkpoint(out_dir, step, model_state, None, {"model_config": dict(model.config.__dict__)})
         print(f"Saved model checkpoint to {out_dir}")
 
 batches.close()          # the rollout generator holds a no_grad context: close it before the interpreter tears torch down

@@ -55,6 +55,8 @@ parser.add_argument("--mmlu-epochs", type=int, default=3)
 parser.add_argument("--gsm8k-epochs", type=int, default=4)
 parser.add_argument("--synthetic-data", action="store_true")
 parser.add_argument("--depth", type=int, default=32, help="model depth with --synthetic-data")
+parser.add_argument("--comm", type=str, default="auto", choices=["auto", "nccl", "fused"],
+                    help="optimizer collectives: torch.distributed or fused peer-to-peer kernels")
 args = parser.parse_args()
 user_config = vars(args).copy()
 
@@ -114,9 +116,16 @@ print0(f"Tokens / micro-batch / rank: {args.device_batch_size} x {args.max_seq_l
 print0(f"Tokens / micro-batch: {world_tokens_per_fwdbwd:,}")
 print0(f"Total batch size {args.total_batch_size:,} => gradient accumulation steps: {grad_accum_steps}")
 
-# pretraining ends with weight decay annealed to zero, so SFT continues without it
-optimizer = model.setup_optimizer(unembedding_lr=args.unembedding_lr, embedding_lr=args.embedding_lr,
-                                  matrix_lr=args.matrix_lr, weight_decay=0.0)
+# pretraining ends with weight decay annealed to zero, so SFT continues without it. The step (micro-batches,
+# sharded update, gradient reset) is train.TrainStep, the object pretraining and the benchmark use.
+from nanochat_b200.train import TrainStep
+scaler = torch.amp.GradScaler() if common.COMPUTE_DTYPE == torch.float16 else None
+trainer = TrainStep(model, grad_accum=grad_accum_steps, comm=args.comm if ddp_world_size > 1 else None, scaler=scaler,
+                    log=print0, unembedding_lr=args.unembedding_lr, embedding_lr=args.embedding_lr,
+                    matrix_lr=args.matrix_lr, weight_decay=0.0)
+optimizer = trainer.optimizer
+if ddp_world_size > 1:
+    print0(f"Optimizer collectives: {trainer.comm_name}")
 if args.load_optimizer and not args.synthetic_data:
     shard = load_optimizer_state("base", device, rank=ddp_rank, model_tag=args.model_tag, step=args.model_step,
                                  world_size=ddp_world_size)
@@ -129,7 +138,6 @@ if args.load_optimizer and not args.synthetic_data:
         print0("Loaded optimizer state from pretrained checkpoint (momentum buffers only, LRs reset)")
     else:
         print0("WARNING: optimizer checkpoint not found, starting with fresh optimizer (slightly worse)")
-scaler = torch.amp.GradScaler() if common.COMPUTE_DTYPE == torch.float16 else None
 for g in optimizer.param_groups:
     g["lr"] *= args.init_lr_frac
     g["initial_lr"] = g["lr"]
@@ -163,7 +171,30 @@ build_val_loader = lambda: sft_batches(val_dataset, render, bos, args.device_bat
 
 # --------------------------------------------------------------------------------- loop
 x, y = next(train_loader)
-progress, step = 0.0, 0
+progress, step, lrm = 0.0, 0, 1.0
+
+
+def current_batch(_micro_step):
+    return x, y
+
+
+def advance_batch(_micro_step):
+    """Runs once a micro-batch's backward is queued: packing the next batch overlaps the GPU work."""
+    global x, y, progress
+    x, y = next(train_loader)
+    progress = max(progress, state.approx_progress)
+
+
+def set_schedules():
+    """The learning-rate schedule runs over consumed-data progress, known once the step's batches are drawn."""
+    global lrm
+    lrm = schedules.sft_lr_multiplier(progress, args.warmup_ratio, args.warmdown_ratio, args.final_lr_frac)
+    for g in optimizer.param_groups:
+        g["lr"] = g["initial_lr"] * lrm
+        if g["kind"] == "muon":
+            g["momentum"] = schedules.sft_muon_momentum(step)
+
+
 min_val_bpb, val_bpb = float("inf"), None
 smooth_train_loss, ema_beta, total_training_time = 0.0, 0.9, 0.0
 while True:
@@ -203,8 +234,9 @@ while True:
         model.train()
 
     if last_step and not args.synthetic_data:
+        model_state = trainer.model_state_dict()      # collective: every rank's parameters made current first
         out_dir = os.path.join(get_base_dir(), "chatsft_checkpoints", args.model_tag if args.model_tag else f"d{depth}")
-        save_checkpoint(out_dir, step, orig_model.state_dict(), optimizer.state_dict(), {
+        save_checkpoint(out_dir, step, model_state, optimizer.state_dict(), {
             "step": step, "val_bpb": val_bpb,
             "model_config": {"sequence_len": args.max_seq_len, "vocab_size": tokenizer.get_vocab_size(),
                              "n_layer": depth, "n_head": model.config.n_head, "n_kv_head": model.config.n_kv_head,
@@ -215,31 +247,7 @@ while True:
 
     synchronize()
     t0 = time.time()
-    for micro_step in range(grad_accum_steps):
-        loss = model(x, y)
-        train_loss = loss.detach()
-        loss = loss / grad_accum_steps
-        if scaler is not None:
-            scaler.scale(loss).backward()
-        else:
-            loss.backward()
-        x, y = next(train_loader)
-        progress = max(progress, state.approx_progress)
-    lrm = schedules.sft_lr_multiplier(progress, args.warmup_ratio, args.warmdown_ratio, args.final_lr_frac)
-    for g in optimizer.param_groups:
-        g["lr"] = g["initial_lr"] * lrm
-        if g["kind"] == "muon":
-            g["momentum"] = schedules.sft_muon_momentum(step)
-    if scaler is not None:
-        scaler.unscale_(optimizer)
-        if is_ddp_initialized():
-            for v in scaler._found_inf_per_device(optimizer).values():
-                dist.all_reduce(v, op=dist.ReduceOp.MAX)
-        scaler.step(optimizer)
-        scaler.update()
-    else:
-        optimizer.step()
-    model.zero_grad(set_to_none=True)
+    train_loss = trainer.step(current_batch, after_backward=advance_batch, before_update=set_schedules)
     synchronize()
     dt = time.time() - t0
     step += 1
@@ -264,6 +272,9 @@ while True:
     elif step % 5000 == 0:
         gc.collect()
 
+from nanochat_b200 import ops
+if device_type == "cuda" and ops.get_kernel_mode() == "native":
+    ops.native_module().check_status()     # raises if any kernel gave up on a bounded wait during the run
 print0(f"Peak memory usage: {get_max_memory() / 1024 / 1024:.2f}MiB")
 print0(f"Total training time: {total_training_time/60:.2f}m")
 print0(f"Minimum validation bpb: {min_val_bpb:.4f}")

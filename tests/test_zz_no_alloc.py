@@ -4,8 +4,10 @@ The allocation-free attention-backward entry point, called through its exported 
 Some callers cannot allocate device memory where they need the backward pass (a fixed, pre-sized
 memory pool; a host application that owns all buffers). For them the library keeps the kernel's
 scratch vector inside its own image. This test calls `nc_attention_bwd_noalloc` twice in a row via
-ctypes and checks dq/dk/dv against the regular (caller-allocated scratch) entry point, and that an
-oversized problem is refused with a clear error. It is collected last on purpose.
+ctypes (two different shapes) and checks dq/dk/dv against the regular (caller-allocated scratch) entry
+point, and that an oversized problem, a null or misaligned pointer and a stride that is not a whole
+number of 16-byte vectors are refused with a clear error before anything is launched. It is collected
+last on purpose.
 """
 import ctypes
 import math
@@ -96,3 +98,30 @@ def test_noalloc_entry_rejects_oversized_problem():
         o.stride(0), o.stride(1), o.stride(2), -1, 0.1, stream)
     assert rc == 1
     assert b"exceeds" in lib.nc_noalloc_last_error()
+
+
+def test_noalloc_entry_rejects_bad_pointers_and_strides():
+    """Each of these must come back as code 2 from the host-side checks: nothing reaches the GPU."""
+    from nanochat_b200.ops import native as nat
+    lib = _lib()
+    q, k, v, d_o = _problem(4, 1, 128, 2, 2)
+    o = torch.empty(1, 128, 2, 128, dtype=BF16, device="cuda")
+    lse = torch.empty(1, 2, 128, dtype=torch.float32, device="cuda")
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call(ptrs, q_strides, kv_strides, o_strides):
+        return lib.nc_attention_bwd_noalloc(*ptrs, 1, 128, 128, 2, 2, *q_strides, *kv_strides, *o_strides, -1, 0.1, stream)
+    good = [t.data_ptr() for t in (q, k, v, o, lse, d_o, dq, dk, dv)]
+    qs, ks, os_ = list(q.stride()[:3]), list(k.stride()[:3]), list(o.stride()[:3])
+    null = list(good)
+    null[3] = None
+    assert call(null, qs, ks, os_) == 2 and b"null" in lib.nc_noalloc_last_error()
+    odd = list(good)
+    odd[0] += 2                                     # one bf16 element past a 16-byte boundary
+    assert call(odd, qs, ks, os_) == 2 and b"aligned" in lib.nc_noalloc_last_error()
+    assert call(good, [qs[0], qs[1] + 4, qs[2]], ks, os_) == 2 and b"strides" in lib.nc_noalloc_last_error()
+    assert call(good, qs, [ks[0], ks[1], 0], os_) == 2
+    assert call(good, qs, ks, [os_[0], os_[1], 64]) == 2 and b"head stride" in lib.nc_noalloc_last_error()
+    torch.cuda.synchronize()
+    nat.check_status(q)
