@@ -283,7 +283,15 @@ def run_ours(args):
         bytes_out = (world - 1) / world * n_all * 2         # bf16 parameters stored to the peers
         link_ms = max(bytes_in, bytes_out) / 770e9 * 1e3    # measured peer copy: 770 GB/s per direction
         flop_ms = ns_flops / world / 1405e12 * 1e3          # measured sustained bf16 GEMM rate
-        opt = {"ms": t.item(), "roofline_ms": max(link_ms, flop_ms), "link_ms": link_ms, "newton_schulz_ms": flop_ms,
+        breakdown = None
+        if trainer.comm is not None and hasattr(trainer.comm, "trace_report") and trainer.comm.trace.enabled:
+            trainer.optimizer.step()
+            mine = trainer.comm.trace_report()       # stages of one more step, this rank's device time
+            keys = list(mine)
+            vals = torch.tensor([mine[k] for k in keys], device=device)
+            dist.all_reduce(vals, op=dist.ReduceOp.MAX)
+            breakdown = {k: round(v, 3) for k, v in zip(keys, vals.tolist())}
+        opt = {"ms": t.item(), "breakdown_ms_max_over_ranks": breakdown, "roofline_ms": max(link_ms, flop_ms), "link_ms": link_ms, "newton_schulz_ms": flop_ms,
                "fraction_of_roofline": max(link_ms, flop_ms) / t.item()}
     tok_s = args.total_batch_size * args.steps / (ms / 1e3)
     peak_mem = torch.cuda.max_memory_allocated() / 2**30

@@ -373,6 +373,10 @@ class GPT(nn.Module):
         """Whole-sequence forward on the sm_100a kernels: one fused autograd node per layer."""
         nat = ops.native_module()
         assert idx.size(1) > 1, "Training forward pass should have T > 1"
+        if idx.dtype != torch.long:          # the SFT loader yields int32 inputs (reference: scripts/chat_sft.py); the
+            idx = idx.long()                 # gather kernels index with 64-bit ids
+        if targets is not None and targets.dtype != torch.long:
+            targets = targets.long()
         if nat.fp8_enabled():
             nat.begin_microstep(idx.device)
         x, _ = nat.embed_norm_smear(idx, self.transformer.wte.weight, self.smear_gate.weight, self.smear_lambda)

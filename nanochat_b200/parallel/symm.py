@@ -33,6 +33,34 @@ from nanochat_b200.parallel.ownership import adamw_shard, muon_shard
 _ALIGN = 256
 
 
+class _StepTrace:
+    """Device time of each stage of a fused step (CUDA events on the launching stream), kept when
+    NANOCHAT_OPT_TRACE=1; `SymmComm.trace_report()` returns the milliseconds of the last traced step."""
+
+    def __init__(self, enabled):
+        self.enabled = enabled
+        self.marks = []
+
+    def begin(self):
+        self.marks = []
+        self.mark("start")
+
+    def mark(self, name):
+        if self.enabled:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.marks.append((name, ev))
+
+    def report(self):
+        if len(self.marks) < 2:
+            return {}
+        torch.cuda.synchronize()
+        out = {}
+        for (_, a), (name, b) in zip(self.marks, self.marks[1:]):
+            out[name] = out.get(name, 0.0) + a.elapsed_time(b)
+        return out
+
+
 class _Pool:
     """A symmetric byte pool with a bump allocator; `peer_ptrs` are the N mapped base addresses."""
 
@@ -102,6 +130,8 @@ class SymmComm:
         self.pad_pool = _Pool(4096, dev, self.group)
         self.pad_pool.buf.zero_()
         self.epoch = 0
+        import os
+        self.trace = _StepTrace(os.environ.get("NANOCHAT_OPT_TRACE", "0") == "1")
 
         def alloc(shape, dtype, device, role="master"):
             if role == "grad":
@@ -141,13 +171,18 @@ class SymmComm:
     def fused_step(self, opt):
         C = self.nat._C
         gp, bp = self.grad_pool, self.bf16_pool
+        tr = self.trace
+        tr.begin()
         self.barrier()                                   # every rank's gradients are complete
+        tr.mark("barrier_in")
         for group in opt.param_groups:
             if group["kind"] == "adamw":
                 self._adamw_group(opt, group, C, gp, bp)
+                tr.mark("adamw " + "x".join(str(d) for d in group["params"][0].shape) + f" n={len(group['params'])}")
             else:
                 self._muon_group(opt, group, C, gp, bp)
         self.barrier()                                   # write-backs landed; peers are done reading my grads
+        tr.mark("barrier_out")
         for g in self.arena.muon_groups:
             if g["shadow"] is not None:
                 for p in g["params"]:
@@ -202,6 +237,7 @@ class SymmComm:
             for work, stacked, ps in gathers:
                 work.wait()
                 torch._foreach_copy_([p.data for p in ps], list(stacked[:len(ps)].unbind(0)))
+            self.trace.mark(f"muon {r}x{c} (nccl)")
             return
         shard = muon_shard(len(params), self.rank, self.world)
         state = opt.state[p0]
@@ -210,7 +246,10 @@ class SymmComm:
             sshape = (shard.chunk, r, 1) if r >= c else (shard.chunk, 1, c)
             state["second_momentum_buffer"] = torch.zeros(sshape, dtype=p0.dtype, device=p0.device)
         n = shard.num_owned
+        tag = f"muon {r}x{c}: "
         if n == 0:
+            for stage in ("pull+momentum", "equilibrate", "newton-schulz", "finish", "broadcast"):
+                self.trace.mark(tag + stage)          # same keys on every rank (the report is reduced over ranks)
             return
         nat = self.nat
         dev = p0.device
@@ -221,8 +260,11 @@ class SymmComm:
         total2 = nat._scratch("muon_total2", (n,), torch.float32, dev)
         grad_off = gp.offset_of(entry["grad"], 4) + shard.start * r * c
         C.p2p_muon_momentum(gp.peer_ptrs, grad_off, state["momentum_buffer"][:n], X, rowss, total, group["momentum"])
+        self.trace.mark(tag + "pull+momentum")
         C.muon_equilibrate(X, rowss, total, rowss2, total2)
+        self.trace.mark(tag + "equilibrate")
         Xo = nat.polar_express_native(X, group["ns_steps"])
+        self.trace.mark(tag + "newton-schulz")
         m = max(r, c)
         ss = nat._scratch("muon_ss", (n * m,), torch.float32, dev)
         scale = nat._scratch("muon_scale", (n * m,), torch.float32, dev)
@@ -231,8 +273,13 @@ class SymmComm:
         shadow = entry["shadow"][shard.start:shard.start + n]
         C.muon_finish(master, Xo, state["second_momentum_buffer"][:n].view(n, -1), ss, scale, shadow, lr,
                       group["weight_decay"], group["beta2"])
+        self.trace.mark(tag + "finish")
         out_off = bp.offset_of(entry["shadow"], 2) + shard.start * r * c
         C.p2p_bcast_bf16(shadow, bp.peer_ptrs, out_off, self.rank)
+        self.trace.mark(tag + "broadcast")
+
+    def trace_report(self):
+        return self.trace.report()
 
     # ---------------------------------------------------------------- master consistency
     @torch.no_grad()

@@ -14,8 +14,14 @@ from nanochat_b200.models.gpt import GPT, GPTConfig                  # noqa: E40
 from nanochat_b200.train import TrainStep                            # noqa: E402
 
 
+# argv[2] (optional) = "layers,width": the default is a 4-layer 256-wide model; "26,128" has the Muon groups of the
+# 26-layer flagship (104 / 26 / 26 matrices: uneven ownership, the last ranks own fewer or none) at toy width
+LAYERS, WIDTH = (int(v) for v in (sys.argv[2] if len(sys.argv) > 2 else "4,256").split(","))
+
+
 def build(device):
-    cfg = GPTConfig(sequence_len=256, vocab_size=2048, n_layer=4, n_head=2, n_kv_head=2, n_embd=256)
+    cfg = GPTConfig(sequence_len=256, vocab_size=2048, n_layer=LAYERS, n_head=WIDTH // 128, n_kv_head=WIDTH // 128,
+                    n_embd=WIDTH)
     torch.manual_seed(42)
     with torch.device("meta"):
         m = GPT(cfg)

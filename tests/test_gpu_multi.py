@@ -18,21 +18,24 @@ def _free_port():
         return s.getsockname()[1]
 
 
+@pytest.mark.parametrize("shape", ["4,256", "26,128"])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_fused_p2p_optimizer_matches_nccl(world, tmp_path):
+def test_fused_p2p_optimizer_matches_nccl(world, shape, tmp_path):
+    """shape = layers,width. "26,128" is the flagship's ownership pattern at toy width: Muon groups of 104, 26 and 26
+    matrices, so with 8 ranks they own 13 / 4 / 4 and the last ranks own fewer or none."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     out = str(tmp_path / "p2p.json")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
-           os.path.join(HERE, "_gpu_dist_worker.py"), out]
+           os.path.join(HERE, "_gpu_dist_worker.py"), out, shape]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", OMP_NUM_THREADS="2")
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, (r.stdout[-1500:], r.stderr[-3000:])
     records = json.load(open(out))
     scratch = os.environ.get("NANOCHAT_TEST_DUMP_DIR", "")
     if scratch and os.path.isdir(scratch):          # keep the per-rank comparison for inspection
-        with open(os.path.join(scratch, f"p2p_world{world}.json"), "w") as f:
+        with open(os.path.join(scratch, f"p2p_world{world}_{shape.replace(',', 'x')}.json"), "w") as f:
             json.dump(records, f, indent=1)
     for rec in records:
         for la, lb in rec["losses"]:
