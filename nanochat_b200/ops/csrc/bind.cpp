@@ -449,22 +449,37 @@ void p2p_barrier(const std::vector<int64_t>& pads, int64_t rank, int64_t epoch, 
 }
 void p2p_adamw(const std::vector<int64_t>& grads, int64_t grad_off, int64_t rank, Tensor& p, Tensor& m, Tensor& v,
                const std::vector<int64_t>& out, int64_t out_off, bool write_local_out, double lr, double beta1,
-               double beta2, double eps, double wd, int64_t step) {
+               double beta2, double eps, double wd, int64_t step, int64_t max_ctas) {
   const c10::cuda::CUDAGuard guard(p.device());
   TORCH_CHECK(p.is_contiguous() && m.is_contiguous() && v.is_contiguous(), "p2p_adamw: contiguous slices");
   NC_CHECK(nc::p2p_adamw(peer_ptrs(grads), (size_t)grad_off, (int)grads.size(), (int)rank, p.data_ptr(),
                          p.scalar_type() == at::kBFloat16, m.data_ptr(), v.data_ptr(), peer_ptrs(out), (size_t)out_off,
-                         write_local_out, (size_t)p.numel(), adamw_args(lr, beta1, beta2, eps, wd, step), cur_stream()));
+                         write_local_out, (size_t)p.numel(), adamw_args(lr, beta1, beta2, eps, wd, step), (int)max_ctas,
+                         cur_stream()));
+  ++g_launches;
 }
 void p2p_muon_momentum(const std::vector<int64_t>& grads, int64_t grad_off, Tensor& buf, Tensor& X, Tensor& rowss,
-                       Tensor& total, double mu) {
+                       Tensor& total, double mu, int64_t max_ctas) {
   const c10::cuda::CUDAGuard guard(buf.device());
   NC_CHECK(nc::p2p_muon_momentum(peer_ptrs(grads), (size_t)grad_off, (int)grads.size(), buf.data_ptr<float>(),
                                  X.data_ptr(), rowss.data_ptr<float>(), (float)mu, (int)X.size(0), (int)X.size(1),
-                                 (int)X.size(2), cur_stream()));
-  // per-matrix totals of the row sums (same reduction the single-GPU path uses)
-  Tensor t = rowss.view({X.size(0), X.size(1)}).sum(1);
-  total.copy_(t);
+                                 (int)X.size(2), (int)max_ctas, cur_stream()));
+  // per-matrix totals of the row sums (the reduction the single-GPU path uses)
+  NC_CHECK(nc::muon_total(rowss.data_ptr<float>(), total.data_ptr<float>(), (int)X.size(0), (int)X.size(1), cur_stream()));
+  g_launches += 2;
+}
+// Statistics + parameter update of this rank's chunk; the bf16 result goes to every rank's shadow stack.
+void p2p_muon_finish(Tensor& p, const Tensor& X, Tensor& second_buf, Tensor& ss, Tensor& scale,
+                     const std::vector<int64_t>& out, int64_t out_off, double lr, double wd, double beta2) {
+  const c10::cuda::CUDAGuard guard(X.device());
+  TORCH_CHECK(p.is_contiguous() && X.is_contiguous() && p.scalar_type() == at::kFloat && X.scalar_type() == at::kBFloat16,
+              "p2p_muon_finish: contiguous fp32 masters and bf16 update");
+  const int k = (int)X.size(0), r = (int)X.size(1), c = (int)X.size(2);
+  NC_CHECK(nc::muon_stats(X.data_ptr(), second_buf.data_ptr<float>(), ss.data_ptr<float>(), scale.data_ptr<float>(), k, r,
+                          c, (float)beta2, cur_stream()));
+  NC_CHECK(nc::p2p_muon_apply(p.data_ptr<float>(), X.data_ptr(), scale.data_ptr<float>(), peer_ptrs(out), (size_t)out_off,
+                              (int)out.size(), k, r, c, (float)lr, (float)wd, cur_stream()));
+  g_launches += 3;
 }
 void p2p_bcast_bf16(const Tensor& src, const std::vector<int64_t>& dst, int64_t dst_off, int64_t rank) {
   const c10::cuda::CUDAGuard guard(src.device());
@@ -517,6 +532,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("p2p_barrier", &p2p_barrier);
   m.def("p2p_adamw", &p2p_adamw);
   m.def("p2p_muon_momentum", &p2p_muon_momentum);
+  m.def("p2p_muon_finish", &p2p_muon_finish);
   m.def("p2p_bcast_bf16", &p2p_bcast_bf16);
   m.def("p2p_small_adamw", &p2p_small_adamw);
   m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("lse"), py::arg("window"),

@@ -11,12 +11,18 @@
 //                      sum in rank order in fp32, x 1/N, update the local fp32/bf16 state, and store
 //                      the new bf16 values into every rank's parameter/shadow buffer
 //   p2p_muon_momentum  the Muon momentum stage (optim.cu) with the gradient averaged from all ranks
-//   p2p_bcast_shadow   the updated bf16 matrices of this rank's Muon chunk written to every peer
+//   p2p_muon_apply     the Muon parameter update (optim.cu: muon_apply) whose bf16 result is stored into every
+//                      rank's shadow from the same registers: the all-gather is the update's write-back
+//   p2p_bcast_shadow   bf16 values of this rank written to every peer (kept for callers that update elsewhere)
 //   p2p_small_adamw    replicated parameters (< 1024 elements): every rank averages all ranks'
 //                      gradients itself and applies AdamW to its own copy (no write-back needed)
 //
 // Sums are taken in rank order 0..N-1, so the result does not depend on timing. Plain peer loads
 // and stores only: no multimem, no TMA on peer memory.
+//
+// A remote load takes a few microseconds, so what sets the pull rate is how many of them a thread has in flight.
+// The pulling kernels are templates on the world size: a thread first issues the 16-byte loads of ALL ranks for its
+// elements (2 x N independent loads), and only then adds them up in rank order.
 #include "comm.h"
 #include "rowops.cuh"
 
@@ -64,18 +70,37 @@ __device__ __forceinline__ float4 ldcg4(const float* p) { return __ldcg(reinterp
 
 // Gradients fp32. p: this rank's slice (fp32 master or bf16 table rows); out.p[r] + out_off: where the new
 // bf16 values go on rank r (shadow of an fp32 master, or the bf16 table itself). n % 8 == 0.
-template <bool P_BF16>
-__global__ void p2p_adamw_kernel(PeerPtrs grads, size_t grad_off, int world, void* __restrict__ p,
-                                 void* __restrict__ m, void* __restrict__ v, PeerPtrs out, size_t out_off,
-                                 int write_local_out, int rank, size_t n, AdamWArgs a) {
+// 128 threads and at most 64 registers per thread: one such CTA fits on an SM beside a resident tensor-core GEMM CTA
+// (320 threads x 168 registers), so the pull can share the GPU with the polar iteration running on another stream.
+template <bool P_BF16, int WORLD>
+__global__ void __launch_bounds__(128, 8)
+p2p_adamw_kernel(PeerPtrs grads, size_t grad_off, int world_rt, void* __restrict__ p,
+                 void* __restrict__ m, void* __restrict__ v, PeerPtrs out, size_t out_off,
+                 int write_local_out, int rank, size_t n, AdamWArgs a) {
+  const int world = WORLD > 0 ? WORLD : world_rt;
   const float step_size = a.lr / a.bias1, inv_bias2 = 1.f / a.bias2, decay = 1.f - a.lr * a.wd;
   const float inv_world = 1.f / world;
   for (size_t i = (blockIdx.x * (size_t)blockDim.x + threadIdx.x) * 8; i < n; i += (size_t)gridDim.x * blockDim.x * 8) {
     float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int r = 0; r < world; ++r) {
-      const float* src = reinterpret_cast<const float*>(grads.p[r]) + grad_off + i;
-      const float4 x = ldcg4(src), y = ldcg4(src + 4);
-      g[0] += x.x; g[1] += x.y; g[2] += x.z; g[3] += x.w; g[4] += y.x; g[5] += y.y; g[6] += y.z; g[7] += y.w;
+    if (WORLD > 0) {
+      float4 x[WORLD > 0 ? WORLD : 1], y[WORLD > 0 ? WORLD : 1];
+#pragma unroll
+      for (int r = 0; r < WORLD; ++r) {          // every rank's loads are in flight before the first add
+        const float* src = reinterpret_cast<const float*>(grads.p[r]) + grad_off + i;
+        x[r] = ldcg4(src);
+        y[r] = ldcg4(src + 4);
+      }
+#pragma unroll
+      for (int r = 0; r < WORLD; ++r) {
+        g[0] += x[r].x; g[1] += x[r].y; g[2] += x[r].z; g[3] += x[r].w;
+        g[4] += y[r].x; g[5] += y[r].y; g[6] += y[r].z; g[7] += y[r].w;
+      }
+    } else {
+      for (int r = 0; r < world; ++r) {
+        const float* src = reinterpret_cast<const float*>(grads.p[r]) + grad_off + i;
+        const float4 x = ldcg4(src), y = ldcg4(src + 4);
+        g[0] += x.x; g[1] += x.y; g[2] += x.z; g[3] += x.w; g[4] += y.x; g[5] += y.y; g[6] += y.z; g[7] += y.w;
+      }
     }
     float pv[8], mv[8], vv[8];
     if (P_BF16) {
@@ -120,9 +145,11 @@ __global__ void p2p_adamw_kernel(PeerPtrs grads, size_t grad_off, int world, voi
 
 // Muon momentum with the gradient averaged over ranks. grads.p[r] + grad_off addresses the (k, r, c) chunk
 // this rank owns inside rank r's gradient stack.
+template <int WORLD>
 __global__ void __launch_bounds__(128)
-p2p_muon_momentum_kernel(PeerPtrs grads, size_t grad_off, int world, float* __restrict__ buf,
+p2p_muon_momentum_kernel(PeerPtrs grads, size_t grad_off, int world_rt, float* __restrict__ buf,
                          __nv_bfloat16* __restrict__ X, float* __restrict__ rowss, float mu, long long rows, int c) {
+  const int world = WORLD > 0 ? WORLD : world_rt;
   const int lane = threadIdx.x & 31;
   const float inv_world = 1.f / world;
   for (long long row = blockIdx.x * 4ll + (threadIdx.x >> 5); row < rows; row += gridDim.x * 4ll) {
@@ -131,9 +158,18 @@ p2p_muon_momentum_kernel(PeerPtrs grads, size_t grad_off, int world, float* __re
     float ss = 0.f;
     for (int j = lane * 4; j < c; j += 128) {
       float4 g = make_float4(0, 0, 0, 0);
-      for (int r = 0; r < world; ++r) {
-        const float4 x = ldcg4(reinterpret_cast<const float*>(grads.p[r]) + grad_off + row * c + j);
-        g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
+      if (WORLD > 0) {
+        float4 x[WORLD > 0 ? WORLD : 1];
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r)
+          x[r] = ldcg4(reinterpret_cast<const float*>(grads.p[r]) + grad_off + row * c + j);
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r) { g.x += x[r].x; g.y += x[r].y; g.z += x[r].z; g.w += x[r].w; }
+      } else {
+        for (int r = 0; r < world; ++r) {
+          const float4 x = ldcg4(reinterpret_cast<const float*>(grads.p[r]) + grad_off + row * c + j);
+          g.x += x.x; g.y += x.y; g.z += x.z; g.w += x.w;
+        }
       }
       float gv[4] = {g.x * inv_world, g.y * inv_world, g.z * inv_world, g.w * inv_world};
       float4 b = *reinterpret_cast<float4*>(br + j);
@@ -152,6 +188,47 @@ p2p_muon_momentum_kernel(PeerPtrs grads, size_t grad_off, int world, float* __re
     }
     ss = warp_sum(ss);
     if (lane == 0) rowss[row] = ss;
+  }
+}
+
+// Muon's parameter update on this rank's chunk of a stack (k matrices of r x c fp32 masters; X the orthogonalised
+// update in bf16; scale per row (per_row) or per column): p <- p - lr*scale*X - lr*wd*p*[X*p >= 0]. The new value is
+// rounded to bf16 once and stored from registers into every rank's shadow stack at out_off (this rank's included):
+// the parameter all-gather is this kernel's write-back. 8 elements per thread (c % 8 == 0: they share a row).
+__global__ void __launch_bounds__(256)
+p2p_muon_apply_kernel(float* __restrict__ p, const __nv_bfloat16* __restrict__ X, const float* __restrict__ scale,
+                      PeerPtrs out, size_t out_off, int world, int r, int c, int per_row, float lr, float wd,
+                      size_t n8) {
+  const size_t per_mat8 = (size_t)r * c / 8;
+  const int c8 = c / 8;
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t mat = i / per_mat8;
+    const size_t rem = i - mat * per_mat8;
+    const int row = (int)(rem / c8), col = (int)(rem - (size_t)row * c8) * 8;
+    float xv[8], pv[8], sc[8];
+    unpack8(reinterpret_cast<const uint4*>(X)[i], xv);
+    const float4 p0 = reinterpret_cast<const float4*>(p)[2 * i], p1 = reinterpret_cast<const float4*>(p)[2 * i + 1];
+    pv[0] = p0.x; pv[1] = p0.y; pv[2] = p0.z; pv[3] = p0.w; pv[4] = p1.x; pv[5] = p1.y; pv[6] = p1.z; pv[7] = p1.w;
+    if (per_row) {
+      const float sv = scale[mat * r + row];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sc[e] = sv;
+    } else {
+      const float4 s0 = *reinterpret_cast<const float4*>(scale + mat * c + col);
+      const float4 s1 = *reinterpret_cast<const float4*>(scale + mat * c + col + 4);
+      sc[0] = s0.x; sc[1] = s0.y; sc[2] = s0.z; sc[3] = s0.w; sc[4] = s1.x; sc[5] = s1.y; sc[6] = s1.z; sc[7] = s1.w;
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float gv = xv[e] * sc[e];
+      const float mask = (gv * pv[e] >= 0.f) ? 1.f : 0.f;
+      pv[e] -= lr * gv + lr * wd * pv[e] * mask;
+    }
+    reinterpret_cast<float4*>(p)[2 * i] = make_float4(pv[0], pv[1], pv[2], pv[3]);
+    reinterpret_cast<float4*>(p)[2 * i + 1] = make_float4(pv[4], pv[5], pv[6], pv[7]);
+    const uint4 packed = pack8(pv);
+    for (int q = 0; q < world; ++q)
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(out.p[q]) + out_off)[i] = packed;
   }
 }
 
@@ -194,21 +271,62 @@ cudaError_t p2p_barrier(const PeerPtrs& pads, int rank, int world, int epoch, in
   return cudaGetLastError();
 }
 
+// `max_ctas` > 0 caps the grid: a pulling kernel that shares the GPU with tensor-core work on another stream needs
+// bytes in flight, not SMs.
+static inline int cap_grid(int grid, int max_ctas) { return (max_ctas > 0 && grid > max_ctas) ? max_ctas : grid; }
+
+template <bool P_BF16>
+static void launch_p2p_adamw(int grid, cudaStream_t s, const PeerPtrs& grads, size_t grad_off, int world, void* p, void* m,
+                             void* v, const PeerPtrs& out, size_t out_off, int write_local_out, int rank, size_t n,
+                             AdamWArgs a) {
+#define NC_ADAMW_CASE(W) \
+  p2p_adamw_kernel<P_BF16, W><<<grid, 128, 0, s>>>(grads, grad_off, world, p, m, v, out, out_off, write_local_out, rank, n, a)
+  switch (world) {
+    case 2: NC_ADAMW_CASE(2); break;
+    case 4: NC_ADAMW_CASE(4); break;
+    case 8: NC_ADAMW_CASE(8); break;
+    default: NC_ADAMW_CASE(0); break;
+  }
+#undef NC_ADAMW_CASE
+}
+
 cudaError_t p2p_adamw(const PeerPtrs& grads, size_t grad_off, int world, int rank, void* p, int p_bf16, void* m, void* v,
-                      const PeerPtrs& out, size_t out_off, int write_local_out, size_t n, AdamWArgs a, cudaStream_t s) {
+                      const PeerPtrs& out, size_t out_off, int write_local_out, size_t n, AdamWArgs a, int max_ctas,
+                      cudaStream_t s) {
   if ((n & 7) || (grad_off & 3) || (out_off & 7)) return cudaErrorInvalidValue;
-  const int grid = grid_for(n / 8, 256);
-  if (p_bf16) p2p_adamw_kernel<true><<<grid, 256, 0, s>>>(grads, grad_off, world, p, m, v, out, out_off, write_local_out, rank, n, a);
-  else p2p_adamw_kernel<false><<<grid, 256, 0, s>>>(grads, grad_off, world, p, m, v, out, out_off, write_local_out, rank, n, a);
+  if (n == 0) return cudaSuccess;
+  const size_t need = (n / 8 + 127) / 128;
+  const int grid = cap_grid((int)(need < 148 * 16 ? need : 148 * 16), max_ctas);
+  if (p_bf16) launch_p2p_adamw<true>(grid, s, grads, grad_off, world, p, m, v, out, out_off, write_local_out, rank, n, a);
+  else launch_p2p_adamw<false>(grid, s, grads, grad_off, world, p, m, v, out, out_off, write_local_out, rank, n, a);
   return cudaGetLastError();
 }
 
 cudaError_t p2p_muon_momentum(const PeerPtrs& grads, size_t grad_off, int world, float* buf, void* X, float* rowss,
-                              float mu, int k, int r, int c, cudaStream_t s) {
+                              float mu, int k, int r, int c, int max_ctas, cudaStream_t s) {
   if ((c & 3) || (grad_off & 3)) return cudaErrorInvalidValue;
   const long long rows = (long long)k * r;
-  const int grid = (int)((rows + 3) / 4 < 148 * 16 ? (rows + 3) / 4 : 148 * 16);
-  p2p_muon_momentum_kernel<<<grid, 128, 0, s>>>(grads, grad_off, world, buf, (__nv_bfloat16*)X, rowss, mu, rows, c);
+  if (rows == 0) return cudaSuccess;
+  const int grid = cap_grid((int)((rows + 3) / 4 < 148 * 16 ? (rows + 3) / 4 : 148 * 16), max_ctas);
+#define NC_MOM_CASE(W) \
+  p2p_muon_momentum_kernel<W><<<grid, 128, 0, s>>>(grads, grad_off, world, buf, (__nv_bfloat16*)X, rowss, mu, rows, c)
+  switch (world) {
+    case 2: NC_MOM_CASE(2); break;
+    case 4: NC_MOM_CASE(4); break;
+    case 8: NC_MOM_CASE(8); break;
+    default: NC_MOM_CASE(0); break;
+  }
+#undef NC_MOM_CASE
+  return cudaGetLastError();
+}
+
+cudaError_t p2p_muon_apply(float* p, const void* X, const float* scale, const PeerPtrs& out, size_t out_off, int world,
+                           int k, int r, int c, float lr, float wd, cudaStream_t s) {
+  if ((c & 7) || (out_off & 7) || world > MAX_RANKS) return cudaErrorInvalidValue;
+  const size_t n8 = (size_t)k * r * c / 8;
+  if (n8 == 0) return cudaSuccess;
+  p2p_muon_apply_kernel<<<grid_for(n8, 256), 256, 0, s>>>(p, (const __nv_bfloat16*)X, scale, out, out_off, world, r, c,
+                                                          r >= c, lr, wd, n8);
   return cudaGetLastError();
 }
 

@@ -245,8 +245,14 @@ cudaError_t muon_equilibrate(void* X, const float* rowss, const float* total, fl
   return cudaGetLastError();
 }
 
-cudaError_t muon_finish(float* p, const void* X, float* second_buf, float* ss_scratch, float* scale_scratch,
-                        void* shadow, int k, int r, int c, float lr, float wd, float beta2, cudaStream_t s) {
+cudaError_t muon_total(const float* rowss, float* total, int k, int r, cudaStream_t s) {
+  if (k == 0) return cudaSuccess;
+  muon_total_kernel<<<k, 256, 0, s>>>(rowss, total, r);
+  return cudaGetLastError();
+}
+
+cudaError_t muon_stats(const void* X, float* second_buf, float* ss_scratch, float* scale_scratch, int k, int r, int c,
+                       float beta2, cudaStream_t s) {
   const int per_row = r >= c;                 // factored second moment keeps rows when r >= c
   const int n = per_row ? r : c, n_red = per_row ? c : r;
   if (per_row) {
@@ -259,9 +265,16 @@ cudaError_t muon_finish(float* p, const void* X, float* second_buf, float* ss_sc
   }
   const float target = sqrtf((float)(r < c ? r : c));
   muon_stats_kernel<<<k, 256, 0, s>>>(ss_scratch, second_buf, scale_scratch, n, n_red, target, beta2);
+  return cudaGetLastError();
+}
+
+cudaError_t muon_finish(float* p, const void* X, float* second_buf, float* ss_scratch, float* scale_scratch,
+                        void* shadow, int k, int r, int c, float lr, float wd, float beta2, cudaStream_t s) {
+  cudaError_t e = muon_stats(X, second_buf, ss_scratch, scale_scratch, k, r, c, beta2, s);
+  if (e != cudaSuccess) return e;
   const size_t total = (size_t)k * r * c;
   muon_apply_kernel<<<ew_grid(total, 256), 256, 0, s>>>(p, (const __nv_bfloat16*)X, scale_scratch,
-                                                        (__nv_bfloat16*)shadow, r, c, per_row, lr, wd, total);
+                                                        (__nv_bfloat16*)shadow, r, c, r >= c, lr, wd, total);
   return cudaGetLastError();
 }
 

@@ -132,6 +132,11 @@ class SymmComm:
         self.epoch = 0
         import os
         self.trace = _StepTrace(os.environ.get("NANOCHAT_OPT_TRACE", "0") == "1")
+        # NANOCHAT_OPT_OVERLAP=0 runs the whole step on one stream (stage times then add up in the trace);
+        # NANOCHAT_OPT_LINK_CTAS caps the grid of the pulling kernels while they share the GPU with the GEMMs
+        self.overlap = os.environ.get("NANOCHAT_OPT_OVERLAP", "1") != "0"
+        self.link_ctas = int(os.environ.get("NANOCHAT_OPT_LINK_CTAS", "296")) if self.overlap else 0
+        self._link_stream = torch.cuda.Stream(device=dev)
 
         def alloc(shape, dtype, device, role="master"):
             if role == "grad":
@@ -169,18 +174,47 @@ class SymmComm:
 
     @torch.no_grad()
     def fused_step(self, opt):
+        """Two streams between two device barriers. The LINK stream pulls: first the gradients of each Muon group
+        (averaged into the momentum kernel), then the reduce + AdamW + write-back kernels of the embedding tables
+        and lm_head; its kernels are NVLink-bound and run on a capped number of small CTAs. The COMPUTE stream (the
+        caller's) orthogonalises each Muon group on the tensor cores as soon as that group's pull has landed and
+        stores the updated bf16 matrices to every rank from the update kernel itself. So the Newton-Schulz GEMMs of
+        one group run while the next groups' gradients and the AdamW traffic cross NVLink."""
         C = self.nat._C
         gp, bp = self.grad_pool, self.bf16_pool
         tr = self.trace
+        main = torch.cuda.current_stream()
+        link = self._link_stream if self.overlap else main
         tr.begin()
         self.barrier()                                   # every rank's gradients are complete
         tr.mark("barrier_in")
-        for group in opt.param_groups:
-            if group["kind"] == "adamw":
+        link.wait_stream(main)
+        muon = [g for g in opt.param_groups if g["kind"] == "muon"]
+        adamw = [g for g in opt.param_groups if g["kind"] == "adamw"]
+        jobs = []
+        with torch.cuda.stream(link):
+            for group in muon:
+                job = self._muon_pull(opt, group, C, gp)
+                if job is not None:
+                    job["pulled"] = torch.cuda.Event()
+                    job["pulled"].record(link)
+                    jobs.append(job)
+                    if not self.overlap:
+                        tr.mark(job["tag"] + "pull+momentum")
+            for group in adamw:
                 self._adamw_group(opt, group, C, gp, bp)
-                tr.mark("adamw " + "x".join(str(d) for d in group["params"][0].shape) + f" n={len(group['params'])}")
-            else:
-                self._muon_group(opt, group, C, gp, bp)
+                if not self.overlap:
+                    tr.mark("adamw " + "x".join(str(d) for d in group["params"][0].shape) + f" n={len(group['params'])}")
+        for group in muon:
+            r, c = group["params"][0].shape
+            if r % 8 or c % 8:
+                self._muon_tiny(opt, group)              # NCCL on the caller's stream while the link stream pulls
+                tr.mark(f"muon {r}x{c} (nccl)")
+        for job in jobs:
+            main.wait_event(job["pulled"])
+            self._muon_update(opt, job, C, bp)
+        main.wait_stream(link)
+        tr.mark("link stream tail")
         self.barrier()                                   # write-backs landed; peers are done reading my grads
         tr.mark("barrier_out")
         for g in self.arena.muon_groups:
@@ -222,23 +256,26 @@ class SymmComm:
                 write_local = True
             C.p2p_adamw(gp.peer_ptrs, grad_off, self.rank, p_slice, state["exp_avg"], state["exp_avg_sq"],
                         bp.peer_ptrs, out_off, write_local, group["lr"], b1, b2, group["eps"],
-                        group["weight_decay"], state["step"])
+                        group["weight_decay"], state["step"], self.link_ctas)
 
-    def _muon_group(self, opt, group, C, gp, bp):
+    def _muon_tiny(self, opt, group):
+        """The value-embedding gate matrices (a few KB): averaged with NCCL, generic sharded update."""
+        info = opt._launch_muon(group, self._nccl())
+        gathers = []
+        opt._finish_muon(group, info, self._nccl(), gathers)
+        for work, stacked, ps in gathers:
+            work.wait()
+            torch._foreach_copy_([p.data for p in ps], list(stacked[:len(ps)].unbind(0)))
+
+    def _muon_pull(self, opt, group, C, gp):
+        """Link-stream half of a Muon group: pull and average the gradients of the matrices this rank owns inside the
+        momentum kernel. Returns the job the compute stream continues with (None for tiny or unowned groups)."""
         params = group["params"]
         p0 = params[0]
         r, c = p0.shape
-        entry = next(g for g in self.arena.muon_groups if g["params"][0] is p0)
         if r % 8 or c % 8:
-            # tiny gate matrices (a few KB): average with NCCL and use the generic sharded update
-            info = opt._launch_muon(group, self._nccl())
-            gathers = []
-            opt._finish_muon(group, info, self._nccl(), gathers)
-            for work, stacked, ps in gathers:
-                work.wait()
-                torch._foreach_copy_([p.data for p in ps], list(stacked[:len(ps)].unbind(0)))
-            self.trace.mark(f"muon {r}x{c} (nccl)")
-            return
+            return None
+        entry = next(g for g in self.arena.muon_groups if g["params"][0] is p0)
         shard = muon_shard(len(params), self.rank, self.world)
         state = opt.state[p0]
         if "momentum_buffer" not in state:
@@ -248,35 +285,44 @@ class SymmComm:
         n = shard.num_owned
         tag = f"muon {r}x{c}: "
         if n == 0:
-            for stage in ("pull+momentum", "equilibrate", "newton-schulz", "finish", "broadcast"):
+            if not self.overlap:
+                self.trace.mark(tag + "pull+momentum")
+            for stage in ("equilibrate", "newton-schulz", "finish+write-back"):
                 self.trace.mark(tag + stage)          # same keys on every rank (the report is reduced over ranks)
-            return
+            return None
         nat = self.nat
         dev = p0.device
-        X = nat._scratch("muon_X", (n, r, c), torch.bfloat16, dev)
-        rowss = nat._scratch("muon_rowss", (n * r,), torch.float32, dev)
-        rowss2 = nat._scratch("muon_rowss2", (n * r,), torch.float32, dev)
-        total = nat._scratch("muon_total", (n,), torch.float32, dev)
-        total2 = nat._scratch("muon_total2", (n,), torch.float32, dev)
+        key = f"_{r}x{c}"                             # scratch is per group: all groups' pulls are in flight at once
+        job = dict(group=group, entry=entry, shard=shard, state=state, n=n, r=r, c=c, tag=tag,
+                   X=nat._scratch("muon_X" + key, (n, r, c), torch.bfloat16, dev),
+                   rowss=nat._scratch("muon_rowss" + key, (n * r,), torch.float32, dev),
+                   rowss2=nat._scratch("muon_rowss2" + key, (n * r,), torch.float32, dev),
+                   total=nat._scratch("muon_total" + key, (n,), torch.float32, dev),
+                   total2=nat._scratch("muon_total2" + key, (n,), torch.float32, dev))
         grad_off = gp.offset_of(entry["grad"], 4) + shard.start * r * c
-        C.p2p_muon_momentum(gp.peer_ptrs, grad_off, state["momentum_buffer"][:n], X, rowss, total, group["momentum"])
-        self.trace.mark(tag + "pull+momentum")
-        C.muon_equilibrate(X, rowss, total, rowss2, total2)
+        C.p2p_muon_momentum(gp.peer_ptrs, grad_off, state["momentum_buffer"][:n], job["X"], job["rowss"], job["total"],
+                            group["momentum"], self.link_ctas)
+        return job
+
+    def _muon_update(self, opt, job, C, bp):
+        """Compute-stream half: equilibrate, polar iteration on the tensor cores, update + write-back to every rank."""
+        group, entry, shard, state = job["group"], job["entry"], job["shard"], job["state"]
+        n, r, c, tag = job["n"], job["r"], job["c"], job["tag"]
+        nat = self.nat
+        dev = job["X"].device
+        C.muon_equilibrate(job["X"], job["rowss"], job["total"], job["rowss2"], job["total2"])
         self.trace.mark(tag + "equilibrate")
-        Xo = nat.polar_express_native(X, group["ns_steps"])
+        Xo = nat.polar_express_native(job["X"], group["ns_steps"])
         self.trace.mark(tag + "newton-schulz")
         m = max(r, c)
         ss = nat._scratch("muon_ss", (n * m,), torch.float32, dev)
         scale = nat._scratch("muon_scale", (n * m,), torch.float32, dev)
         lr = group["lr"] * max(1.0, r / c) ** 0.5
         master = entry["master"][shard.start:shard.start + n]
-        shadow = entry["shadow"][shard.start:shard.start + n]
-        C.muon_finish(master, Xo, state["second_momentum_buffer"][:n].view(n, -1), ss, scale, shadow, lr,
-                      group["weight_decay"], group["beta2"])
-        self.trace.mark(tag + "finish")
         out_off = bp.offset_of(entry["shadow"], 2) + shard.start * r * c
-        C.p2p_bcast_bf16(shadow, bp.peer_ptrs, out_off, self.rank)
-        self.trace.mark(tag + "broadcast")
+        C.p2p_muon_finish(master, Xo, state["second_momentum_buffer"][:n].view(n, -1), ss, scale, bp.peer_ptrs, out_off,
+                          lr, group["weight_decay"], group["beta2"])
+        self.trace.mark(tag + "finish+write-back")
 
     def trace_report(self):
         return self.trace.report()

@@ -81,7 +81,10 @@ def main():
             dp, dq = p.float() - initial[n], q.float() - initial[n]
             tol = rel * dq.abs().mean().item() + 1e-7
             frac = ((dp - dq).abs() > tol).float().mean().item()
-            if frac > 2e-2:
+            # per-layer scalars: their gradients are atomically accumulated sums with heavy cancellation, and the first
+            # Adam steps move a parameter by +-lr whatever the gradient's size, so a component near zero may take the
+            # other sign in another summation order; a few of a few dozen elements are allowed to
+            if frac > (0.35 if p.numel() < 64 else 2e-2):
                 bad[n] = (round((dp - dq).abs().max().item(), 5), round(frac, 4), round(dq.abs().mean().item(), 5))
         return dict(sorted(bad.items(), key=lambda kv: -kv[1][1])[:8])
     # same kernels, different collectives: only the summation order differs
