@@ -261,17 +261,15 @@ def run_ours(args):
     # its bytes over NVLink at the measured per-direction peer bandwidth.
     opt = None
     if world > 1:
-        reps = 3
-        trainer.optimizer.step()
+        # two more real steps with an event pair around the update: what the update costs once the gradient
+        # pushes have ridden on the backward pass (a bare optimizer.step() loop would pay them in the open)
+        trainer.optimizer_events = []
+        for _ in range(2):
+            step_device()
         torch.cuda.synchronize()
-        dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(reps):
-            trainer.optimizer.step()
-        e1.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / reps], device=device)
+        t = torch.tensor([sum(a.elapsed_time(b) for a, b in trainer.optimizer_events) / len(trainer.optimizer_events)],
+                         device=device)
+        trainer.optimizer_events = None
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         n_all = sum(p.numel() for p in model.parameters())
         ns_flops = 0.0
@@ -279,19 +277,21 @@ def run_ours(args):
             if p.dim() == 2 and min(p.shape) >= 8:
                 n, m = min(p.shape), max(p.shape)
                 ns_flops += 5 * (2.0 * n * n * m + 2.0 * n ** 3 + 2.0 * n * n * m)
-        bytes_in = (world - 1) / world * n_all * 4          # fp32 gradient slices pulled from the peers
-        bytes_out = (world - 1) / world * n_all * 2         # bf16 parameters stored to the peers
-        link_ms = max(bytes_in, bytes_out) / 770e9 * 1e3    # measured peer copy: 770 GB/s per direction
+        bytes_in = (world - 1) / world * n_all * 4          # fp32 gradient slices arriving from the peers: pushed by
+        #                                                     the last micro-batch's backward pass, outside the update
+        bytes_out = (world - 1) / world * n_all * 2         # bf16 parameters stored to the peers by the update kernels
+        link_ms = bytes_out / 770e9 * 1e3                   # measured peer copy: 770 GB/s per direction
+        push_ms = bytes_in / 770e9 * 1e3
         flop_ms = ns_flops / world / 1405e12 * 1e3          # measured sustained bf16 GEMM rate
         breakdown = None
         if trainer.comm is not None and hasattr(trainer.comm, "trace_report") and trainer.comm.trace.enabled:
-            trainer.optimizer.step()
-            mine = trainer.comm.trace_report()       # stages of one more step, this rank's device time
+            mine = trainer.comm.trace_report()       # stages of the last step, this rank's device time
             keys = list(mine)
             vals = torch.tensor([mine[k] for k in keys], device=device)
             dist.all_reduce(vals, op=dist.ReduceOp.MAX)
             breakdown = {k: round(v, 3) for k, v in zip(keys, vals.tolist())}
         opt = {"ms": t.item(), "breakdown_ms_max_over_ranks": breakdown, "roofline_ms": max(link_ms, flop_ms), "link_ms": link_ms, "newton_schulz_ms": flop_ms,
+               "gradient_push_link_ms_under_backward": push_ms,
                "fraction_of_roofline": max(link_ms, flop_ms) / t.item()}
     tok_s = args.total_batch_size * args.steps / (ms / 1e3)
     peak_mem = torch.cuda.max_memory_allocated() / 2**30

@@ -487,6 +487,20 @@ void p2p_bcast_bf16(const Tensor& src, const std::vector<int64_t>& dst, int64_t 
   NC_CHECK(nc::p2p_bcast_bf16(src.data_ptr(), peer_ptrs(dst), (size_t)dst_off, (int)dst.size(), (int)rank,
                               (size_t)src.numel(), cur_stream()));
 }
+void p2p_push_slices(const Tensor& src, int64_t slice, const std::vector<int64_t>& stage, int64_t dst_off, int64_t rank,
+                     int64_t max_ctas) {
+  const c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.is_contiguous() && src.scalar_type() == at::kFloat, "p2p_push_slices: contiguous fp32 gradient");
+  NC_CHECK(nc::p2p_push_slices(src.data_ptr<float>(), (size_t)src.numel(), (size_t)slice, peer_ptrs(stage),
+                               (size_t)dst_off, (int)rank, (int)max_ctas, cur_stream()));
+  ++g_launches;
+}
+void p2p_copy_f32(const Tensor& src, int64_t dst_ptr) {
+  const c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(src.is_contiguous() && src.scalar_type() == at::kFloat, "p2p_copy_f32: contiguous fp32 source");
+  NC_CHECK(nc::p2p_copy_f32(src.data_ptr<float>(), reinterpret_cast<float*>(dst_ptr), (size_t)src.numel(), cur_stream()));
+  ++g_launches;
+}
 void p2p_small_adamw(const std::vector<int64_t>& grads, int64_t grad_off, Tensor& p, Tensor& m, Tensor& v, double lr,
                      double beta1, double beta2, double eps, double wd, int64_t step) {
   const c10::cuda::CUDAGuard guard(p.device());
@@ -535,6 +549,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("p2p_muon_finish", &p2p_muon_finish);
   m.def("p2p_bcast_bf16", &p2p_bcast_bf16);
   m.def("p2p_small_adamw", &p2p_small_adamw);
+  m.def("p2p_push_slices", &p2p_push_slices);
+  m.def("p2p_copy_f32", &p2p_copy_f32);
   m.def("attn_fwd", &attn_fwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("lse"), py::arg("window"),
         py::arg("scale"), py::arg("amax_o") = py::none());
   m.def("attn_bwd", &attn_bwd, py::arg("q"), py::arg("k"), py::arg("v"), py::arg("o"), py::arg("lse"), py::arg("d_o"),

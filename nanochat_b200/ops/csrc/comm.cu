@@ -244,6 +244,28 @@ __global__ void p2p_bcast_kernel(const __nv_bfloat16* __restrict__ src, PeerPtrs
   }
 }
 
+// Push half of the reduce-scatter for gradients that no GEMM epilogue can deliver to their owner (embedding tables,
+// whose gradient is a scatter-add, and any tensor whose backward ran outside the last micro-batch's fused path).
+// `src` is this rank's fp32 gradient of a tensor sharded into equal contiguous slices of `slice` elements, slice o owned
+// by rank o. Every element outside this rank's own slice is stored into its owner's staging region: stage.p[o] +
+// dst_off addresses the slot reserved for THIS rank there. n % 4 == 0, slice % 4 == 0.
+__global__ void __launch_bounds__(256)
+p2p_push_slices_kernel(const float* __restrict__ src, size_t n4, size_t slice4, PeerPtrs stage, size_t dst_off, int rank) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    const int owner = (int)(i / slice4);
+    if (owner == rank) continue;
+    const float4 val = reinterpret_cast<const float4*>(src)[i];
+    reinterpret_cast<float4*>(reinterpret_cast<float*>(stage.p[owner]) + dst_off)[i - (size_t)owner * slice4] = val;
+  }
+}
+
+// Plain vector copy of n fp32 values to an address that may be peer memory (one matrix to its owner's slot).
+__global__ void __launch_bounds__(256)
+p2p_copy_f32_kernel(const float* __restrict__ src, float* __restrict__ dst, size_t n4) {
+  for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x)
+    reinterpret_cast<float4*>(dst)[i] = reinterpret_cast<const float4*>(src)[i];
+}
+
 // Replicated small parameter: average all ranks' gradients, AdamW on the local copy.
 __global__ void p2p_small_adamw_kernel(PeerPtrs grads, size_t grad_off, int world, float* __restrict__ p,
                                        float* __restrict__ m, float* __restrict__ v, int n, AdamWArgs a) {
@@ -265,15 +287,15 @@ static inline int grid_for(size_t work, int threads) {
   return (int)(need < 148 * 8 ? (need ? need : 1) : 148 * 8);
 }
 
+// `max_ctas` > 0 caps the grid: a link-bound kernel that shares the GPU with tensor-core work on another stream needs
+// bytes in flight, not SMs.
+static inline int cap_grid(int grid, int max_ctas) { return (max_ctas > 0 && grid > max_ctas) ? max_ctas : grid; }
+
 cudaError_t p2p_barrier(const PeerPtrs& pads, int rank, int world, int epoch, int* status, cudaStream_t s) {
   if (world > MAX_RANKS) return cudaErrorInvalidValue;
   p2p_barrier_kernel<<<1, 32, 0, s>>>(pads, rank, world, epoch, status);
   return cudaGetLastError();
 }
-
-// `max_ctas` > 0 caps the grid: a pulling kernel that shares the GPU with tensor-core work on another stream needs
-// bytes in flight, not SMs.
-static inline int cap_grid(int grid, int max_ctas) { return (max_ctas > 0 && grid > max_ctas) ? max_ctas : grid; }
 
 template <bool P_BF16>
 static void launch_p2p_adamw(int grid, cudaStream_t s, const PeerPtrs& grads, size_t grad_off, int world, void* p, void* m,
@@ -335,6 +357,21 @@ cudaError_t p2p_bcast_bf16(const void* src, const PeerPtrs& dst, size_t dst_off,
   if ((n & 7) || (dst_off & 7)) return cudaErrorInvalidValue;
   if (n == 0) return cudaSuccess;
   p2p_bcast_kernel<<<grid_for(n / 8, 256), 256, 0, s>>>((const __nv_bfloat16*)src, dst, dst_off, world, rank, n / 8);
+  return cudaGetLastError();
+}
+
+cudaError_t p2p_push_slices(const float* src, size_t n, size_t slice, const PeerPtrs& stage, size_t dst_off, int rank,
+                            int max_ctas, cudaStream_t s) {
+  if ((n & 3) || (slice & 3) || (dst_off & 3) || slice == 0) return cudaErrorInvalidValue;
+  if (n == 0) return cudaSuccess;
+  p2p_push_slices_kernel<<<cap_grid(grid_for(n / 4, 256), max_ctas), 256, 0, s>>>(src, n / 4, slice / 4, stage, dst_off, rank);
+  return cudaGetLastError();
+}
+
+cudaError_t p2p_copy_f32(const float* src, float* dst, size_t n, cudaStream_t s) {
+  if ((n & 3) || (reinterpret_cast<size_t>(dst) & 15) || (reinterpret_cast<size_t>(src) & 15)) return cudaErrorInvalidValue;
+  if (n == 0) return cudaSuccess;
+  p2p_copy_f32_kernel<<<grid_for(n / 4, 256), 256, 0, s>>>(src, dst, n / 4);
   return cudaGetLastError();
 }
 

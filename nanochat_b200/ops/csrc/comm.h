@@ -28,6 +28,10 @@ cudaError_t p2p_muon_apply(float* p, const void* X, const float* scale, const Pe
                            int k, int r, int c, float lr, float wd, cudaStream_t s);
 cudaError_t p2p_bcast_bf16(const void* src, const PeerPtrs& dst, size_t dst_off, int world, int rank, size_t n,
                            cudaStream_t s);
+// Gradient pushes (the reduce-scatter's transfer when no GEMM epilogue delivers it): see comm.cu.
+cudaError_t p2p_push_slices(const float* src, size_t n, size_t slice, const PeerPtrs& stage, size_t dst_off, int rank,
+                            int max_ctas, cudaStream_t s);
+cudaError_t p2p_copy_f32(const float* src, float* dst, size_t n, cudaStream_t s);
 cudaError_t p2p_small_adamw(const PeerPtrs& grads, size_t grad_off, int world, float* p, float* m, float* v, int n,
                             AdamWArgs a, cudaStream_t s);
 

@@ -266,9 +266,43 @@ def _wgrad_gemm(A, B, out, **kw):
     return out
 
 
+# Gradient sink (multi-GPU, last micro-batch of a step; see parallel/symm.py). While one is installed, a weight
+# gradient that is final when written goes where its owner will read it: `sink.targets(w)` lists row ranges of w
+# with, for each, the tensor to write (a view of the owning rank's staging slot, i.e. peer memory) or None for
+# rows this rank owns itself. The GEMM reads the locally accumulated gradient as its `aux` operand and stores
+# accumulated + new product to the target: the epilogue's stores are the reduce-scatter's transfer.
+_grad_sink = None
+
+
+def set_grad_sink(sink):
+    global _grad_sink
+    _grad_sink = sink
+
+
+def _table_grad_final(p):
+    """The kernel that completes this embedding table's gradient for the step has been queued."""
+    if _grad_sink is not None:
+        _grad_sink.table_grad_final(p)
+
+
 def _accumulate_wgrad(w, dy2, x2, scale_a=None, scale_b=None):
     """w.grad (fp32) += dy2^T @ x2, fused in the GEMM epilogue (bf16 operands, or fp8 with their scales)."""
     kw = dict(a_mn=True, b_mn=True, scale_a=scale_a, scale_b=scale_b)
+    targets = _grad_sink.targets(w) if (_grad_sink is not None and w.grad is not None) else None
+    if targets is not None:
+        fresh = getattr(w, "_grad_fresh", False)
+        rows = w.shape[0]
+        for lo, hi, out in targets:
+            a = dy2 if (lo == 0 and hi == rows) else dy2[:, lo:hi]
+            local = w.grad if (lo == 0 and hi == rows) else w.grad[lo:hi]
+            dst = local if out is None else out
+            if fresh:
+                _wgrad_gemm(a, x2, dst, **kw)
+            else:
+                _wgrad_gemm(a, x2, dst, aux=local, beta=1.0, **kw)
+        w._grad_fresh = False
+        _grad_sink.mark_pushed(w)
+        return
     if w.grad is None:
         w.grad = torch.empty_like(w, dtype=w.dtype)
         _wgrad_gemm(dy2, x2, w.grad, **kw)
@@ -497,6 +531,7 @@ class _EmbedFn(Function):
         dlam = _grad_buffer(lam)
         _C.embed_bwd(dx.contiguous(), idx, wte, gate_w.detach().float().contiguous().view(-1), lam.detach().float(),
                      dwte, dgate.view(-1), dlam)
+        _table_grad_final(wte)
         return None, None, None, None
 
 
@@ -676,6 +711,7 @@ class _LayerFn(Function):
             wg32 = wgate.detach().float().contiguous()
             _C.qkv_post_bwd(dqkv, qkv, n_head, n_kv_head, cos2, sin2, T, rstd, xn, wg32, ve_w, idx,
                             _grad_buffer(ve_w), _grad_buffer(wgate), dgate_x, amax_dqkv)
+            _table_grad_final(ve_w)
         else:
             _C.qkv_post_bwd(dqkv, qkv, n_head, n_kv_head, cos2, sin2, T, rstd, None, None, None, None,
                             None, None, None, amax_dqkv)
@@ -695,19 +731,38 @@ class _LayerFn(Function):
             gemm(dqkv[:, :nq], sq, dxn, b_mn=True)
             gemm(dqkv[:, nq:nq + nkv], sk, dxn, b_mn=True, aux=dxn, beta=1.0)
             gemm(dqkv[:, nq + nkv:], sv, dxn, b_mn=True, aux=dxn, beta=1.0)
-        fused_g = None
+        fused_g, fused_out = None, None
         if all(w.grad is not None for w in (wq, wk, wv)):
             fresh = [getattr(w, "_grad_fresh", False) for w in (wq, wk, wv)]
             if all(fresh) or not any(fresh):
                 fused_g = _contiguous_rows([wq.grad, wk.grad, wv.grad])
+        sunk = False
+        if fused_g is not None and _grad_sink is not None:
+            # last micro-batch on several GPUs: the three gradients go to their owner. One GEMM if q, k and v of this
+            # layer have the same owner (their slots are adjacent there too), otherwise one per matrix.
+            tq, tk, tv = (_grad_sink.targets(w) for w in (wq, wk, wv))
+            if tq is not None or tk is not None or tv is not None:
+                sunk = True
+                if tq is not None and tk is not None and tv is not None:
+                    fused_out = _contiguous_rows([tq[0][2], tk[0][2], tv[0][2]])
+                if fused_out is None:
+                    fused_g = None
         if fused_g is not None:
             wa, wb = (d8, xq8) if d8 is not None else (dqkv, xn)
             kw = dict(a_mn=True, b_mn=True, scale_a=sd, scale_b=sx) if d8 is not None else dict(a_mn=True, b_mn=True)
+            dst = fused_out if fused_out is not None else fused_g
             if fresh[0]:
-                _wgrad_gemm(wa, wb, fused_g, **kw)
+                _wgrad_gemm(wa, wb, dst, **kw)
                 wq._grad_fresh = wk._grad_fresh = wv._grad_fresh = False
             else:
-                _wgrad_gemm(wa, wb, fused_g, aux=fused_g, beta=1.0, **kw)
+                _wgrad_gemm(wa, wb, dst, aux=fused_g, beta=1.0, **kw)
+            if sunk:
+                for w in (wq, wk, wv):
+                    _grad_sink.mark_pushed(w)
+        elif d8 is not None:
+            _accumulate_wgrad(wq, d8[:, :nq], xq8, sd, sx)
+            _accumulate_wgrad(wk, d8[:, nq:nq + nkv], xq8, sd, sx)
+            _accumulate_wgrad(wv, d8[:, nq + nkv:], xq8, sd, sx)
         else:
             _accumulate_wgrad(wq, dqkv[:, :nq], xn)
             _accumulate_wgrad(wk, dqkv[:, nq:nq + nkv], xn)

@@ -2,27 +2,33 @@
 Fused peer-to-peer optimizer path for one NVSwitch domain (2-8 GPUs).
 
 Replaces the optimizer's NCCL collectives (reference: nanochat/optim.py:274-318 reduces,
-:359,407-417 gathers) by kernels that read and write the other ranks' memory directly:
+:359,407-417 gathers) by kernels that read and write the other ranks' memory directly. Ownership,
+optimizer state layout and hyper-parameters are the reference's, so per-rank optimizer
+checkpoints remain interchangeable with the NCCL path.
 
-  * gradients, bf16 weight shadows and bf16 embedding tables live in two symmetric pools
-    (`torch.distributed._symmetric_memory` allocates and exchanges the mappings; every rank
-    has the same layout at the same offsets);
-  * reduce-scatter + update + all-gather of an AdamW tensor is ONE kernel over the rank's row
-    slice (`p2p_adamw`): pull the slice of all N gradients over NVLink, average in rank order,
-    apply AdamW to the local state, store the new bf16 values into all N shadows / tables;
-  * a Muon group pulls and averages the gradients of the matrices this rank owns inside the
-    momentum kernel (`p2p_muon_momentum`), runs the polar iteration locally on the tcgen05
-    GEMM, and broadcasts the updated bf16 shadows to the peers (`p2p_bcast_bf16`);
-  * replicated small parameters average all ranks' gradients themselves (`p2p_small_adamw`);
-  * two device-side barriers per step (bounded waits, status word) bracket the phase.
+Reduce-scatter = a PUSH that rides on the last micro-batch's backward pass. Every rank has a
+staging pool (symmetric memory: same layout on every rank) with, for each sharded tensor, one slot
+per source rank the size of the owner's slice. On the last micro-batch of a step
+  * the weight-gradient GEMM of a matrix owned by another rank writes its result
+    (accumulated gradient + this micro-batch's product, fp32) straight into the owner's slot
+    for this rank: the GEMM's epilogue stores ARE the transfer, tile by tile, under the rest of
+    the backward pass (lm_head: one GEMM per owner's row slice);
+  * embedding-table gradients (scatter-adds) are pushed by a copy kernel on a side stream as soon
+    as the layer that produces them has run.
+The owner then sums its W slots from LOCAL memory inside the update kernels (rank order, so the
+result does not depend on timing).
 
-What crosses NVLink per step is therefore fp32 gradients in (as in the reference) but bf16
-parameters out (half of the reference's fp32 all-gather). The fp32 masters stay with their
-owners; `sync_masters()` makes every replica's masters consistent on demand (checkpointing),
-using NCCL broadcasts since that is rare and off the hot path.
+All-gather = the update kernels' write-back: AdamW (`p2p_adamw`) and the Muon update
+(`p2p_muon_apply`) store the new bf16 values into every rank's shadow / table from registers.
 
-Ownership, optimizer state layout and hyper-parameters are the reference's, so per-rank
-optimizer checkpoints remain interchangeable with the NCCL path.
+A step is bracketed by two device-side barriers (bounded waits, status word). Between them two
+streams run: the link stream sums + updates + writes back the AdamW tensors (NVLink-store bound,
+capped number of small CTAs) while the caller's stream orthogonalises the Muon groups on the tensor
+cores. The fp32 masters stay with their owners; `sync_masters()` makes every replica's masters
+consistent on demand (checkpointing), using NCCL broadcasts since that is rare and off the hot path.
+
+If a step's gradients were not produced through that last-micro-batch path (a driver that calls
+backward itself), the missing pushes are made by the copy kernel at the start of the step.
 """
 
 import torch
@@ -109,6 +115,29 @@ def _pool_sizes(model):
     return grad + 4096, bf16 + 4096
 
 
+def _stage_plan(model, world):
+    """Staging regions: {key: (offset in fp32 elements, slice elements)} and the pool size in bytes. Keys are
+    ('muon', shape) for a Muon stack and id(param) for a row-sharded AdamW tensor; a region is `world` slots of
+    one owner's slice."""
+    plan, off = {}, 0
+    align = _ALIGN // 4
+    matrix_params = list(model.transformer.h.parameters())
+    for shape in sorted({tuple(p.shape) for p in matrix_params}):
+        if shape[0] % 8 or shape[1] % 8:
+            continue
+        k = sum(1 for p in matrix_params if tuple(p.shape) == shape)
+        slice_elems = -(-k // world) * shape[0] * shape[1]
+        plan[("muon", shape)] = (off, slice_elems)
+        off = (off + world * slice_elems + align - 1) // align * align
+    big = [model.lm_head.weight, model.transformer.wte.weight] + [ve.weight for ve in model.value_embeds.values()]
+    for p in big:
+        assert p.shape[0] % world == 0, "row-sharded tensors need rows divisible by the world size"
+        slice_elems = p.shape[0] // world * p.shape[1]
+        plan[id(p)] = (off, slice_elems)
+        off = (off + world * slice_elems + align - 1) // align * align
+    return plan, off * 4 + 4096
+
+
 class SymmComm:
     """Communicator whose `fused_step` runs the whole sharded optimizer step with in-kernel NVLink traffic."""
 
@@ -129,6 +158,15 @@ class SymmComm:
         self.bf16_pool = _Pool(bf16_bytes, dev, self.group)
         self.pad_pool = _Pool(4096, dev, self.group)
         self.pad_pool.buf.zero_()
+        self.stage_plan, stage_bytes = _stage_plan(model, self.world)
+        self.stage_pool = _Pool(stage_bytes, dev, self.group)
+        # each rank's staging pool as an fp32 tensor in this process (peer memory for the others): slices of these
+        # are the `out` operands of the last micro-batch's weight-gradient GEMMs
+        self.stage_peer = [self.stage_pool.handle.get_buffer(o, (stage_bytes // 4,), torch.float32, 0)
+                           for o in range(self.world)]
+        self._targets = {}            # id(param) -> [(row_lo, row_hi, remote out tensor or None)]
+        self._pushed = set()          # ids of parameters / table entries whose final gradient reached its owners
+        self._sink_on = False
         self.epoch = 0
         import os
         self.trace = _StepTrace(os.environ.get("NANOCHAT_OPT_TRACE", "0") == "1")
@@ -147,6 +185,7 @@ class SymmComm:
 
         self.arena = ParamArena(model, alloc=alloc, with_shadows=True)
         self._fallback = None
+        self._plan_targets()
         torch.cuda.synchronize()
         dist.barrier(group)
 
@@ -160,6 +199,97 @@ class SymmComm:
             from nanochat_b200.parallel.comm import TorchDistComm
             self._fallback = TorchDistComm(None if self.group is dist.group.WORLD else self.group)
         return self._fallback
+
+    # ------------------------------------------------------------------ gradient pushes
+    def _plan_targets(self):
+        """Where each non-owned gradient goes: a view of the owner's slot for this rank."""
+        W, me = self.world, self.rank
+        for g in self.arena.muon_groups:
+            r, c = g["shape"]
+            if r % 8 or c % 8:
+                continue
+            off, slice_elems = self.stage_plan[("muon", (r, c))]
+            chunk = -(-len(g["params"]) // W)
+            for j, p in enumerate(g["params"]):
+                owner = j // chunk
+                if owner == me:
+                    continue
+                at = off + me * slice_elems + (j % chunk) * r * c
+                self._targets[id(p)] = [(0, r, self.stage_peer[owner][at:at + r * c].view(r, c))]
+        for d in self.arena.adamw_big:
+            p = d["param"]
+            if p.dtype != torch.float32:
+                continue                      # bf16 tables: scatter-added gradients, pushed by the copy kernel
+            off, slice_elems = self.stage_plan[id(p)]
+            rows, cols = p.shape[0] // W, p.shape[1]
+            at = off + me * slice_elems
+            self._targets[id(p)] = [
+                (o * rows, (o + 1) * rows,
+                 None if o == me else self.stage_peer[o][at:at + slice_elems].view(rows, cols)) for o in range(W)]
+
+    # surface used by ops.native while the last micro-batch's backward runs
+    def targets(self, w):
+        return self._targets.get(id(w))
+
+    def mark_pushed(self, w):
+        self._pushed.add(id(w))
+
+    def table_grad_final(self, p):
+        """Called by the backward pass right after the kernel that completes a table's gradient: push it to the
+        owners on the link stream, under the rest of the backward pass."""
+        d = self._entry_of(p)
+        if d is None or id(p) in self._pushed:
+            return
+        main = torch.cuda.current_stream()
+        self._link_stream.wait_stream(main)
+        with torch.cuda.stream(self._link_stream):
+            self._push_sharded(d["grad"], self.stage_plan[id(p)], self.link_ctas)
+        self._pushed.add(id(p))
+
+    def begin_last_microbatch(self):
+        """From here to `end_last_microbatch()` gradients are final when written: deliver them to their owners."""
+        self._sink_on = True
+        self.nat.set_grad_sink(self)
+
+    def end_last_microbatch(self):
+        self._sink_on = False
+        self.nat.set_grad_sink(None)
+
+    def _push_sharded(self, grad, plan_entry, max_ctas=0):
+        off, slice_elems = plan_entry
+        self.nat._C.p2p_push_slices(grad.view(-1), slice_elems, self.stage_pool.peer_ptrs,
+                                    off + self.rank * slice_elems, self.rank, max_ctas)
+
+    def _push_missing(self):
+        """Gradients that did not travel with the backward pass (a driver that runs its own backward calls)."""
+        W, me = self.world, self.rank
+        for g in self.arena.muon_groups:
+            r, c = g["shape"]
+            if r % 8 or c % 8:
+                continue
+            remote = [p for p in g["params"] if id(p) in self._targets]
+            missing = [p for p in remote if id(p) not in self._pushed]
+            if not missing:
+                continue
+            if len(missing) == len(remote):
+                self._push_sharded(g["grad"], self.stage_plan[("muon", (r, c))])
+            else:
+                for p in missing:
+                    dst = self._targets[id(p)][0][2]
+                    self.nat._C.p2p_copy_f32(p.grad, dst.data_ptr())
+        for d in self.arena.adamw_big:
+            p = d["param"]
+            if id(p) not in self._pushed:
+                self._push_sharded(d["grad"], self.stage_plan[id(p)])
+        self._pushed.clear()
+
+    def _slots(self, plan_entry, own_grad_ptr):
+        """The W addresses an owner sums: its slot for every source rank, and its own gradient where it lies."""
+        off, slice_elems = plan_entry
+        base = self.stage_pool.peer_ptrs[self.rank]
+        ptrs = [base + 4 * (off + s * slice_elems) for s in range(self.world)]
+        ptrs[self.rank] = own_grad_ptr
+        return ptrs
 
     def barrier(self):
         self.epoch += 1
@@ -186,7 +316,10 @@ class SymmComm:
         main = torch.cuda.current_stream()
         link = self._link_stream if self.overlap else main
         tr.begin()
-        self.barrier()                                   # every rank's gradients are complete
+        main.wait_stream(self._link_stream)              # table pushes issued during the backward pass
+        self._push_missing()
+        tr.mark("late pushes")
+        self.barrier()                                   # every rank's gradients have landed in their owners' slots
         tr.mark("barrier_in")
         link.wait_stream(main)
         muon = [g for g in opt.param_groups if g["kind"] == "muon"]
@@ -247,14 +380,14 @@ class SymmComm:
                 state["exp_avg"] = torch.zeros_like(p_slice)
                 state["exp_avg_sq"] = torch.zeros_like(p_slice)
             state["step"] += 1
-            grad_off = gp.offset_of(entry["grad"], 4) + shard.row_start * cols
+            slots = self._slots(self.stage_plan[id(p)], entry["grad"][shard.row_start:shard.row_end].data_ptr())
             if p.dtype == torch.bfloat16:      # the table itself is the bf16 tensor every rank reads
                 out_off = bp.offset_of(p.data, 2) + shard.row_start * cols
                 write_local = False            # the kernel already wrote p_slice in place
             else:
                 out_off = bp.offset_of(entry["shadow"], 2) + shard.row_start * cols
                 write_local = True
-            C.p2p_adamw(gp.peer_ptrs, grad_off, self.rank, p_slice, state["exp_avg"], state["exp_avg_sq"],
+            C.p2p_adamw(slots, 0, self.rank, p_slice, state["exp_avg"], state["exp_avg_sq"],
                         bp.peer_ptrs, out_off, write_local, group["lr"], b1, b2, group["eps"],
                         group["weight_decay"], state["step"], self.link_ctas)
 
@@ -299,8 +432,8 @@ class SymmComm:
                    rowss2=nat._scratch("muon_rowss2" + key, (n * r,), torch.float32, dev),
                    total=nat._scratch("muon_total" + key, (n,), torch.float32, dev),
                    total2=nat._scratch("muon_total2" + key, (n,), torch.float32, dev))
-        grad_off = gp.offset_of(entry["grad"], 4) + shard.start * r * c
-        C.p2p_muon_momentum(gp.peer_ptrs, grad_off, state["momentum_buffer"][:n], job["X"], job["rowss"], job["total"],
+        slots = self._slots(self.stage_plan[("muon", (r, c))], entry["grad"][shard.start:shard.start + n].data_ptr())
+        C.p2p_muon_momentum(slots, 0, state["momentum_buffer"][:n], job["X"], job["rowss"], job["total"],
                             group["momentum"], self.link_ctas)
         return job
 

@@ -74,6 +74,9 @@ class TrainStep:
         if optimizer is not None and comm is not None:
             self.optimizer.comm = comm
         self.steps_done = 0
+        # set to a list to collect a (start, end) CUDA event pair around every optimizer update (benchmarks: the
+        # update's exposed device time inside real steps, after whatever it overlapped with the backward pass)
+        self.optimizer_events = None
 
     # ------------------------------------------------------------------------------ one step
     def backward(self, loss):
@@ -86,6 +89,10 @@ class TrainStep:
 
     def optimizer_step(self):
         """Sharded optimizer update on the accumulated gradients, then gradient reset."""
+        events = None
+        if self.optimizer_events is not None and self.model.get_device().type == "cuda":
+            events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            events[0].record()
         with self.timers.phase("optimizer"):
             if self.scaler is not None:
                 self.scaler.unscale_(self.optimizer)
@@ -96,6 +103,9 @@ class TrainStep:
                 self.scaler.update()
             else:
                 self.optimizer.step()
+        if events is not None:
+            events[1].record()
+            self.optimizer_events.append(events)
         self.zero_grads()
         self.steps_done += 1
 
@@ -114,11 +124,20 @@ class TrainStep:
         data the step consumed). Returns the last micro-batch's loss (detached, on device)."""
         scale = (1.0 / self.grad_accum) if loss_scale is None else loss_scale
         loss = None
+        comm = self.comm if self.comm is not None else getattr(self.optimizer, "comm", None)
+        sink = comm if hasattr(comm, "begin_last_microbatch") else None
         for i in range(self.grad_accum):
             x, y = fetch(i)
             with self.timers.phase("forward"):
                 loss = self.model(x, y)
-            self.backward(loss * scale)
+            last = sink is not None and i == self.grad_accum - 1
+            if last:
+                sink.begin_last_microbatch()      # gradients written from here on are final: they go to their owners
+            try:
+                self.backward(loss * scale)
+            finally:
+                if last:
+                    sink.end_last_microbatch()
             if after_backward is not None:
                 after_backward(i)
         if before_update is not None:
