@@ -175,6 +175,7 @@ class SymmComm:
         self.overlap = os.environ.get("NANOCHAT_OPT_OVERLAP", "1") != "0"
         self.link_ctas = int(os.environ.get("NANOCHAT_OPT_LINK_CTAS", "296")) if self.overlap else 0
         self._link_stream = torch.cuda.Stream(device=dev)
+        self.time_updates = False     # benchmarks: keep an event pair per step, read with `update_ms()`
 
         def alloc(shape, dtype, device, role="master"):
             if role == "grad":
@@ -321,6 +322,9 @@ class SymmComm:
         tr.mark("late pushes")
         self.barrier()                                   # every rank's gradients have landed in their owners' slots
         tr.mark("barrier_in")
+        if self.time_updates:                            # from "every rank has arrived" to the end of the step
+            self._t0 = torch.cuda.Event(enable_timing=True)
+            self._t0.record()
         link.wait_stream(main)
         muon = [g for g in opt.param_groups if g["kind"] == "muon"]
         adamw = [g for g in opt.param_groups if g["kind"] == "adamw"]
@@ -350,6 +354,9 @@ class SymmComm:
         tr.mark("link stream tail")
         self.barrier()                                   # write-backs landed; peers are done reading my grads
         tr.mark("barrier_out")
+        if self.time_updates:
+            self._t1 = torch.cuda.Event(enable_timing=True)
+            self._t1.record()
         for g in self.arena.muon_groups:
             if g["shadow"] is not None:
                 for p in g["params"]:
@@ -459,6 +466,12 @@ class SymmComm:
 
     def trace_report(self):
         return self.trace.report()
+
+    def update_ms(self):
+        """Device time of the last step from the moment every rank had arrived (after the first barrier's wait, which
+        is the ranks' skew, not work) to the end of the second barrier. Synchronises."""
+        self._t1.synchronize()
+        return self._t0.elapsed_time(self._t1)
 
     # ---------------------------------------------------------------- master consistency
     @torch.no_grad()

@@ -80,6 +80,7 @@ parser.add_argument("--synthetic-data", action="store_true", help="uniform-rando
 parser.add_argument("--vocab-size", type=int, default=32768, help="vocabulary size with --synthetic-data")
 parser.add_argument("--synthetic-cycle", type=int, default=0,
                     help="with --synthetic-data: repeat the first N batches forever (0 = fresh random batches)")
+parser.add_argument("--no-final-save", action="store_true", help="do not write the checkpoint of the last step (timing runs)")
 parser.add_argument("--comm", type=str, default="auto", choices=["auto", "nccl", "fused"],
                     help="optimizer collectives: torch.distributed or fused peer-to-peer kernels")
 parser.add_argument("--kernels", type=str, default="native", choices=["native", "torch"])
@@ -342,8 +343,8 @@ while True:
             print0(tokenizer.decode(sample[0]))
         model.train()
 
-    if last_step or (step > 0 and step != args.resume_from_step and args.save_every > 0
-                     and step % args.save_every == 0):
+    if (last_step and not args.no_final_save) or (step > 0 and step != args.resume_from_step and args.save_every > 0
+                                                  and step % args.save_every == 0):
         save_checkpoint(checkpoint_dir, step, trainer.model_state_dict(), optimizer.state_dict(), {
             "step": step, "val_bpb": val_bpb, "model_config": model_config_kwargs, "user_config": user_config,
             "device_batch_size": args.device_batch_size, "max_seq_len": args.max_seq_len,
