@@ -17,7 +17,10 @@ B200-native differences: the cache position is mirrored on the host so a decode
 step never calls `.item()`; on CUDA the per-token forward of a `GPT` is replayed
 from a captured CUDA graph whose positions live in device memory (see
 `runtime.DecodeGraph`), and weights are consumed from bf16 shadows instead of
-being re-cast from fp32 every token.
+being re-cast from fp32 every token. On that path the cache is paged
+(`PagedKVCache`): the prompt is prefilled straight into pages that every sample
+row's page table points at, so forking N samples copies at most one partial page
+per row instead of the whole prompt, and N samples hold the prompt once.
 """
 
 import signal
@@ -134,6 +137,146 @@ class KVCache:
             self.prev_embedding = other.prev_embedding.expand(self.batch_size, -1, -1).clone()
 
 
+PAGE_TOKENS = 64
+
+
+class _PromptView:
+    """The shared prompt pages of a PagedKVCache seen as a batch-1 contiguous cache: what the prefill writes into.
+    Has the KVCache surface the model's forward uses."""
+
+    def __init__(self, owner, capacity):
+        self.owner = owner
+        self.batch_size = 1
+        self.max_seq_len = capacity
+        self.n_layers = owner.n_layers
+        self.cache_seqlens = torch.zeros(1, dtype=torch.int32, device=owner.k_pool.device)
+        self.prev_embedding = None
+        self._pos = 0
+
+    def get_pos(self):
+        return self._pos
+
+    def get_layer_cache(self, layer_idx):
+        o, n = self.owner, self.max_seq_len // self.owner.page_tokens
+        shape = (1, self.max_seq_len, o.n_heads, o.head_dim)
+        return o.k_pool[layer_idx, :n].view(shape), o.v_pool[layer_idx, :n].view(shape)
+
+    def advance(self, num_tokens):
+        self.cache_seqlens += num_tokens
+        self._pos += num_tokens
+
+
+class PagedKVCache:
+    """K/V store of `batch_size` sample rows as pages of PAGE_TOKENS tokens plus a per-row page table
+    (reference behaviour: nanochat/engine.py:82-137, a contiguous cache per row and a copy at the fork).
+
+    Pool pages [0, shared_pages) hold the prompt, written once by the batch-1 prefill through `begin_prompt()`;
+    `fork()` points every row's table at the prompt's full pages and gives each row private pages for the prompt's
+    partial last page (copied: rows append into it) and for what it decodes. The decode kernels address tokens
+    through the table (`ops/csrc/decode.cu`: KvPages). The pool grows when a request needs more pages than any before
+    it; `pool_version` then moves so that a captured decode graph is rebuilt on the new addresses.
+    """
+
+    paged = True
+
+    def __init__(self, batch_size, num_heads, seq_len, head_dim, num_layers, device, dtype, page_tokens=PAGE_TOKENS):
+        assert page_tokens & (page_tokens - 1) == 0, "page size must be a power of two"
+        self.batch_size = batch_size
+        self.max_seq_len = seq_len                  # per-row capacity in tokens (what the page table can address)
+        self.n_layers, self.n_heads, self.head_dim = num_layers, num_heads, head_dim
+        self.page_tokens = page_tokens
+        self.max_pages = -(-seq_len // page_tokens)
+        self.device, self.dtype = device, dtype
+        self.table = torch.zeros(batch_size, self.max_pages, dtype=torch.int32, device=device)
+        self.cache_seqlens = torch.zeros(batch_size, dtype=torch.int32, device=device)
+        self.k_pool = self.v_pool = None
+        self.shared_pages = self.private_pages = 0
+        self.pool_version = 0
+        self.prev_embedding = None
+        self._pos = 0
+
+    # ----------------------------------------------------------------------------- pool
+    def reserve(self, prompt_tokens, new_tokens):
+        """Make room for a prompt of `prompt_tokens` and `new_tokens` decoded tokens per row."""
+        P = self.page_tokens
+        assert prompt_tokens + new_tokens <= self.max_seq_len
+        shared = -(-prompt_tokens // P)
+        private = -(-(prompt_tokens % P + new_tokens) // P)
+        if self.k_pool is not None and shared <= self.shared_pages and private <= self.private_pages:
+            return
+        self.shared_pages = max(shared, self.shared_pages)
+        self.private_pages = max(private, self.private_pages)
+        # one spare page at the end: table entries a row has no page for point at it, so a token appended past a row's
+        # pages lands there instead of in a page that holds someone's keys
+        total = self.shared_pages + self.batch_size * self.private_pages + 1
+        self.spare_page = total - 1
+        shape = (self.n_layers, total, P, self.n_heads, self.head_dim)
+        self.k_pool = self.v_pool = None            # release before allocating the larger pool
+        self.k_pool = torch.zeros(shape, device=self.device, dtype=self.dtype)
+        self.v_pool = torch.zeros(shape, device=self.device, dtype=self.dtype)
+        self.pool_version += 1
+
+    def pool_bytes(self):
+        return 0 if self.k_pool is None else 2 * self.k_pool.numel() * self.k_pool.element_size()
+
+    def reset(self):
+        self.cache_seqlens.zero_()
+        self.prev_embedding = None
+        self._pos = 0
+
+    def get_pos(self):
+        return self._pos
+
+    def get_layer_cache(self, layer_idx):
+        """One layer's pools, (pages, PAGE_TOKENS, H, D): the paged decode kernels take them with `table`."""
+        return self.k_pool[layer_idx], self.v_pool[layer_idx]
+
+    def advance(self, num_tokens):
+        self.cache_seqlens += num_tokens
+        self._pos += num_tokens
+
+    # --------------------------------------------------------------------- prompt, fork
+    def begin_prompt(self, prompt_tokens):
+        """A batch-1 contiguous view of the shared pages for the prefill of a `prompt_tokens`-token prompt."""
+        assert self.k_pool is not None and -(-prompt_tokens // self.page_tokens) <= self.shared_pages
+        self.reset()
+        return _PromptView(self, -(-prompt_tokens // self.page_tokens) * self.page_tokens)
+
+    def fork(self, view):
+        """Every row continues the prompt in `view`: full prompt pages are shared, the partial last one is copied."""
+        P, B = self.page_tokens, self.batch_size
+        n = view.get_pos()
+        full, rem = n // P, n % P
+        first_private = self.shared_pages + torch.arange(B, dtype=torch.int32, device=self.device) * self.private_pages
+        table = torch.full((B, self.max_pages), self.spare_page, dtype=torch.int32, device=self.device)
+        if full:
+            table[:, :full] = torch.arange(full, dtype=torch.int32, device=self.device)
+        own = min(self.private_pages, self.max_pages - full)
+        table[:, full:full + own] = first_private[:, None] + torch.arange(own, dtype=torch.int32, device=self.device)
+        self.table.copy_(table)
+        if rem:
+            idx = first_private.long()
+            self.k_pool[:, idx, :rem] = self.k_pool[:, full:full + 1, :rem]
+            self.v_pool[:, idx, :rem] = self.v_pool[:, full:full + 1, :rem]
+        self.cache_seqlens.fill_(n)
+        self._pos = n
+        self.prev_embedding = None
+        if view.prev_embedding is not None:
+            self.prev_embedding = view.prev_embedding.expand(B, -1, -1).clone()
+
+    def row_capacity(self):
+        """Tokens a row can hold with the pages it has now."""
+        return min(self.max_seq_len, (self._pos // self.page_tokens + self.private_pages) * self.page_tokens)
+
+    def gather_row(self, layer_idx, row):
+        """(T, H, D) keys and values of one row in position order (tests and debugging; copies)."""
+        n = self._pos
+        pages = self.table[row, :-(-n // self.page_tokens)].long()
+        k = self.k_pool[layer_idx, pages].reshape(-1, self.n_heads, self.head_dim)[:n]
+        v = self.v_pool[layer_idx, pages].reshape(-1, self.n_heads, self.head_dim)[:n]
+        return k, v
+
+
 @torch.inference_mode()
 def sample_next_token(logits, rng, temperature=1.0, top_k=None):
     """(B, V) logits -> (B, 1) ids; argmax at temperature 0, else top-k / full multinomial."""
@@ -192,19 +335,23 @@ class Engine:
         cfg = self.model.config
         geometry = dict(num_heads=cfg.n_kv_head, head_dim=cfg.n_embd // cfg.n_head,
                         num_layers=cfg.n_layer, device=device, dtype=common.COMPUTE_DTYPE)
-        # 1) batch-1 prefill of the prompt
-        prompt_cache = KVCache(batch_size=1, seq_len=len(tokens), **geometry)
         ids = torch.tensor([tokens], dtype=torch.long, device=device)
-        logits = self.model.forward(ids, kv_cache=prompt_cache)
-        logits = logits[:, -1, :].expand(num_samples, -1)
-        # 2) fork the cache for every sample row
         capacity = (len(tokens) + max_tokens) if max_tokens is not None else cfg.sequence_len
-        cache = self._pooled_cache(num_samples, capacity, geometry)
+        cache = self._pooled_cache(num_samples, len(tokens), capacity, geometry)
         pooled = cache is not None
-        if not pooled:
+        if pooled:
+            # 1) batch-1 prefill straight into the pages every row will share  2) fork = page tables + one partial page
+            view = cache.begin_prompt(len(tokens))
+            logits = self.model.forward(ids, kv_cache=view)
+            cache.fork(view)
+        else:
+            # 1) batch-1 prefill of the prompt  2) fork: copy it into every sample row of a contiguous cache
+            prompt_cache = KVCache(batch_size=1, seq_len=len(tokens), **geometry)
+            logits = self.model.forward(ids, kv_cache=prompt_cache)
             cache = KVCache(batch_size=num_samples, seq_len=capacity, **geometry)
-        cache.prefill(prompt_cache)
-        del prompt_cache
+            cache.prefill(prompt_cache)
+            del prompt_cache
+        logits = logits[:, -1, :].expand(num_samples, -1)
         try:
             yield from self._decode_loop(tokens, num_samples, max_tokens, temperature, top_k, rng, logits, cache,
                                          (python_start, python_end, output_start, output_end, assistant_end, bos))
@@ -212,17 +359,17 @@ class Engine:
             if pooled:
                 cache.in_use = False
 
-    def _pooled_cache(self, rows, capacity, geometry):
-        """A full-length cache that lives as long as the engine, so its captured decode graph is reused.
-        None when the graph path does not apply or the pooled cache is busy (nested generations)."""
+    def _pooled_cache(self, rows, prompt_tokens, capacity, geometry):
+        """The paged cache of this row count. It lives as long as the engine, so its captured decode graph is reused;
+        its page pool grows to the largest request seen. None when the graph path does not apply or the cache is
+        busy (nested generations)."""
+        from nanochat_b200.runtime import graph_path_applies
         cfg = self.model.config
-        device = geometry["device"]
-        if (device.type != "cuda" or ops.get_kernel_mode() != "native" or rows > 64
-                or capacity > cfg.sequence_len or geometry["head_dim"] != 128):
+        if capacity > cfg.sequence_len or not graph_path_applies(self.model, rows):
             return None
         cache = self._cache_pool.get(rows)
         if cache is None:
-            cache = KVCache(batch_size=rows, seq_len=cfg.sequence_len, **geometry)
+            cache = PagedKVCache(batch_size=rows, seq_len=cfg.sequence_len, **geometry)
             cache.pooled = True
             cache.in_use = False
             self._cache_pool[rows] = cache
@@ -230,6 +377,7 @@ class Engine:
             return None
         cache.in_use = True
         cache.reset()
+        cache.reserve(prompt_tokens, capacity - prompt_tokens)
         return cache
 
     def _decode_loop(self, tokens, num_samples, max_tokens, temperature, top_k, rng, logits, cache, specials):

@@ -297,16 +297,38 @@ void decode_embed(const Tensor& ids, const Tensor& wte, const Tensor& gate_w, co
 }
 
 // qkv: (B, (H+2Hkv)*128); cos/sin: (Tmax, 64); seqlens: int32 (B); k_cache/v_cache: (B, Tmax, Hkv, 128) of one layer.
+// Paged store: k_cache/v_cache are one layer's pool (n_pages, page_tokens, Hkv, 128), `table` int32 (B, max_pages),
+// `t_max` the per-row capacity in tokens.
+static nc::KvPages kv_pages(const optional<Tensor>& table, const Tensor& cache, int64_t B) {
+  nc::KvPages pg;
+  if (!table.has_value() || !table->defined()) return pg;
+  TORCH_CHECK(table->is_cuda() && table->scalar_type() == at::kInt && table->dim() == 2 && table->is_contiguous() &&
+              table->size(0) == B, "page table: contiguous int32 (B, max_pages)");
+  const int64_t tokens = cache.size(1);
+  TORCH_CHECK(tokens > 0 && (tokens & (tokens - 1)) == 0, "page size must be a power of two");
+  int shift = 0;
+  while ((int64_t(1) << shift) < tokens) ++shift;
+  pg.table = table->data_ptr<int>();
+  pg.max_pages = (int)table->size(1);
+  pg.page_shift = shift;
+  return pg;
+}
+
 void decode_qkv_post(Tensor& qkv, int64_t H, int64_t Hkv, const Tensor& cos_t, const Tensor& sin_t, const Tensor& seqlens,
                      const optional<Tensor>& xn, const optional<Tensor>& wg, const optional<Tensor>& ve,
-                     const optional<Tensor>& idx, Tensor& k_cache, Tensor& v_cache) {
+                     const optional<Tensor>& idx, Tensor& k_cache, Tensor& v_cache, const optional<Tensor>& table,
+                     int64_t t_max) {
   check_bf16(qkv, "qkv"); check_bf16(cos_t, "cos"); check_bf16(sin_t, "sin"); check_bf16(k_cache, "k_cache");
   check_bf16(v_cache, "v_cache");
   TORCH_CHECK(qkv.dim() == 2 && qkv.stride(1) == 1 && qkv.size(1) == (H + 2 * Hkv) * 128, "qkv shape");
   TORCH_CHECK(cos_t.is_contiguous() && sin_t.is_contiguous() && cos_t.size(-1) == 64, "rotary tables (T, 64)");
   TORCH_CHECK(seqlens.scalar_type() == at::kInt && seqlens.numel() == qkv.size(0), "seqlens int32 (B)");
-  TORCH_CHECK(k_cache.dim() == 4 && k_cache.size(0) == qkv.size(0) && k_cache.size(2) == Hkv && k_cache.size(3) == 128 &&
-              k_cache.stride(3) == 1 && k_cache.stride(2) == 128 && v_cache.strides() == k_cache.strides(), "cache layout");
+  const bool paged = table.has_value() && table->defined();
+  TORCH_CHECK(k_cache.dim() == 4 && (paged || k_cache.size(0) == qkv.size(0)) && k_cache.size(2) == Hkv &&
+              k_cache.size(3) == 128 && k_cache.stride(3) == 1 && k_cache.stride(2) == 128 &&
+              v_cache.strides() == k_cache.strides(), "cache layout");
+  const nc::KvPages pages = kv_pages(table, k_cache, qkv.size(0));
+  const int64_t cap = paged ? t_max : k_cache.size(1);
   const bool has_ve = ve.has_value() && ve->defined();
   if (has_ve) {
     check_bf16(*ve, "ve"); check_bf16(*xn, "xn");
@@ -318,19 +340,20 @@ void decode_qkv_post(Tensor& qkv, int64_t H, int64_t Hkv, const Tensor& cos_t, c
                                has_ve ? wg->data_ptr<float>() : nullptr, has_ve ? ve->data_ptr() : nullptr,
                                has_ve ? ve->stride(0) : 0, has_ve ? reinterpret_cast<const long long*>(idx->data_ptr<int64_t>()) : nullptr,
                                k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0), k_cache.stride(1),
-                               (int)k_cache.size(1), (int)qkv.size(0), status_ptr(qkv), cur_stream()));
+                               (int)cap, (int)qkv.size(0), status_ptr(qkv), pages, cur_stream()));
 }
 
 // q: (B, H*128) view (row pitch free); y: (B, H*128); scratch fp32 with at least decode_attn_scratch(B, H) elements.
 void decode_attn(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& seqlens, int64_t H,
-                 int64_t Hkv, int64_t window, double scale, Tensor& scratch, Tensor& y) {
+                 int64_t Hkv, int64_t window, double scale, Tensor& scratch, Tensor& y, const optional<Tensor>& table) {
   check_bf16(q, "q"); check_bf16(y, "y");
   TORCH_CHECK(scratch.scalar_type() == at::kFloat &&
               (size_t)scratch.numel() >= nc::decode_attn_scratch_floats((int)q.size(0), (int)H), "scratch too small");
   const c10::cuda::CUDAGuard guard(q.device());
   NC_CHECK(nc::decode_attn(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), k_cache.stride(0),
                            k_cache.stride(1), seqlens.data_ptr<int>(), (int)q.size(0), (int)H, (int)Hkv, (int)window,
-                           (float)scale, scratch.data_ptr<float>(), y.data_ptr(), y.stride(0), cur_stream()));
+                           (float)scale, scratch.data_ptr<float>(), y.data_ptr(), y.stride(0),
+                           kv_pages(table, k_cache, q.size(0)), cur_stream()));
 }
 int64_t decode_attn_scratch(int64_t B, int64_t H) { return (int64_t)nc::decode_attn_scratch_floats((int)B, (int)H); }
 
@@ -518,8 +541,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemv_rows", &gemv_rows);
   m.def("gemv_rows_mix", &gemv_rows_mix);
   m.def("decode_embed", &decode_embed);
-  m.def("decode_qkv_post", &decode_qkv_post);
-  m.def("decode_attn", &decode_attn);
+  m.def("decode_qkv_post", &decode_qkv_post, py::arg("qkv"), py::arg("H"), py::arg("Hkv"), py::arg("cos"), py::arg("sin"),
+        py::arg("seqlens"), py::arg("xn"), py::arg("wg"), py::arg("ve"), py::arg("idx"), py::arg("k_cache"),
+        py::arg("v_cache"), py::arg("table") = py::none(), py::arg("t_max") = 0);
+  m.def("decode_attn", &decode_attn, py::arg("q"), py::arg("k_cache"), py::arg("v_cache"), py::arg("seqlens"), py::arg("H"),
+        py::arg("Hkv"), py::arg("window"), py::arg("scale"), py::arg("scratch"), py::arg("y"), py::arg("table") = py::none());
   m.def("decode_attn_scratch", &decode_attn_scratch);
   m.def("amax_bf16", &amax_bf16);
   m.def("quantize_bf16", &quantize_bf16);

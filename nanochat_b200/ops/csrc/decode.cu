@@ -278,6 +278,15 @@ decode_embed_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __re
   }
 }
 
+// Where token t of row b lives in one layer's K (or V) store. Contiguous cache: b * c_bat + t * c_tok. Paged cache
+// (pages.table != nullptr): the store is a pool of pages of 2^page_shift tokens, c_bat is the pitch of a page and
+// table[b * max_pages + (t >> page_shift)] names the page; rows may share pages (a common prompt prefix is held once).
+__device__ __forceinline__ long long kv_token_offset(const KvPages& pages, int b, int t, long long c_bat, long long c_tok) {
+  if (pages.table == nullptr) return b * c_bat + (long long)t * c_tok;
+  const int page = pages.table[(long long)b * pages.max_pages + (t >> pages.page_shift)];
+  return page * c_bat + (long long)(t & ((1 << pages.page_shift) - 1)) * c_tok;
+}
+
 // One warp per (row, head slot): slots [0,H) = q heads, [H,H+Hkv) = k heads, [H+Hkv,H+2Hkv) = v heads. D = 128.
 __global__ void __launch_bounds__(128)
 decode_qkv_post_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, int H, int Hkv, const __nv_bfloat16* __restrict__ cos_t,
@@ -285,7 +294,7 @@ decode_qkv_post_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, int H, int
                        const __nv_bfloat16* __restrict__ xn, long long ld_xn, const float* __restrict__ wg,
                        const __nv_bfloat16* __restrict__ ve, long long ld_ve, const long long* __restrict__ idx,
                        __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache, long long c_bat,
-                       long long c_tok, int t_max, int B, int* __restrict__ status) {
+                       long long c_tok, int t_max, int B, int* __restrict__ status, KvPages pages) {
   const int lane = threadIdx.x & 31;
   const int slot_all = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int slots = H + 2 * Hkv;
@@ -326,7 +335,7 @@ decode_qkv_post_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, int H, int
   if (slot >= H) {
     const bool is_v = slot >= H + Hkv;
     const int hkv = slot - H - (is_v ? Hkv : 0);
-    dst = (is_v ? v_cache : k_cache) + b * c_bat + (long long)pos * c_tok + hkv * 128;
+    dst = (is_v ? v_cache : k_cache) + kv_token_offset(pages, b, pos, c_bat, c_tok) + hkv * 128;
   }
   *reinterpret_cast<uint32_t*>(dst + 2 * lane) = o1;
   *reinterpret_cast<uint32_t*>(dst + 64 + 2 * lane) = o2;
@@ -340,7 +349,7 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
                    const __nv_bfloat16* __restrict__ v_cache, long long c_bat, long long c_tok,
                    const int* __restrict__ seqlens, int H, int Hkv, int window, float scale_log2,
                    float* __restrict__ partial, unsigned int* __restrict__ arrivals, __nv_bfloat16* __restrict__ y,
-                   long long ldy) {
+                   long long ldy, KvPages pages) {
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hkv = h / (H / Hkv);
@@ -361,14 +370,14 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
   const int d = threadIdx.x;
   s_q[d] = __bfloat162float(q[b * ldq + h * 128 + d]);
   __syncthreads();
-  const __nv_bfloat16* kb = k_cache + b * c_bat + hkv * 128;
-  const __nv_bfloat16* vb = v_cache + b * c_bat + hkv * 128 + lane * 4;   // phase 2: a lane owns 4 dims
+  const __nv_bfloat16* kb = k_cache + hkv * 128;
+  const __nv_bfloat16* vb = v_cache + hkv * 128 + lane * 4;   // phase 2: a lane owns 4 dims
   float M = -1.0e30f, L = 0.f, O = 0.f;
   for (int tile = k_begin; tile < k_end; tile += 128) {
     const int j = tile + d;
     float sc = -1.0e30f;
     if (j < k_end) {
-      const uint4* kr = reinterpret_cast<const uint4*>(kb + (long long)j * c_tok);
+      const uint4* kr = reinterpret_cast<const uint4*>(kb + kv_token_offset(pages, b, j, c_bat, c_tok));
       float acc = 0.f;
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
@@ -396,11 +405,10 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
     // weighted sum of V: warp w takes keys w, w+4, ... (independent 8-byte loads, many in flight), then the four
     // partial vectors are added per dim
     const int cnt = min(128, k_end - tile);
-    const __nv_bfloat16* vt = vb + (long long)tile * c_tok;
     float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll 8
     for (int jj = warp; jj < cnt; jj += 4) {
-      const uint2 vr = *reinterpret_cast<const uint2*>(vt + (long long)jj * c_tok);
+      const uint2 vr = *reinterpret_cast<const uint2*>(vb + kv_token_offset(pages, b, tile + jj, c_bat, c_tok));
       const float2 v01 = unpack_bf16(vr.x), v23 = unpack_bf16(vr.y);
       const float pw = s_p[jj];
       o0 += pw * v01.x; o1 += pw * v01.y; o2 += pw * v23.x; o3 += pw * v23.y;
@@ -493,13 +501,16 @@ cudaError_t decode_embed(const long long* ids, const void* wte, long long ldw, i
 cudaError_t decode_qkv_post(void* qkv, long long ld, int H, int Hkv, const void* cos_t, const void* sin_t,
                             const int* seqlens, const void* xn, long long ld_xn, const float* wg, const void* ve,
                             long long ld_ve, const long long* idx, void* k_cache, void* v_cache, long long c_bat,
-                            long long c_tok, int t_max, int B, int* status, cudaStream_t s) {
+                            long long c_tok, int t_max, int B, int* status, const KvPages& pages, cudaStream_t s) {
+  if (pages.table != nullptr && (pages.page_shift < 0 || pages.page_shift > 16 || pages.max_pages <= 0 ||
+                                 t_max > (pages.max_pages << pages.page_shift)))
+    return cudaErrorInvalidValue;
   const int warps = B * (H + 2 * Hkv);
   return launch_pdl(decode_qkv_post_kernel, dim3((warps + 3) / 4), dim3(128), s,
       reinterpret_cast<__nv_bfloat16*>(qkv), ld, H, Hkv, reinterpret_cast<const __nv_bfloat16*>(cos_t),
       reinterpret_cast<const __nv_bfloat16*>(sin_t), seqlens, reinterpret_cast<const __nv_bfloat16*>(xn), ld_xn, wg,
       reinterpret_cast<const __nv_bfloat16*>(ve), ld_ve, idx, reinterpret_cast<__nv_bfloat16*>(k_cache),
-      reinterpret_cast<__nv_bfloat16*>(v_cache), c_bat, c_tok, t_max, B, status);
+      reinterpret_cast<__nv_bfloat16*>(v_cache), c_bat, c_tok, t_max, B, status, pages);
 }
 
 // partial results plus one arrival counter per (row, head); the counters must start at zero (they return to zero)
@@ -507,13 +518,13 @@ size_t decode_attn_scratch_floats(int B, int H) { return (size_t)B * H * kSplits
 
 cudaError_t decode_attn(const void* q, long long ldq, const void* k_cache, const void* v_cache, long long c_bat,
                         long long c_tok, const int* seqlens, int B, int H, int Hkv, int window, float scale,
-                        float* scratch, void* y, long long ldy, cudaStream_t s) {
+                        float* scratch, void* y, long long ldy, const KvPages& pages, cudaStream_t s) {
   if (H % Hkv != 0) return cudaErrorInvalidValue;
   unsigned int* arrivals = reinterpret_cast<unsigned int*>(scratch + (size_t)B * H * kSplits * 130);
   return launch_pdl(decode_attn_kernel, dim3(kSplits, H, B), dim3(128), s,
       reinterpret_cast<const __nv_bfloat16*>(q), ldq, reinterpret_cast<const __nv_bfloat16*>(k_cache),
       reinterpret_cast<const __nv_bfloat16*>(v_cache), c_bat, c_tok, seqlens, H, Hkv, window,
-      scale * 1.4426950408889634f, scratch, arrivals, reinterpret_cast<__nv_bfloat16*>(y), ldy);
+      scale * 1.4426950408889634f, scratch, arrivals, reinterpret_cast<__nv_bfloat16*>(y), ldy, pages);
 }
 
 }  // namespace nc

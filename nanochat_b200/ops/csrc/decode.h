@@ -8,6 +8,16 @@ namespace nc {
 
 enum DecodeEpilogue : int { DEC_EPI_NONE = 0, DEC_EPI_RELU2 = 1 };
 
+// Paged KV store of one layer: a pool (n_pages, 2^page_shift tokens, Hkv, 128) plus a per-row page table
+// (B, max_pages) int32. Rows may name the same page (a prompt prefix shared by every sample of a prompt is stored
+// once). table == nullptr selects the contiguous (B, Tmax, Hkv, 128) layout; `c_bat` is then the row pitch, with a
+// table it is the page pitch.
+struct KvPages {
+  const int* table = nullptr;
+  int max_pages = 0;
+  int page_shift = 0;
+};
+
 // out[b, n] = epi(sum_k xe[b, k] * W[n, k]) + aux[b, n]   for b < B <= 8 (aux optional). K, ldx, ldw multiples of 8.
 // norm_input != 0: xe = rmsnorm(x) (the normalisation is folded into the dot products), else xe = x.
 cudaError_t gemv_rows(const void* x, long long ldx, const void* W, long long ldw, void* out, long long ldo,
@@ -30,17 +40,18 @@ cudaError_t decode_embed(const long long* ids, const void* wte, long long ldw, i
 // In place on qkv (B rows of [q heads | k heads | v heads]): rotary at position seqlens[b] + RMS norm + 1.2 on
 // q and k; v += 3*sigmoid(xn[:12] . wg[hkv]) * ve[idx[b]] when ve != nullptr; k and v are appended to the
 // caches at (b, seqlens[b]) (cache strides c_bat / c_tok in elements, heads contiguous). A row whose position
-// is outside [0, t_max) is left alone and `status` records it.
+// is outside [0, t_max) is left alone and `status` records it. With a page table (see KvPages) the token goes to
+// page table[b][pos >> page_shift]; t_max must not exceed max_pages << page_shift.
 cudaError_t decode_qkv_post(void* qkv, long long ld, int H, int Hkv, const void* cos_t, const void* sin_t,
                             const int* seqlens, const void* xn, long long ld_xn, const float* wg, const void* ve,
                             long long ld_ve, const long long* idx, void* k_cache, void* v_cache, long long c_bat,
-                            long long c_tok, int t_max, int B, int* status, cudaStream_t s);
+                            long long c_tok, int t_max, int B, int* status, const KvPages& pages, cudaStream_t s);
 
 // y[b, h, :] = softmax(q[b, h] . K[b, lo..pos, hkv] * scale) V, pos = seqlens[b], lo = max(0, pos - window)
 // (window < 0: 0). scratch: decode_attn_scratch_floats(B, H) floats, zeroed once before the first call.
 size_t decode_attn_scratch_floats(int B, int H);
 cudaError_t decode_attn(const void* q, long long ldq, const void* k_cache, const void* v_cache, long long c_bat,
                         long long c_tok, const int* seqlens, int B, int H, int Hkv, int window, float scale,
-                        float* scratch, void* y, long long ldy, cudaStream_t s);
+                        float* scratch, void* y, long long ldy, const KvPages& pages, cudaStream_t s);
 
 }  // namespace nc

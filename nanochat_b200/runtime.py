@@ -35,7 +35,9 @@ class DecodeGraph:
         self.nat, self.C_ = nat, nat._C
         self.model, self.cache = model, kv_cache
         cfg = model.config
-        dev = kv_cache.k_cache.device
+        dev = kv_cache.cache_seqlens.device
+        self.paged = getattr(kv_cache, "paged", False)
+        self.pool_version = getattr(kv_cache, "pool_version", 0)
         B, C = kv_cache.batch_size, cfg.n_embd
         self.B, self.C = B, C
         self.H, self.Hkv = cfg.n_head, cfg.n_kv_head
@@ -136,12 +138,16 @@ class DecodeGraph:
                 self._linear(self.xn, w["qkv"], self.qkv)
             ve = m.value_embeds[str(i)].weight if str(i) in m.value_embeds else None
             kc, vc = cache.get_layer_cache(i)
+            # a paged cache: one layer's page pools + the rows' page table; the row capacity bounds the append
+            table = cache.table if self.paged else None
+            t_max = cache.max_seq_len if self.paged else 0
             C_.decode_qkv_post(self.qkv, H, Hkv, self.cos, self.sin, cache.cache_seqlens,
                                self.xn if ve is not None else None, w["wg"] if ve is not None else None, ve,
-                               idx if ve is not None else None, kc, vc)
+                               idx if ve is not None else None, kc, vc, table, t_max)
             window = m.window_sizes[i][0]
             window = window if 0 <= window < cache.max_seq_len else -1
-            C_.decode_attn(self.qkv[:, :nq], kc, vc, cache.cache_seqlens, H, Hkv, window, scale, self.scratch, self.y)
+            C_.decode_attn(self.qkv[:, :nq], kc, vc, cache.cache_seqlens, H, Hkv, window, scale, self.scratch, self.y,
+                           table)
             self._linear(self.y, w["o"], self.xa, aux=self.xm)
             self._linear(self.xa, w["fc"], self.h, relu2=True, norm_input=True)   # GEMV: norm(xa) folded in
             out = self.x_backout if i == backout_layer else self.xs[i & 1]
@@ -184,20 +190,26 @@ class DecodeGraph:
         return self.logits
 
 
+def graph_path_applies(model, rows):
+    """True when `rows` sample rows of this model decode through the captured-graph kernels."""
+    from nanochat_b200.models.gpt import GPT
+    if not isinstance(model, GPT) or ops.get_kernel_mode() != "native":
+        return False
+    cfg = model.config
+    wte = model.transformer.wte.weight
+    return (wte.is_cuda and cfg.n_embd // cfg.n_head == 128 and rows <= MAX_ROWS and cfg.n_embd % 8 == 0
+            and common.COMPUTE_DTYPE == torch.bfloat16 and wte.dtype == torch.bfloat16)
+
+
 def decode_graph_for(engine, kv_cache):
     """The DecodeGraph bound to `kv_cache` (created on first use), or None when the fast path does not apply."""
-    from nanochat_b200.models.gpt import GPT
     model = engine.model
-    if not isinstance(model, GPT) or not kv_cache.k_cache.is_cuda or ops.get_kernel_mode() != "native":
-        return None
-    cfg = model.config
-    if (cfg.n_embd // cfg.n_head != 128 or kv_cache.batch_size > MAX_ROWS or common.COMPUTE_DTYPE != torch.bfloat16
-            or model.transformer.wte.weight.dtype != torch.bfloat16 or cfg.n_embd % 8 != 0
-            or not getattr(kv_cache, "pooled", False)):
+    if (not getattr(kv_cache, "pooled", False) or not kv_cache.cache_seqlens.is_cuda
+            or not graph_path_applies(model, kv_cache.batch_size)):
         return None
     graphs = engine._decode_graphs
     g = graphs.get(id(kv_cache))
-    if g is None or g.cache is not kv_cache:
-        g = DecodeGraph(model, kv_cache)
+    if g is None or g.cache is not kv_cache or g.pool_version != getattr(kv_cache, "pool_version", 0):
+        g = DecodeGraph(model, kv_cache)       # first use, or the page pool moved: capture on the new addresses
         graphs[id(kv_cache)] = g
     return g

@@ -256,3 +256,89 @@ def test_sampling_kernel_semantics():
     rng = torch.Generator(device="cuda").manual_seed(4)
     cold = nat.sample_next_token(logits, rng, 0.05, None)[:, 0]
     assert (cold == logits.argmax(-1)).float().mean().item() >= 0.5
+
+
+def test_paged_decode_kernels_match_contiguous_cache():
+    """The same keys and values behind a shuffled page table: the attention output is bitwise the contiguous one (same
+    arithmetic, other addresses), and the append writes the new token's K/V into the page its position maps to."""
+    from nanochat_b200.ops import native as nat
+    g = torch.Generator(device="cuda").manual_seed(11)
+    B, H, Hkv, T, P = 3, 4, 2, 320, 64
+    kc = torch.randn(B, T, Hkv, 128, device="cuda", generator=g).to(BF16)
+    vc = torch.randn(B, T, Hkv, 128, device="cuda", generator=g).to(BF16)
+    q = torch.randn(B, H * 128, device="cuda", generator=g).to(BF16)
+    seqlens = torch.tensor([5, 150, 299], dtype=torch.int32, device="cuda")
+    n_pages = T // P
+    perm = torch.randperm(B * n_pages, device="cuda", generator=g)
+    table = perm.view(B, n_pages).to(torch.int32).contiguous()
+    k_pool = torch.zeros(B * n_pages + 1, P, Hkv, 128, dtype=BF16, device="cuda")
+    v_pool = torch.zeros_like(k_pool)
+    k_pool[table.long().view(-1)] = kc.view(B * n_pages, P, Hkv, 128)
+    v_pool[table.long().view(-1)] = vc.view(B * n_pages, P, Hkv, 128)
+    scratch = torch.zeros(nat._C.decode_attn_scratch(B, H), dtype=torch.float32, device="cuda")
+    for window in (-1, 64):
+        want = torch.empty(B, H * 128, dtype=BF16, device="cuda")
+        got = torch.empty_like(want)
+        nat._C.decode_attn(q, kc, vc, seqlens, H, Hkv, window, 1.0 / math.sqrt(128), scratch, want)
+        nat._C.decode_attn(q, k_pool, v_pool, seqlens, H, Hkv, window, 1.0 / math.sqrt(128), scratch, got, table)
+        assert torch.equal(got, want), window
+    # append: rotary + norm of k, plain v, written at (row, seqlens[row]) through the table
+    qkv = torch.randn(B, (H + 2 * Hkv) * 128, device="cuda", generator=g).to(BF16)
+    cos = torch.randn(T, 64, device="cuda", generator=g).to(BF16)
+    sin = torch.randn(T, 64, device="cuda", generator=g).to(BF16)
+    a, b = qkv.clone(), qkv.clone()
+    kc2, vc2 = kc.clone(), vc.clone()
+    nat._C.decode_qkv_post(a, H, Hkv, cos, sin, seqlens, None, None, None, None, kc2, vc2)
+    nat._C.decode_qkv_post(b, H, Hkv, cos, sin, seqlens, None, None, None, None, k_pool, v_pool, table, T)
+    assert torch.equal(a, b)
+    for row in range(B):
+        pos = int(seqlens[row])
+        page = int(table[row, pos // P])
+        assert torch.equal(k_pool[page, pos % P], kc2[row, pos])
+        assert torch.equal(v_pool[page, pos % P], vc2[row, pos])
+    nat.check_status()
+
+
+def test_paged_engine_cache_holds_the_prompt_once():
+    """Many samples of one prompt: the page tables of all rows name the same pages for the prompt's full pages, each
+    row owns its partial page and what it decodes, the pool is far smaller than one contiguous cache per row, and the
+    tokens are those of the contiguous op-level path."""
+    from nanochat_b200 import ops
+    from nanochat_b200.engine import Engine, PagedKVCache, PAGE_TOKENS
+    model = _model()
+    cfg = model.config
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, 2040, (150,), generator=g).tolist()          # 2 full pages + 22 tokens
+    rows, new = 8, 20
+    eng = Engine(model, _Tok())
+    fast = [c for c, _ in eng.generate(prompt, num_samples=rows, max_tokens=new, temperature=0.0)]
+    cache = eng._cache_pool[rows]
+    assert isinstance(cache, PagedKVCache)
+    table = cache.table.cpu()
+    full = len(prompt) // PAGE_TOKENS
+    assert full == 2
+    assert all(table[r, :full].tolist() == [0, 1] for r in range(rows))        # shared prompt pages
+    own = table[:, full].tolist()
+    assert len(set(own)) == rows and min(own) >= cache.shared_pages            # private continuation pages
+    per_token = 2 * cfg.n_layer * cfg.n_kv_head * 128 * 2
+    contiguous = rows * (len(prompt) + new) * per_token
+    assert cache.pool_bytes() < 0.5 * contiguous, (cache.pool_bytes(), contiguous)
+    # every row's keys of the prompt are the shared ones
+    k0, _ = cache.gather_row(0, 0)
+    k5, _ = cache.gather_row(0, 5)
+    assert torch.equal(k0[:len(prompt)], k5[:len(prompt)])
+    ops.native_module().check_status()
+    eng2 = Engine(model, _Tok())
+    eng2._pooled_cache = lambda *a, **k: None
+    slow = [c for c, _ in eng2.generate(prompt, num_samples=rows, max_tokens=new, temperature=0.0)]
+    agree = 0
+    for a, b in zip(fast, slow):
+        if a != b:
+            break
+        agree += 1
+    assert agree >= 8, (agree, fast[:10], slow[:10])
+    assert all(len(set(col)) == 1 for col in fast[:8])                        # greedy: every row decodes the same tokens
+    # a longer request grows the pool; the graph is rebuilt on the new pool and still agrees with itself
+    longer = [c for c, _ in eng.generate(prompt, num_samples=rows, max_tokens=new + 70, temperature=0.0)]
+    assert longer[:agree] == fast[:agree]
+    ops.native_module().check_status()
