@@ -322,7 +322,7 @@ def test_paged_engine_cache_holds_the_prompt_once():
     assert len(set(own)) == rows and min(own) >= cache.shared_pages            # private continuation pages
     per_token = 2 * cfg.n_layer * cfg.n_kv_head * 128 * 2
     contiguous = rows * (len(prompt) + new) * per_token
-    assert cache.pool_bytes() < 0.5 * contiguous, (cache.pool_bytes(), contiguous)
+    assert cache.pool_bytes() < 0.6 * contiguous, (cache.pool_bytes(), contiguous)
     # every row's keys of the prompt are the shared ones
     k0, _ = cache.gather_row(0, 0)
     k5, _ = cache.gather_row(0, 5)
