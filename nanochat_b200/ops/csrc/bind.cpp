@@ -239,6 +239,19 @@ void softcap_ce_bwd(Tensor& logits, const Tensor& targets, const Tensor& lse, co
                               lse.data_ptr<float>(), gscale.data_ptr<float>(), gscale.numel() > 1 ? 1 : 0,
                               (int)logits.size(0), (int)V, (int)logits.size(1), (float)cap, cur_stream()));
 }
+void softcap_ce_bwd_fp8(const Tensor& logits, const Tensor& targets, const Tensor& lse, const Tensor& gscale,
+                        const Tensor& amax, Tensor& out, Tensor& inv_scale, int64_t V, double cap) {
+  const c10::cuda::CUDAGuard guard(logits.device());
+  check_bf16(logits, "logits");
+  TORCH_CHECK(out.scalar_type() == at::kFloat8_e5m2 && out.is_contiguous() && out.sizes() == logits.sizes(),
+              "out: contiguous e5m2 shaped like the logits");
+  TORCH_CHECK(amax.scalar_type() == at::kFloat && amax.numel() == 1 && inv_scale.scalar_type() == at::kFloat &&
+              inv_scale.numel() == 1, "amax / inv_scale: fp32 device scalars");
+  NC_CHECK(nc::softcap_ce_bwd_fp8(logits.data_ptr(), logits.stride(0), (const long long*)targets.data_ptr<int64_t>(),
+                                  lse.data_ptr<float>(), gscale.data_ptr<float>(), gscale.numel() > 1 ? 1 : 0,
+                                  amax.data_ptr<float>(), out.data_ptr(), inv_scale.data_ptr<float>(),
+                                  (int)logits.size(0), (int)V, (int)logits.size(1), (float)cap, cur_stream()));
+}
 void softcap_logits(const Tensor& logits, Tensor& out, int64_t V, double cap) {
   const c10::cuda::CUDAGuard guard(logits.device());
   NC_CHECK(nc::softcap_logits(logits.data_ptr(), logits.stride(0), out.data_ptr<float>(), (int)logits.size(0), (int)V,
@@ -564,6 +577,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cast_f32_bf16", &cast_f32_bf16);
   m.def("softcap_ce_fwd", &softcap_ce_fwd);
   m.def("softcap_ce_bwd", &softcap_ce_bwd);
+  m.def("softcap_ce_bwd_fp8", &softcap_ce_bwd_fp8);
   m.def("softcap_logits", &softcap_logits);
   m.def("adamw_step", &adamw_step);
   m.def("muon_momentum", &muon_momentum);

@@ -51,6 +51,10 @@ cudaError_t softcap_ce_fwd(const void* logits, long long ld, const long long* ta
 cudaError_t softcap_ce_bwd(void* logits, long long ld, const long long* targets, const float* lse,
                            const float* gscale, int gscale_stride, int M, int V, int V_padded, float cap,
                            cudaStream_t s);
+// dlogits as e5m2 with one scale (amax: device scalar bounding |dlogits|); out dense (M, V_padded) bytes.
+cudaError_t softcap_ce_bwd_fp8(const void* logits, long long ld, const long long* targets, const float* lse,
+                               const float* gscale, int gscale_stride, const float* amax, void* out, float* inv_scale,
+                               int M, int V, int V_padded, float cap, cudaStream_t s);
 // Inference: out[row, :V] = cap*tanh(l/cap) in fp32.
 cudaError_t softcap_logits(const void* logits, long long ld, float* out, int M, int V, float cap, cudaStream_t s);
 

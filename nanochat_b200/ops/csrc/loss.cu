@@ -8,6 +8,8 @@
 #include "fused.h"
 #include "rowops.cuh"
 
+#include <cuda_fp8.h>
+
 namespace nc {
 
 constexpr int CE_THREADS = 256;
@@ -84,6 +86,49 @@ softcap_ce_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const lo
   }
 }
 
+// The same gradient written as e5m2 for the fp8 dgrad / wgrad GEMMs, straight from fp32: q = sat(d * 57344 / amax),
+// *inv_scale = amax / 57344. `amax` is a device scalar that bounds |d| (|d loss / d l| never exceeds the row's
+// gradient scale), so no pass over the matrix is needed to find it and no bf16 copy of the gradient is written.
+// out: dense (M, V_padded) bytes. V_padded % 16 == 0.
+__global__ void __launch_bounds__(CE_THREADS)
+softcap_ce_bwd_fp8_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ targets,
+                          const float* __restrict__ lse_in, const float* __restrict__ gscale, int gscale_stride,
+                          const float* __restrict__ amax, uint8_t* __restrict__ out, float* __restrict__ inv_scale,
+                          int V, int V_padded, float cap) {
+  const int row = blockIdx.x;
+  const __nv_bfloat16* lrow = logits + (size_t)row * ld;
+  uint8_t* orow = out + (size_t)row * V_padded;
+  const float inv_cap = 1.f / cap;
+  const long long tgt = targets[row];
+  const float a = fmaxf(__ldg(amax), 1e-12f);
+  const float qs = 57344.f / a;
+  if (row == 0 && threadIdx.x == 0) *inv_scale = a / 57344.f;
+  const float gs = (tgt >= 0 ? gscale[(size_t)row * gscale_stride] : 0.f) * qs;
+  const float lse = lse_in[row];
+  const int nvec = V_padded >> 4;
+  for (int vi = threadIdx.x; vi < nvec; vi += CE_THREADS) {
+    float f[16];
+    unpack8(*(reinterpret_cast<const uint4*>(lrow) + 2 * vi), *reinterpret_cast<float(*)[8]>(f));
+    unpack8(*(reinterpret_cast<const uint4*>(lrow) + 2 * vi + 1), *reinterpret_cast<float(*)[8]>(f + 8));
+    uint32_t w[4];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int c = vi * 16 + j;
+      const float z = softcap(f[j], cap, inv_cap);
+      const float dz = __expf(z - lse) - (c == tgt ? 1.f : 0.f);
+      const float u = z * inv_cap;
+      f[j] = (c < V) ? gs * dz * (1.f - u * u) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_fp8x2_storage_t p0 = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * j], f[4 * j + 1]), __NV_SATFINITE, __NV_E5M2);
+      const __nv_fp8x2_storage_t p1 = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * j + 2], f[4 * j + 3]), __NV_SATFINITE, __NV_E5M2);
+      w[j] = static_cast<uint32_t>(p0) | (static_cast<uint32_t>(p1) << 16);
+    }
+    *(reinterpret_cast<uint4*>(orow) + vi) = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+}
+
 __global__ void __launch_bounds__(CE_THREADS)
 softcap_logits_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, float* __restrict__ out, int V,
                       float cap) {
@@ -107,6 +152,15 @@ cudaError_t softcap_ce_bwd(void* logits, long long ld, const long long* targets,
   if ((ld & 7) || (V_padded & 7)) return cudaErrorInvalidValue;
   softcap_ce_bwd_kernel<<<M, CE_THREADS, 0, s>>>((__nv_bfloat16*)logits, ld, targets, lse, gscale, gscale_stride, V,
                                                  V_padded, cap);
+  return cudaGetLastError();
+}
+
+cudaError_t softcap_ce_bwd_fp8(const void* logits, long long ld, const long long* targets, const float* lse,
+                               const float* gscale, int gscale_stride, const float* amax, void* out, float* inv_scale,
+                               int M, int V, int V_padded, float cap, cudaStream_t s) {
+  if ((ld & 7) || (V_padded & 15)) return cudaErrorInvalidValue;
+  softcap_ce_bwd_fp8_kernel<<<M, CE_THREADS, 0, s>>>((const __nv_bfloat16*)logits, ld, targets, lse, gscale,
+                                                     gscale_stride, amax, (uint8_t*)out, inv_scale, V, V_padded, cap);
   return cudaGetLastError();
 }
 

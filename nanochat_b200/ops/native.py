@@ -838,18 +838,22 @@ class _HeadFn(Function):
             gscale = (dout.float() / n_valid).reshape(1)
         else:
             gscale = dout.float().contiguous().view(-1)
-        _C.softcap_ce_bwd(logits, tgt, lse, gscale, vocab_size, softcap)     # logits <- dlogits
         dxn = torch.empty(M, C, dtype=BF16, device=dev)
-        if ctx.f8 is not None:
+        if ctx.f8 is not None and logits.shape[1] % 16 == 0:
             xq8, sx = ctx.f8
-            # |d loss / d logit| <= the row's gradient scale, which bounds amax without a pass over the matrix
+            # |d loss / d logit| <= the row's gradient scale, which bounds amax without a pass over the matrix; the
+            # gradient is written once, as e5m2, straight from the fp32 arithmetic (no bf16 copy, no second pass)
             amax = gscale.abs().max().reshape(1)
-            g8, sg = quantize(logits, E5M2, amax=amax)
+            g8 = torch.empty(logits.shape, dtype=E5M2, device=dev)
+            sg = torch.empty(1, dtype=torch.float32, device=dev)
+            _C.softcap_ce_bwd_fp8(logits, tgt, lse, gscale, amax, g8, sg, vocab_size, softcap)
+            del logits
             w8, sw = fp8_weight(shadow_of(w))
             gemm(g8, w8, dxn, b_mn=True, scale_a=sg, scale_b=sw)
             _accumulate_wgrad(w, g8, xq8, sg, sx)
             del g8
         else:
+            _C.softcap_ce_bwd(logits, tgt, lse, gscale, vocab_size, softcap)     # logits <- dlogits
             gemm(logits, shadow_of(w), dxn, b_mn=True)
             _accumulate_wgrad(w, logits, xn)
         dx = torch.empty(M, C, dtype=BF16, device=dev)
