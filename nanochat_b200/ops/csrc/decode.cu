@@ -353,6 +353,21 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
   const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int hkv = h / (H / Hkv);
+  // The row's page table does not change while a sequence is decoded (and the kernel before this one in the stream
+  // does not write it), so it is copied to shared memory before the wait on that kernel: the lookups of the key loop
+  // then cost a shared-memory read instead of a dependent global load in front of every key.
+  __shared__ int s_table[128];
+  if (pages.table != nullptr && pages.max_pages <= 128) {
+    if ((int)threadIdx.x < pages.max_pages) s_table[threadIdx.x] = pages.table[(long long)b * pages.max_pages + threadIdx.x];
+    pages.table = nullptr;
+    pages.max_pages = -1;                             // marks "table in shared memory" for the address helper below
+  }
+  auto token_offset = [&](int t) -> long long {
+    if (pages.max_pages == -1) {
+      return s_table[t >> pages.page_shift] * c_bat + (long long)(t & ((1 << pages.page_shift) - 1)) * c_tok;
+    }
+    return kv_token_offset(pages, b, t, c_bat, c_tok);
+  };
   pdl_wait();
   pdl_trigger();
   const int pos = seqlens[b];                         // the new token sits at `pos`; it sees keys lo..pos
@@ -377,7 +392,7 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
     const int j = tile + d;
     float sc = -1.0e30f;
     if (j < k_end) {
-      const uint4* kr = reinterpret_cast<const uint4*>(kb + kv_token_offset(pages, b, j, c_bat, c_tok));
+      const uint4* kr = reinterpret_cast<const uint4*>(kb + token_offset(j));
       float acc = 0.f;
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
@@ -408,7 +423,7 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, const __n
     float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll 8
     for (int jj = warp; jj < cnt; jj += 4) {
-      const uint2 vr = *reinterpret_cast<const uint2*>(vb + kv_token_offset(pages, b, tile + jj, c_bat, c_tok));
+      const uint2 vr = *reinterpret_cast<const uint2*>(vb + token_offset(tile + jj));
       const float2 v01 = unpack_bf16(vr.x), v23 = unpack_bf16(vr.y);
       const float pw = s_p[jj];
       o0 += pw * v01.x; o1 += pw * v01.y; o2 += pw * v23.x; o3 += pw * v23.y;
