@@ -248,6 +248,70 @@ __device__ __forceinline__ void store_tile_bf16_staged(const GemmKernelArgs& arg
   }
 }
 
+// fp32 epilogue through the same per-warp staging tile: 32 columns (128 B of fp32) of the warp's 32 rows per pass, written
+// out as whole 128-byte lines. Weight gradients are the fp32 outputs; on several GPUs the last micro-batch writes them
+// into another rank's memory over NVLink, where a warp-wide store of 32 scattered 16-byte pieces (one per row) costs a
+// packet each while a 128-byte line travels as one. The auxiliary operand (the gradient accumulated so far) is read
+// the same way.
+template <int BN>
+__device__ __forceinline__ void store_tile_f32_staged(const GemmKernelArgs& args, uint32_t taddr, int b, int row0, int n0,
+                                                      float alpha, float beta, float& amax, int c_begin, int c_end,
+                                                      uint8_t* stage, int lane) {
+  float* cbase = reinterpret_cast<float*>(args.C) + b * args.bsc;
+  const float* xbase = args.aux ? reinterpret_cast<const float*>(args.aux) + b * args.bsaux : nullptr;
+  const int sub_r = lane >> 3, unit = lane & 7;     // coalesced phase: 4 rows x 8 units (16 B = 4 floats) per instruction
+#pragma unroll 1
+  for (int g = c_begin; g < c_end; g += 2) {
+    const int nch = min(2, c_end - g);              // 16-column chunks in this pass
+    const int col0 = n0 + g * 16;
+    if (xbase) {
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int r = it * 4 + sub_r;
+        const int col = col0 + unit * 4;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row0 + r < args.M && unit < nch * 4 && col + 4 <= args.N)
+          v = *reinterpret_cast<const float4*>(xbase + static_cast<long long>(row0 + r) * args.ldaux + col);
+        *reinterpret_cast<float4*>(stage + r * 128 + ((unit ^ (r & 7)) << 4)) = v;
+      }
+      __syncwarp();
+    }
+    uint32_t acc[2][16];
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc)
+      if (cc < nch) tmem_ld16(taddr + (g + cc) * 16, acc[cc]);
+    tmem_wait_ld();
+#pragma unroll
+    for (int cc = 0; cc < 2; ++cc) {
+      if (cc < nch) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint8_t* slot = stage + lane * 128 + (((cc * 4 + q) ^ (lane & 7)) << 4);
+          float4 o = make_float4(__uint_as_float(acc[cc][q * 4]) * alpha, __uint_as_float(acc[cc][q * 4 + 1]) * alpha,
+                                 __uint_as_float(acc[cc][q * 4 + 2]) * alpha, __uint_as_float(acc[cc][q * 4 + 3]) * alpha);
+          if (xbase) {
+            const float4 x = *reinterpret_cast<const float4*>(slot);
+            o.x += beta * x.x; o.y += beta * x.y; o.z += beta * x.z; o.w += beta * x.w;
+          }
+          if (row0 + lane < args.M && col0 + (cc * 4 + q) * 4 + 4 <= args.N)
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(o.x), fabsf(o.y)), fmaxf(fabsf(o.z), fabsf(o.w))));
+          *reinterpret_cast<float4*>(slot) = o;
+        }
+      }
+    }
+    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int r = it * 4 + sub_r;
+      const int col = col0 + unit * 4;
+      if (row0 + r < args.M && unit < nch * 4 && col + 4 <= args.N)
+        *reinterpret_cast<float4*>(cbase + static_cast<long long>(row0 + r) * args.ldc + col) =
+            *reinterpret_cast<const float4*>(stage + r * 128 + ((unit ^ (r & 7)) << 4));
+    }
+    __syncwarp();                                   // the tile is reused by the next pass
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN, bool FP8>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -365,7 +429,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int row = mb * BM + quad * 32 + lane;
       const int n0 = nb * BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC_STRIDE;
-      if (args.c_f32)
+      if (args.c_f32 && args.epi == EPI_LINEAR)
+        store_tile_f32_staged<BN>(args, taddr, b, mb * BM + quad * 32, n0, alpha, beta, amax, c_begin, c_end,
+                                  epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane);
+      else if (args.c_f32)
         store_tile_row<BN>(args, taddr, b, row, n0, alpha, beta, amax, c_begin, c_end);
       else
         store_tile_bf16_staged<BN>(args, taddr, b, mb * BM + quad * 32, n0, alpha, beta, amax, c_begin, c_end,
@@ -553,7 +620,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int row = mb * (2 * BM) + rank * BM + quad * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC_STRIDE;
-      if (args.c_f32)
+      if (args.c_f32 && args.epi == EPI_LINEAR)
+        store_tile_f32_staged<BN>(args, taddr, b, mb * (2 * BM) + rank * BM + quad * 32, nb * BN, alpha, beta, amax,
+                                  c_begin, c_end, epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane);
+      else if (args.c_f32)
         store_tile_row<BN>(args, taddr, b, row, nb * BN, alpha, beta, amax, c_begin, c_end);
       else
         store_tile_bf16_staged<BN>(args, taddr, b, mb * (2 * BM) + rank * BM + quad * 32, nb * BN, alpha, beta, amax,

@@ -170,9 +170,10 @@ class SymmComm:
         self.epoch = 0
         import os
         self.trace = _StepTrace(os.environ.get("NANOCHAT_OPT_TRACE", "0") == "1")
-        # NANOCHAT_OPT_OVERLAP=0 runs the whole step on one stream (stage times then add up in the trace);
-        # NANOCHAT_OPT_LINK_CTAS caps the grid of the pulling kernels while they share the GPU with the GEMMs
-        self.overlap = os.environ.get("NANOCHAT_OPT_OVERLAP", "1") != "0"
+        # NANOCHAT_OPT_OVERLAP=1 runs the slot sums + AdamW kernels on a second stream beside the Newton-Schulz GEMMs
+        # (default off: since the gradients arrive by push those kernels read local memory and take ~2 ms; measured
+        # at 2 and 4 GPUs the overlap gives nothing and slows the GEMMs); NANOCHAT_OPT_LINK_CTAS caps their grid then
+        self.overlap = os.environ.get("NANOCHAT_OPT_OVERLAP", "0") != "0"
         self.link_ctas = int(os.environ.get("NANOCHAT_OPT_LINK_CTAS", "296")) if self.overlap else 0
         self._link_stream = torch.cuda.Stream(device=dev)
         self.time_updates = False     # benchmarks: keep an event pair per step, read with `update_ms()`
@@ -244,7 +245,7 @@ class SymmComm:
         main = torch.cuda.current_stream()
         self._link_stream.wait_stream(main)
         with torch.cuda.stream(self._link_stream):
-            self._push_sharded(d["grad"], self.stage_plan[id(p)], self.link_ctas)
+            self._push_sharded(d["grad"], self.stage_plan[id(p)], 148)    # few CTAs: it shares the GPU with the backward pass
         self._pushed.add(id(p))
 
     def begin_last_microbatch(self):
