@@ -43,6 +43,7 @@ struct GemmKernelArgs {
   float* amax_out;          // optional: max |C| over everything this launch stores (atomic, fp32 bits)
   int epi;
   int c_f32;
+  int f32_staged;           // fp32 output through the staging tile (whole 128-byte lines) instead of per-row pieces
   int m_blocks, n_blocks, group_m;
   uint32_t idesc;
   int* status;
@@ -429,7 +430,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int row = mb * BM + quad * 32 + lane;
       const int n0 = nb * BN;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC_STRIDE;
-      if (args.c_f32 && args.epi == EPI_LINEAR)
+      if (args.c_f32 && args.f32_staged && args.epi == EPI_LINEAR)
         store_tile_f32_staged<BN>(args, taddr, b, mb * BM + quad * 32, n0, alpha, beta, amax, c_begin, c_end,
                                   epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane);
       else if (args.c_f32)
@@ -620,7 +621,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_after();
       const int row = mb * (2 * BM) + rank * BM + quad * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC_STRIDE;
-      if (args.c_f32 && args.epi == EPI_LINEAR)
+      if (args.c_f32 && args.f32_staged && args.epi == EPI_LINEAR)
         store_tile_f32_staged<BN>(args, taddr, b, mb * (2 * BM) + rank * BM + quad * 32, nb * BN, alpha, beta, amax,
                                   c_begin, c_end, epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane);
       else if (args.c_f32)
@@ -663,6 +664,15 @@ static int group_m_override(int dflt) {
   return env > 0 ? env : dflt;
 }
 
+// NANOCHAT_F32_EPILOGUE=direct selects the per-row fp32 stores (A/B measurements); default: staged.
+static int f32_staged_default() {
+  static const int v = [] {
+    const char* e = getenv("NANOCHAT_F32_EPILOGUE");
+    return (e && e[0] == 'd') ? 0 : 1;
+  }();
+  return v;
+}
+
 template <int BN, bool A_MN, bool B_MN, bool FP8>
 static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t stream) {
   using C = Cfg<BN, A_MN, B_MN, FP8>;
@@ -698,7 +708,7 @@ static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t strea
   a.M = d.M; a.N = d.N; a.K = d.K; a.batch = d.batch;
   a.C = d.C; a.ldc = d.ldc; a.bsc = d.bsc;
   a.aux = d.aux; a.ldaux = d.ldaux; a.bsaux = d.bsaux;
-  a.alpha = d.alpha; a.beta = d.beta; a.epi = d.epi; a.c_f32 = d.c_f32;
+  a.alpha = d.alpha; a.beta = d.beta; a.epi = d.epi; a.c_f32 = d.c_f32; a.f32_staged = f32_staged_default();
   a.scale_a = d.scale_a; a.scale_b = d.scale_b; a.amax_out = d.amax_out;
   a.m_blocks = (d.M + BM - 1) / BM;
   a.n_blocks = (d.N + BN - 1) / BN;
@@ -758,7 +768,7 @@ static cudaError_t launch_pair_cfg(const GemmDesc& d, int* status, cudaStream_t 
   a.M = d.M; a.N = d.N; a.K = d.K; a.batch = d.batch;
   a.C = d.C; a.ldc = d.ldc; a.bsc = d.bsc;
   a.aux = d.aux; a.ldaux = d.ldaux; a.bsaux = d.bsaux;
-  a.alpha = d.alpha; a.beta = d.beta; a.epi = d.epi; a.c_f32 = d.c_f32;
+  a.alpha = d.alpha; a.beta = d.beta; a.epi = d.epi; a.c_f32 = d.c_f32; a.f32_staged = f32_staged_default();
   a.scale_a = d.scale_a; a.scale_b = d.scale_b; a.amax_out = d.amax_out;
   a.m_blocks = (d.M + 2 * BM - 1) / (2 * BM);
   a.n_blocks = (d.N + BN - 1) / BN;
