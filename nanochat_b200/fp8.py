@@ -12,10 +12,12 @@ Recipes
               gradients in the two backward GEMMs (the reference's only recipe). Runs on
               `torch._scaled_mm`; kept as the numerical comparison point.
   mxfp8       block scaling: every 32 consecutive elements along the reduction dim share one
-              power-of-two (E8M0) scale, so quantisation needs no global amax pass and can be fused
-              into the producer of the tensor. Executed by the tcgen05 block-scaled GEMM when the
-              extension provides it, otherwise emulated (quantise-dequantise to bf16 + bf16 GEMM)
-              so the numerics can be studied anywhere.
+              power-of-two (E8M0) scale, so quantisation needs no global amax pass. On a B200 with
+              the native kernels the three matmuls of a layer run on the hardware block-scaled GEMM
+              (`tcgen05.mma.kind::mxf8f6f4.block_scale`, `ops/csrc/gemm.cu: gemm_mx_kernel`) on
+              operands quantised by `ops/csrc/quant.cu: mx_quantize_bf16_kernel`; elsewhere, or when a
+              reduction dim is not a multiple of 128, the same numerics are emulated
+              (quantise-dequantise to bf16 + bf16 GEMM).
 `rowwise` is accepted by the command line of the reference but rejected here exactly as there.
 """
 
@@ -91,6 +93,37 @@ class _MxEmulatedMatmul(torch.autograd.Function):
         return dx, dw.to(w.dtype)
 
 
+class _MxHardwareMatmul(torch.autograd.Function):
+    """MXFP8 on the tensor cores: each of the three products quantises its two operands along ITS reduction dim
+    (activations / weights e4m3, output gradients e5m2) and runs the block-scaled GEMM."""
+
+    @staticmethod
+    def forward(ctx, x2, w):
+        from nanochat_b200 import ops
+        nat = ops.native_module()
+        ctx.save_for_backward(x2, w)
+        return nat.mx_linear(x2, w)                                              # (M, K) x (N, K)^T, reduce over K
+
+    @staticmethod
+    def backward(ctx, dy):
+        from nanochat_b200 import ops
+        nat = ops.native_module()
+        x2, w = ctx.saved_tensors
+        E5M2 = torch.float8_e5m2
+        dy = dy.to(torch.bfloat16)
+        wt = w.to(torch.bfloat16).t().contiguous()                               # (K, N): reduce over N
+        dx = nat.mx_linear(dy, wt, x_dtype=E5M2)
+        dyt, xt = dy.t().contiguous(), x2.to(torch.bfloat16).t().contiguous()    # (N, M), (K, M): reduce over M
+        dw = nat.mx_linear(dyt, xt, x_dtype=E5M2, out_dtype=torch.float32)
+        return dx.to(x2.dtype), dw.to(w.dtype)
+
+
+def _mx_hardware_ok(x2, w):
+    """The block-scaled GEMM needs every reduction dim (K, N and M of the three products) to be a multiple of 128."""
+    return (_native_active() and x2.is_cuda and x2.dtype == torch.bfloat16
+            and x2.shape[0] % 128 == 0 and x2.shape[1] % 128 == 0 and w.shape[0] % 128 == 0)
+
+
 class Float8Linear(nn.Linear):
     """nn.Linear whose matmuls run in FP8; weights (and bias) keep their storage precision."""
 
@@ -104,7 +137,7 @@ class Float8Linear(nn.Linear):
             return ops.linear(x, self.weight)
         x2 = x.reshape(-1, x.shape[-1])
         if self.recipe == "mxfp8":
-            y = _MxEmulatedMatmul.apply(x2, self.weight)
+            y = (_MxHardwareMatmul if _mx_hardware_ok(x2, self.weight) else _MxEmulatedMatmul).apply(x2, self.weight)
         else:
             y = _TensorwiseMatmul.apply(x2, self.weight)
         y = y.reshape(*x.shape[:-1], y.shape[-1])
@@ -156,6 +189,9 @@ def convert_to_float8_training(module, *, config=None, module_filter_fn=None):
     walk(module)
     if recipe == "tensorwise":
         _set_native_fp8(True)
+    else:
+        # the fused per-layer path runs the tensorwise recipe only; block-scaled layers go through the modules
+        module._fp8_module_path = True
     return module
 
 

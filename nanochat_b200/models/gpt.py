@@ -340,7 +340,8 @@ class GPT(nn.Module):
         T0 = 0 if kv_cache is None else kv_cache.get_pos()
         cos_sin = self.cos[:, T0:T0 + T], self.sin[:, T0:T0 + T]
 
-        if kv_cache is None and common.COMPUTE_DTYPE == torch.bfloat16 and ops.use_native(self.transformer.wte.weight):
+        if (kv_cache is None and common.COMPUTE_DTYPE == torch.bfloat16 and ops.use_native(self.transformer.wte.weight)
+                and not getattr(self, "_fp8_module_path", False)):
             return self._forward_native(idx, targets, cos_sin, loss_reduction)
 
         if (kv_cache is not None and T > 1 and T0 == 0 and kv_cache.prev_embedding is None

@@ -102,6 +102,48 @@ void gemm(const Tensor& A, const Tensor& B, Tensor& C, const optional<Tensor>& a
   }
 }
 
+// MXFP8: A (M, K) and B (N, K) row-major fp8, sfa / sfb uint8 in the blocked scale layout (see gemm.h), C (M, N).
+void gemm_mx(const Tensor& A, const Tensor& sfa, const Tensor& B, const Tensor& sfb, Tensor& C, const optional<Tensor>& aux,
+             double alpha, double beta, int64_t epi, int64_t bn) {
+  auto is8 = [](const Tensor& t) { return t.scalar_type() == at::kFloat8_e4m3fn || t.scalar_type() == at::kFloat8_e5m2; };
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && is8(A) && is8(B) && A.dim() == 2 && B.dim() == 2, "gemm_mx: 2-D fp8 operands");
+  TORCH_CHECK(A.stride(1) == 1 && B.stride(1) == 1 && C.stride(1) == 1 && A.size(1) == B.size(1), "gemm_mx: K-major A, B");
+  TORCH_CHECK(C.scalar_type() == at::kBFloat16 || C.scalar_type() == at::kFloat, "gemm_mx: C bf16 or fp32");
+  TORCH_CHECK(C.size(0) == A.size(0) && C.size(1) == B.size(0), "gemm_mx: C shape");
+  const int64_t M = A.size(0), N = B.size(0), K = A.size(1);
+  TORCH_CHECK(K % 128 == 0, "gemm_mx: K must be a multiple of 128");
+  auto chunks = [&](int64_t rows) { return ((rows + 127) / 128) * (K / 128) * 512; };
+  TORCH_CHECK(sfa.scalar_type() == at::kByte && sfa.is_contiguous() && sfa.numel() >= chunks(M), "gemm_mx: sfa too small");
+  TORCH_CHECK(sfb.scalar_type() == at::kByte && sfb.is_contiguous() && sfb.numel() >= chunks(N), "gemm_mx: sfb too small");
+  const c10::cuda::CUDAGuard guard(A.device());
+  nc::GemmDesc d{};
+  d.batch = 1; d.M = (int)M; d.N = (int)N; d.K = (int)K;
+  d.A = A.data_ptr(); d.lda = A.stride(0); d.B = B.data_ptr(); d.ldb = B.stride(0);
+  d.C = C.data_ptr(); d.c_f32 = C.scalar_type() == at::kFloat; d.ldc = C.stride(0);
+  if (aux.has_value() && aux->defined()) {
+    TORCH_CHECK(aux->scalar_type() == C.scalar_type() && aux->stride(1) == 1, "aux must match C");
+    d.aux = aux->data_ptr(); d.ldaux = aux->stride(0);
+  }
+  d.alpha = (float)alpha; d.beta = (float)beta; d.epi = (int)epi; d.bn = (int)bn;
+  d.a_e5m2 = A.scalar_type() == at::kFloat8_e5m2;
+  d.b_e5m2 = B.scalar_type() == at::kFloat8_e5m2;
+  nc::MxScales sf{sfa.data_ptr<uint8_t>(), sfb.data_ptr<uint8_t>()};
+  NC_CHECK(nc::gemm_mxfp8(d, sf, status_ptr(A), cur_stream()));
+}
+// x (R, K) bf16 rows -> q (R, K) fp8 (its dtype picks the format) + blocked E8M0 scales (pre-filled by the caller).
+void mx_quantize(const Tensor& x, Tensor& q, Tensor& sf) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && q.is_contiguous() && q.sizes() == x.sizes(), "mx_quantize: shapes");
+  TORCH_CHECK(q.scalar_type() == at::kFloat8_e4m3fn || q.scalar_type() == at::kFloat8_e5m2, "mx_quantize: q fp8");
+  const int64_t R = x.size(0), K = x.size(1);
+  TORCH_CHECK(K % 128 == 0, "mx_quantize: K must be a multiple of 128");
+  TORCH_CHECK(sf.scalar_type() == at::kByte && sf.is_contiguous() && sf.numel() >= ((R + 127) / 128) * (K / 128) * 512,
+              "mx_quantize: scale buffer too small");
+  const c10::cuda::CUDAGuard guard(x.device());
+  NC_CHECK(nc::mx_quantize_bf16(x.data_ptr(), x.stride(0), (int)R, (int)K, q.data_ptr(), sf.data_ptr<uint8_t>(),
+                                q.scalar_type() == at::kFloat8_e5m2, cur_stream()));
+}
+
 int64_t gemm_pick_bn(int64_t M, int64_t N, int64_t batch) { return nc::gemm_pick_bn((int)M, (int)N, (int)batch); }
 
 std::vector<int64_t> read_status(const Tensor& like) {
@@ -562,6 +604,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("decode_attn_scratch", &decode_attn_scratch);
   m.def("amax_bf16", &amax_bf16);
   m.def("quantize_bf16", &quantize_bf16);
+  m.def("gemm_mx", &gemm_mx);
+  m.def("mx_quantize", &mx_quantize);
   m.def("read_status", &read_status);
   m.def("launch_count", &launch_count);
   m.def("mixnorm_fwd", &mixnorm_fwd);

@@ -464,6 +464,184 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
 }
 
+// ------------------------------------------------------------------ block-scaled (MXFP8) kernel
+// kind::mxf8f6f4.block_scale: A (M x K) and B (N x K) K-major 8-bit floats, one E8M0 scale per 32 elements of K.
+// The pipeline is the single-CTA one above plus the scale factors: each k-block (128 elements of K = four MMAs of
+// K = 32) brings one 512-byte chunk of A scales (128 rows x 4 K blocks) and BN/128 chunks of B scales into shared memory
+// with untiled bulk copies on the stage's barrier; the MMA thread moves them into tensor memory with tcgen05.cp (32 rows
+// x 16 bytes, replicated over the four lane quadrants: lane l holds the scales of rows l % 32 + 32 g in column g, one
+// byte per K block) and issues the four MMAs with the scale-factor id of their K block. tcgen05.cp and tcgen05.mma of
+// one thread execute in order, so the same scale columns are reused by every k-block. Tensor memory: accumulators in
+// columns [0, 256) (two stages of 128 columns, or one of 256), scales from column 256 on.
+template <int BN>
+struct MxCfg {
+  static_assert(BN == 128 || BN == 256, "MXFP8 tiles are 128 x 128 or 128 x 256");
+  static constexpr int BK = 128;
+  static constexpr int A_BYTES = BM * ROW_BYTES;
+  static constexpr int B_BYTES = BN * ROW_BYTES;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int SF_CHUNK = 512;
+  static constexpr int SFB_CHUNKS = BN / 128;
+  static constexpr int SF_STAGE = SF_CHUNK * (1 + SFB_CHUNKS);
+  static constexpr int EPI_BYTES = 8 * 32 * 128;
+  static constexpr int MAX_STAGES = (227 * 1024 - 2048 - EPI_BYTES) / (STAGE_BYTES + SF_STAGE);
+  static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
+  static constexpr int ACC_STAGES = BN == 256 ? 1 : 2;
+  static constexpr int ACC_STRIDE = BN;
+  static constexpr int SF_COL = 256;
+  static constexpr int TMEM_COLS = 512;
+  static constexpr int SMEM_BYTES = STAGES * (STAGE_BYTES + SF_STAGE) + 1024 /*align*/ + 512 /*barriers*/ + EPI_BYTES;
+};
+
+struct MxKernelScales {
+  const unsigned char* sfa;
+  const unsigned char* sfb;
+  int k_blocks;        // K / 128
+  int sfb_row_blocks;  // ceil(N / 128): chunks beyond it do not exist and are not fetched
+};
+
+template <int BN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const GemmKernelArgs args, const MxKernelScales sf) {
+  using C = MxCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* empty = full + C::STAGES;
+  uint64_t* acc_full = empty + C::STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES + 512;      // 8 x 4 KB, 128-byte aligned
+  uint8_t* sf_smem = epi_stage + C::EPI_BYTES;                       // STAGES x (A chunk | B chunks), 512-byte chunks
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_kb = sf.k_blocks;
+  const int total_tiles = args.m_blocks * args.n_blocks * args.batch;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&acc_full[s], 1); mbar_init(&acc_empty[s], EPI_WARPS); }
+    *abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
+  if (warp == 1) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ producer: operand tiles + scale chunks
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int b, mb, nb; tile_coords(t, args, b, mb, nb);
+        const int m0 = mb * BM, n0 = nb * BN;
+        int sfb_have = sf.sfb_row_blocks - nb * C::SFB_CHUNKS;          // B scale chunks that exist for this tile
+        sfb_have = sfb_have < 0 ? 0 : (sfb_have > C::SFB_CHUNKS ? C::SFB_CHUNKS : sfb_have);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, args.status, ST_WAIT_EMPTY, t)) { ok = false; break; }
+          uint8_t* sA = tiles + stage * C::STAGE_BYTES;
+          uint8_t* sB = sA + C::A_BYTES;
+          uint8_t* sS = sf_smem + stage * C::SF_STAGE;
+          mbar_arrive_expect_tx(&full[stage], C::A_BYTES + C::B_BYTES + C::SF_CHUNK * (1 + sfb_have));
+          tma_load_3d(sA, &tmA, &full[stage], kb * C::BK, m0, b);
+          tma_load_3d(sB, &tmB, &full[stage], kb * C::BK, n0, b);
+          bulk_load_1d(sS, sf.sfa + (static_cast<size_t>(mb) * num_kb + kb) * C::SF_CHUNK, C::SF_CHUNK, &full[stage]);
+          for (int j = 0; j < sfb_have; ++j)
+            bulk_load_1d(sS + C::SF_CHUNK * (1 + j),
+                         sf.sfb + (static_cast<size_t>(nb * C::SFB_CHUNKS + j) * num_kb + kb) * C::SF_CHUNK, C::SF_CHUNK,
+                         &full[stage]);
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // -------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0; bool ok = true;
+      int acc = 0; uint32_t acc_phase = 0;
+      const uint32_t sfa_tmem = tmem_base + C::SF_COL, sfb_tmem = tmem_base + C::SF_COL + 4;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag, args.status, ST_WAIT_TMEM_EMPTY, t)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * C::ACC_STRIDE;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, args.status, ST_WAIT_FULL, t)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + stage * C::STAGE_BYTES);
+          const uint32_t b_addr = a_addr + C::A_BYTES;
+          const uint32_t s_addr = smem_u32(sf_smem + stage * C::SF_STAGE);
+          tmem_cp_32x128b_warpx4(sfa_tmem, umma_desc_noswizzle(s_addr, 128, 128));
+#pragma unroll
+          for (int j = 0; j < C::SFB_CHUNKS; ++j)
+            tmem_cp_32x128b_warpx4(sfb_tmem + 4 * j, umma_desc_noswizzle(s_addr + C::SF_CHUNK * (1 + j), 128, 128));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t a_desc = umma_desc_sw128(a_addr + k * 32, 16, 1024);
+            const uint64_t b_desc = umma_desc_sw128(b_addr + k * 32, 16, 1024);
+            const uint32_t idesc = args.idesc | (static_cast<uint32_t>(k) << 29) | (static_cast<uint32_t>(k) << 4);
+            mma_mxf8(d_tmem, a_desc, b_desc, idesc, sfa_tmem, sfb_tmem, (kb | k) != 0);
+          }
+          mma_commit(&empty[stage]);   // frees the stage (tiles and scale chunks) once the copies and MMAs have read it
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        mma_commit(&acc_full[acc]);
+        if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const int quad = warp & 3;
+    constexpr int CHUNKS = BN / 16, SPLIT = (CHUNKS + 1) / 2;
+    const int c_begin = (warp - 2) < 4 ? 0 : SPLIT, c_end = (warp - 2) < 4 ? SPLIT : CHUNKS;
+    int acc = 0; uint32_t acc_phase = 0; bool ok = true;
+    float amax = 0.f;
+    const float alpha = args.alpha, beta = args.beta;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int b, mb, nb; tile_coords(t, args, b, mb, nb);
+      if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, args.status, ST_WAIT_TMEM_FULL, t)) { ok = false; break; }
+      tc_fence_after();
+      const int row = mb * BM + quad * 32 + lane;
+      const int n0 = nb * BN;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * C::ACC_STRIDE;
+      if (args.c_f32 && args.f32_staged && args.epi == EPI_LINEAR)
+        store_tile_f32_staged<BN>(args, taddr, b, mb * BM + quad * 32, n0, alpha, beta, amax, c_begin, c_end,
+                                  epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane);
+      else if (args.c_f32)
+        store_tile_row<BN>(args, taddr, b, row, n0, alpha, beta, amax, c_begin, c_end);
+      else
+        store_tile_bf16_staged<BN>(args, taddr, b, mb * BM + quad * 32, n0, alpha, beta, amax, c_begin, c_end,
+                                   epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (++acc == C::ACC_STAGES) { acc = 0; acc_phase ^= 1; }
+    }
+    if (args.amax_out) {
+#pragma unroll
+      for (int w = 16; w > 0; w >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, w));
+      if (lane == 0 && amax > 0.f) atomicMax(reinterpret_cast<unsigned int*>(args.amax_out), __float_as_uint(amax));
+    }
+  }
+
+  __syncthreads();
+  if (*abort_flag) {
+    unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::TMEM_COLS);
+  }
+}
+
 // ------------------------------------------------------------------ CTA-pair kernel
 // Same pipeline with cta_group::2: a cluster of two CTAs computes one 256 x BN tile. Each CTA loads its
 // own 128 rows of A and its own half (BN/2 columns) of B, so a k-block costs each SM 16 KB + BN/2 * 128 B
@@ -893,6 +1071,62 @@ cudaError_t gemm_fp8(const GemmDesc& d, int* status, cudaStream_t stream) {
   const GemmPlan p = gemm_plan(d, true);
   if (best_is_invalid(p, d)) return cudaErrorInvalidValue;
   return launch_major<true>(p.bn, p.pair, d, status, stream);
+}
+
+
+template <int BN>
+static cudaError_t launch_mx(const GemmDesc& d, const MxScales& sf, int* status, cudaStream_t stream) {
+  using C = MxCfg<BN>;
+  static PerDeviceOnce configured;
+  auto kern = gemm_mx_kernel<BN>;
+  cudaError_t ce = configured.once(
+      [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES); });
+  if (ce != cudaSuccess) return ce;
+  CUtensorMap tmA, tmB;
+  const uint64_t batch = 1;
+  {
+    uint64_t dims[3] = {(uint64_t)d.K, (uint64_t)d.M, batch}, str[2];
+    uint32_t box[3] = {C::BK, BM, 1};
+    str[0] = static_cast<uint64_t>(d.lda);
+    str[1] = str[0] * dims[1];
+    if (!make_tmap(&tmA, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.A, dims, str, box)) return cudaErrorInvalidValue;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)d.K, (uint64_t)d.N, batch}, str[2];
+    uint32_t box[3] = {C::BK, BN, 1};
+    str[0] = static_cast<uint64_t>(d.ldb);
+    str[1] = str[0] * dims[1];
+    if (!make_tmap(&tmB, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.B, dims, str, box)) return cudaErrorInvalidValue;
+  }
+  GemmKernelArgs a;
+  a.M = d.M; a.N = d.N; a.K = d.K; a.batch = 1;
+  a.C = d.C; a.ldc = d.ldc; a.bsc = 0;
+  a.aux = d.aux; a.ldaux = d.ldaux; a.bsaux = 0;
+  a.alpha = d.alpha; a.beta = d.beta; a.epi = d.epi; a.c_f32 = d.c_f32; a.f32_staged = f32_staged_default();
+  a.scale_a = nullptr; a.scale_b = nullptr; a.amax_out = d.amax_out;
+  a.m_blocks = (d.M + BM - 1) / BM;
+  a.n_blocks = (d.N + BN - 1) / BN;
+  a.group_m = group_m_override(16);
+  a.idesc = umma_idesc_mxf8(BM, BN, d.a_e5m2, d.b_e5m2, 0, 0);
+  a.status = status;
+  MxKernelScales ks;
+  ks.sfa = sf.sfa; ks.sfb = sf.sfb; ks.k_blocks = d.K / 128; ks.sfb_row_blocks = (d.N + 127) / 128;
+  const long long tiles = 1ll * a.m_blocks * a.n_blocks;
+  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  kern<<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, a, ks);
+  return cudaGetLastError();
+}
+
+cudaError_t gemm_mxfp8(const GemmDesc& d, const MxScales& sf, int* status, cudaStream_t stream) {
+  if (d.M <= 0 || d.N <= 0 || d.K <= 0) return cudaSuccess;
+  if (d.a_mn || d.b_mn || d.batch != 1 || (d.K % 128) || (d.lda % 16) || (d.ldb % 16) || !sf.sfa || !sf.sfb ||
+      (reinterpret_cast<uintptr_t>(sf.sfa) & 15) || (reinterpret_cast<uintptr_t>(sf.sfb) & 15))
+    return cudaErrorInvalidValue;
+  if (d.c_f32 ? (d.N % 4) : (d.N % 8)) return cudaErrorInvalidValue;
+  const int bn = d.bn ? d.bn : (d.N > 128 ? 256 : 128);
+  if (bn == 256) return launch_mx<256>(d, sf, status, stream);
+  if (bn == 128) return launch_mx<128>(d, sf, status, stream);
+  return cudaErrorInvalidValue;
 }
 
 }  // namespace nc

@@ -39,6 +39,22 @@ struct GemmDesc {
 };
 
 cudaError_t gemm_bf16(const GemmDesc& d, int* status, cudaStream_t stream);
+
+// Block-scaled 8-bit GEMM (MXFP8: tcgen05.mma.kind::mxf8f6f4.block_scale): A (M x K) and B (N x K) are K-major e4m3 /
+// e5m2 bytes, every 32 consecutive K elements of a row share one E8M0 scale. K % 128 == 0. Scale factors come in the
+// tensor core's blocked layout: for each block of 128 rows and 128 K elements one 512-byte chunk, chunks ordered
+// [row block][k block], byte (r % 32) * 16 + ((r % 128) / 32) * 4 + (k / 32) % 4 for row r and element k. The scale
+// arrays cover whole 128-row blocks (pad rows: any finite scale, e.g. 127 = 2^0). Same epilogues as the other GEMMs.
+struct MxScales {
+  const unsigned char* sfa;    // ceil(M/128) * (K/128) chunks
+  const unsigned char* sfb;    // ceil(N/128) * (K/128) chunks
+};
+cudaError_t gemm_mxfp8(const GemmDesc& d, const MxScales& sf, int* status, cudaStream_t stream);
+// Rows of a bf16 matrix (R x K, row pitch ld, K % 128 == 0) to MXFP8: q dense (R x K) bytes, sf in the blocked layout
+// above (ceil(R/128) * (K/128) chunks; the caller pre-fills pad rows). Scale of a block = 2^(floor(log2 amax) - emax),
+// emax = 8 (e4m3) or 15 (e5m2); an all-zero block gets 2^-127.
+cudaError_t mx_quantize_bf16(const void* x, long long ld, int rows, int cols, void* q, unsigned char* sf, int e5m2,
+                             cudaStream_t stream);
 // Same contract with 1-byte A and B (lda/ldb/bs* in elements = bytes, multiples of 16).
 cudaError_t gemm_fp8(const GemmDesc& d, int* status, cudaStream_t stream);
 int gemm_pick_bn(int M, int N, int batch);

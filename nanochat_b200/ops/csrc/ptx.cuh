@@ -106,6 +106,12 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uin
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
       : "memory");
 }
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16 bytes).
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
                ::"l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(smem_u32(src))
@@ -154,6 +160,21 @@ __device__ __forceinline__ void mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_
       "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+// Block-scaled 8-bit MMA: D[tmem] (+)= (A * SFA) * (B * SFB)^T with E8M0 scale factors read from tensor memory.
+__device__ __forceinline__ void mma_mxf8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+      : "memory");
+}
+// Shared memory -> tensor memory copy of one scale-factor chunk: 32 rows x 16 bytes, replicated into the four
+// 32-lane quadrants (lane l of every quadrant receives row l % 32 in four consecutive 32-bit columns).
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t dst_tmem, uint64_t src_desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(dst_tmem), "l"(src_desc) : "memory");
 }
 // A operand read from TMEM (used by attention: P stays in tensor memory).
 __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
@@ -282,6 +303,24 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t
   d |= 1ull << 46;   // descriptor version
   d |= 2ull << 61;   // SWIZZLE_128B
   return d;
+}
+// Shared-memory matrix descriptor without swizzle, K-major: 8-row x 16-byte core matrices, rows 16 B apart inside a
+// core matrix, `sbo_bytes` between successive 8-row groups (the source of a tcgen05.cp of scale factors).
+__device__ __forceinline__ uint64_t umma_desc_noswizzle(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fff) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fff) << 32;
+  d |= 1ull << 46;   // descriptor version
+  return d;          // layout type 0 = no swizzle
+}
+// Instruction descriptor for kind::mxf8f6f4.block_scale: 8-bit float operands (format 0 = e4m3, 1 = e5m2), E8M0 scale
+// factors, K = 32 per instruction, one scale per 32 elements of K ("scale_vec::1X"). `a_sf_id` / `b_sf_id` pick the byte
+// (0..3) of the 32-bit scale-factor words in tensor memory, i.e. which of the four 32-wide K blocks those words cover.
+__host__ __device__ constexpr uint32_t umma_idesc_mxf8(int m, int n, bool a_e5m2, bool b_e5m2, int a_sf_id, int b_sf_id) {
+  return (static_cast<uint32_t>(b_sf_id & 3) << 4) | (static_cast<uint32_t>(a_e5m2) << 7) |
+         (static_cast<uint32_t>(b_e5m2) << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (1u << 23) /* E8M0 scales */ |
+         (static_cast<uint32_t>(m >> 4) << 24) | (static_cast<uint32_t>(a_sf_id & 3) << 29);
 }
 // Instruction descriptor for kind::f16 with bf16 inputs and fp32 accumulation.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n, bool a_mn_major, bool b_mn_major) {

@@ -8,6 +8,7 @@
 // word is an input of the second kernel, so a producer that already knows it (a GEMM epilogue) can skip
 // the first pass. Rows may be strided (row pitch in elements); the fp8 output is dense.
 #include "fused.h"
+#include "gemm.h"
 #include "host_utils.cuh"
 #include "ptx.cuh"
 
@@ -93,6 +94,66 @@ cudaError_t quantize_bf16(const void* x, long long ld, int rows, int cols, const
   auto* qp = reinterpret_cast<uint8_t*>(q);
   if (e5m2) quantize_bf16_kernel<true><<<grid, 256, 0, s>>>(xp, ld, rows, cols, amax, qp, inv_scale);
   else      quantize_bf16_kernel<false><<<grid, 256, 0, s>>>(xp, ld, rows, cols, amax, qp, inv_scale);
+  return cudaGetLastError();
+}
+
+
+// ------------------------------------------------------------------------------ MXFP8
+// One thread per block of 32 consecutive elements of a row: amax of the block, scale 2^(floor(log2 amax) - emax) stored
+// as an E8M0 byte in the tensor core's blocked scale layout (gemm.h: MxScales), elements divided by the scale and
+// converted with saturation. The block's 64 bytes come in as four 16-byte loads and leave as two.
+template <bool E5M2>
+__global__ void __launch_bounds__(256)
+mx_quantize_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int rows, int cols, uint8_t* __restrict__ q,
+                        uint8_t* __restrict__ sf) {
+  constexpr int EMAX = E5M2 ? 15 : 8;                 // exponent of the largest power of two the format holds
+  const int blocks_per_row = cols >> 5;
+  const int k_chunks = cols >> 7;                     // 128-element K blocks per row = scale chunks per row block
+  const long long total = (long long)rows * blocks_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / blocks_per_row), kb = (int)(i - (long long)r * blocks_per_row);
+    const uint4* src = reinterpret_cast<const uint4*>(x + (long long)r * ld + kb * 32);
+    uint32_t w[16];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 v = src[j];
+      w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float2 f = unpack_bf16(w[j]);
+      amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+    }
+    int se = static_cast<int>((__float_as_uint(amax) >> 23) & 0xff) - 127 - EMAX;     // floor(log2 amax) - emax
+    se = se < -127 ? -127 : se;
+    const float inv = __uint_as_float(static_cast<uint32_t>(127 - se) << 23);         // 2^-se, exact
+    uint32_t out[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float2 lo = unpack_bf16(w[2 * j]), hi = unpack_bf16(w[2 * j + 1]);
+      lo.x *= inv; lo.y *= inv; hi.x *= inv; hi.y *= inv;
+      const __nv_fp8x2_storage_t p0 = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, E5M2 ? __NV_E5M2 : __NV_E4M3);
+      const __nv_fp8x2_storage_t p1 = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, E5M2 ? __NV_E5M2 : __NV_E4M3);
+      out[j] = static_cast<uint32_t>(p0) | (static_cast<uint32_t>(p1) << 16);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(q + (long long)r * cols + kb * 32);
+    dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
+    dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+    const size_t chunk = static_cast<size_t>(r >> 7) * k_chunks + (kb >> 2);
+    sf[chunk * 512 + (r & 31) * 16 + ((r & 127) >> 5) * 4 + (kb & 3)] = static_cast<uint8_t>(se + 127);
+  }
+}
+
+cudaError_t mx_quantize_bf16(const void* x, long long ld, int rows, int cols, void* q, unsigned char* sf, int e5m2,
+                             cudaStream_t s) {
+  if ((cols & 127) || (ld & 7)) return cudaErrorInvalidValue;
+  if (rows == 0) return cudaSuccess;
+  const int grid = quant_grid((long long)rows * (cols >> 5));
+  auto* xp = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto* qp = reinterpret_cast<uint8_t*>(q);
+  if (e5m2) mx_quantize_bf16_kernel<true><<<grid, 256, 0, s>>>(xp, ld, rows, cols, qp, sf);
+  else      mx_quantize_bf16_kernel<false><<<grid, 256, 0, s>>>(xp, ld, rows, cols, qp, sf);
   return cudaGetLastError();
 }
 

@@ -201,6 +201,40 @@ def quantize(x2, dtype=E4M3, amax=None):
     return q, inv
 
 
+# Block-scaled fp8 (MXFP8): every 32 consecutive elements along the reduction dim share a power-of-two (E8M0) scale, so
+# quantisation needs no amax over the tensor. `mx_quantize` returns the fp8 rows and their scales in the layout the
+# tensor core reads (one 512-byte chunk per 128 rows x 128 reduction elements); `gemm_mx` runs
+# tcgen05.mma.kind::mxf8f6f4.block_scale on them. Reference semantics: nanochat/fp8.py:125-192 (the matmuls it replaces).
+def mx_scale_bytes(rows, k):
+    return -(-rows // 128) * (k // 128) * 512
+
+
+def mx_quantize(x2, dtype=None):
+    """(fp8 rows, blocked E8M0 scales) of a bf16 matrix (R, K), K % 128 == 0, quantised along K."""
+    dtype = dtype or E4M3
+    assert x2.dim() == 2 and x2.shape[1] % 128 == 0, "MXFP8 needs a reduction dim that is a multiple of 128"
+    x2 = x2 if x2.stride(1) == 1 else x2.contiguous()
+    q = torch.empty(x2.shape, dtype=dtype, device=x2.device)
+    # rows that pad the last 128-row block keep scale 2^0: their operand rows are zero-filled by the tile loads
+    sf = torch.full((mx_scale_bytes(*x2.shape),), 127, dtype=torch.uint8, device=x2.device)
+    _C.mx_quantize(x2, q, sf)
+    return q, sf
+
+
+def gemm_mx(a8, sfa, b8, sfb, out, *, aux=None, alpha=1.0, beta=0.0, epi=EPI_LINEAR, bn=0):
+    """out (M, N) = epilogue(alpha * (a8 * sfa) @ (b8 * sfb)^T, aux): both operands row-major along the reduction dim."""
+    _C.gemm_mx(a8, sfa, b8, sfb, out, aux, alpha, beta, epi, bn)
+    return out
+
+
+def mx_linear(x2, w2, x_dtype=None, w_dtype=None, out_dtype=BF16):
+    """x2 (M, K) @ w2 (N, K)^T with both operands quantised to MXFP8 along K on the way in."""
+    xq, xs = mx_quantize(x2.to(BF16), x_dtype or E4M3)
+    wq, ws = mx_quantize(w2.to(BF16), w_dtype or E4M3)
+    out = torch.empty(x2.shape[0], w2.shape[0], dtype=out_dtype, device=x2.device)
+    return gemm_mx(xq, xs, wq, ws, out)
+
+
 def fp8_weight(w_bf16):
     """e4m3 copy + scale of a bf16 weight matrix (or fused stack), cached until the next optimizer step."""
     key = (w_bf16.data_ptr(), tuple(w_bf16.shape))
