@@ -47,8 +47,9 @@ def parse_args():
     ap.add_argument("--decode-tokens", type=int, default=256)
     ap.add_argument("--comm", type=str, default="auto", choices=["auto", "fused", "nccl"],
                     help="optimizer collectives for N>1: fused peer-to-peer kernels or NCCL")
-    ap.add_argument("--precision", type=str, default="fp8", choices=["fp8", "bf16"],
-                    help="our arm: fp8 = tensorwise e4m3/e5m2 linear layers (the reference's headline recipe)")
+    ap.add_argument("--precision", type=str, default="fp8", choices=["fp8", "bf16", "mxfp8"],
+                    help="our arm: fp8 = tensorwise e4m3/e5m2 linear layers (the reference's headline recipe); mxfp8 = "
+                         "block-scaled fp8 on the hardware block-scaled GEMM (module path, not the fused layer path)")
     ap.add_argument("--ref-bf16", action="store_true", help="reference arm without --fp8")
     ap.add_argument("--ref-eager", action="store_true", help="reference arm without torch.compile")
     return ap.parse_args()
@@ -200,6 +201,11 @@ def run_ours(args):
         convert_to_float8_training(model, config=Float8LinearConfig.from_recipe_name("tensorwise"),
                                    module_filter_fn=default_fp8_filter)
         dtype = "fp8 (tensorwise e4m3/e5m2 linears, bf16 elsewhere)"
+    elif args.precision == "mxfp8":
+        from nanochat_b200.fp8 import Float8LinearConfig, convert_to_float8_training, default_fp8_filter
+        convert_to_float8_training(model, config=Float8LinearConfig.from_recipe_name("mxfp8"),
+                                   module_filter_fn=default_fp8_filter)
+        dtype = "mxfp8 (block-scaled e4m3/e5m2 linears on tcgen05 block_scale MMAs, bf16 elsewhere)"
     from nanochat_b200.train import TrainStep
     B, T = args.device_batch_size, args.seq_len
     assert args.total_batch_size % (B * T * world) == 0

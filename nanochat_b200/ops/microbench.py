@@ -58,6 +58,16 @@ def bench_gemm(args, nat):
     m, n, k = args.m, args.n, args.k
     bf16 = torch.bfloat16
     dev = "cuda"
+    if args.dtype == "mxfp8":        # block-scaled fp8, y[m,n] = x[m,k] W[n,k]^T with both operands scaled along k
+        assert args.layout == "fwd", "the block-scaled GEMM takes K-major operands: quantise along the reduction dim"
+        A = torch.randn(m, k, device=dev).to(bf16)
+        B = torch.randn(n, k, device=dev).to(bf16)
+        (aq, asf), (bq, bsf) = nat.mx_quantize(A), nat.mx_quantize(B)
+        C = torch.empty(m, n, device=dev, dtype=bf16)
+        ms = _time(lambda: nat.gemm_mx(aq, asf, bq, bsf, C, bn=args.bn), args.iters, args.warmup)
+        ms_q = _time(lambda: nat.mx_quantize(A), args.iters, args.warmup)
+        return dict(op="gemm_mx/fwd", dtype="mxfp8", m=m, n=n, k=k, bn=args.bn, ms=ms, tflops=2.0 * m * n * k / ms / 1e9,
+                    quantize_a_ms=ms_q, quantize_a_gbs=(m * k * 3 + m * k / 32) / ms_q / 1e6)
     if args.dtype == "fp8" or args.pair >= 0:
         shapes = {"fwd": ((m, k), (n, k)), "dgrad": ((m, k), (k, n)), "wgrad": ((k, m), (k, n))}[args.layout]
         (A, sa), (B, sb) = _operand(shapes[0], args.dtype), _operand(shapes[1], args.dtype)
@@ -128,7 +138,7 @@ def main():
     ap.add_argument("--k", type=int, default=1664)
     ap.add_argument("--bn", type=int, default=0, help="N tile (0 = heuristic)")
     ap.add_argument("--layout", default="fwd", choices=["fwd", "dgrad", "wgrad"])
-    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8"], help="GEMM operand type")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8", "mxfp8"], help="GEMM operand type")
     ap.add_argument("--pair", type=int, default=-1, help="GEMM: 1 = CTA-pair kernel, 0 = single-CTA kernel, -1 = library choice")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--seq", type=int, default=2048)
