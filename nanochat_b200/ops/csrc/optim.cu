@@ -72,21 +72,43 @@ __global__ void __launch_bounds__(128)
 muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ buf, __nv_bfloat16* __restrict__ X,
                      float* __restrict__ rowss, float mu, float grad_scale, long long rows, int c) {
   const int lane = threadIdx.x & 31;
+  const bool vec = (c & 3) == 0;            // rows of whole float4s (every matrix the fused path sees)
   for (long long row = blockIdx.x * 4ll + (threadIdx.x >> 5); row < rows; row += gridDim.x * 4ll) {
     const float* gr = g + row * c;
     float* br = buf + row * c;
     __nv_bfloat16* xr = X + row * c;
     float ss = 0.f;
-    for (int j = lane; j < c; j += 32) {
-      const float gv = gr[j] * grad_scale;
-      float bv = br[j];
-      bv += (1.f - mu) * (gv - bv);
-      br[j] = bv;
-      const float u = gv + mu * (bv - gv);
-      const __nv_bfloat16 xb = __float2bfloat16_rn(u);
-      xr[j] = xb;
-      const float xf = __bfloat162float(xb);
-      ss += xf * xf;
+    if (vec) {
+      for (int j = lane * 4; j < c; j += 128) {
+        const float4 g4 = *reinterpret_cast<const float4*>(gr + j);
+        const float4 b4 = *reinterpret_cast<const float4*>(br + j);
+        float gv[4] = {g4.x * grad_scale, g4.y * grad_scale, g4.z * grad_scale, g4.w * grad_scale};
+        float bv[4] = {b4.x, b4.y, b4.z, b4.w};
+        __nv_bfloat16 xb[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          bv[e] += (1.f - mu) * (gv[e] - bv[e]);
+          const float u = gv[e] + mu * (bv[e] - gv[e]);
+          xb[e] = __float2bfloat16_rn(u);
+          const float xf = __bfloat162float(xb[e]);
+          ss += xf * xf;
+        }
+        *reinterpret_cast<float4*>(br + j) = make_float4(bv[0], bv[1], bv[2], bv[3]);
+        __nv_bfloat162 lo(xb[0], xb[1]), hi(xb[2], xb[3]);
+        *reinterpret_cast<uint2*>(xr + j) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      }
+    } else {
+      for (int j = lane; j < c; j += 32) {
+        const float gv = gr[j] * grad_scale;
+        float bv = br[j];
+        bv += (1.f - mu) * (gv - bv);
+        br[j] = bv;
+        const float u = gv + mu * (bv - gv);
+        const __nv_bfloat16 xb = __float2bfloat16_rn(u);
+        xr[j] = xb;
+        const float xf = __bfloat162float(xb);
+        ss += xf * xf;
+      }
     }
     ss = warp_sum(ss);
     if (lane == 0) rowss[row] = ss;
@@ -114,6 +136,7 @@ __global__ void __launch_bounds__(128)
 muon_equilibrate_kernel(__nv_bfloat16* __restrict__ X, const float* __restrict__ rowss,
                         const float* __restrict__ total, float* __restrict__ rowss2, long long rows, int r, int c) {
   const int lane = threadIdx.x & 31;
+  const bool vec = (c & 7) == 0;            // rows of whole 16-byte vectors
   for (long long row = blockIdx.x * 4ll + (threadIdx.x >> 5); row < rows; row += gridDim.x * 4ll) {
     const int mat = (int)(row / r);
     const float target = sqrtf(total[mat]) * rsqrtf((float)r);
@@ -121,11 +144,24 @@ muon_equilibrate_kernel(__nv_bfloat16* __restrict__ X, const float* __restrict__
     const float scale = bf16_round(target / rn);
     __nv_bfloat16* xr = X + row * c;
     float ss = 0.f;
-    for (int j = lane; j < c; j += 32) {
-      const __nv_bfloat16 xb = __float2bfloat16_rn(__bfloat162float(xr[j]) * scale);
-      xr[j] = xb;
-      const float xf = __bfloat162float(xb);
-      ss += xf * xf;
+    if (vec) {
+      for (int j = lane * 8; j < c; j += 256) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(xr + j), f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          f[e] = bf16_round(f[e] * scale);
+          ss += f[e] * f[e];
+        }
+        *reinterpret_cast<uint4*>(xr + j) = pack8(f);
+      }
+    } else {
+      for (int j = lane; j < c; j += 32) {
+        const __nv_bfloat16 xb = __float2bfloat16_rn(__bfloat162float(xr[j]) * scale);
+        xr[j] = xb;
+        const float xf = __bfloat162float(xb);
+        ss += xf * xf;
+      }
     }
     ss = warp_sum(ss);
     if (lane == 0) rowss2[row] = ss;
@@ -134,6 +170,20 @@ muon_equilibrate_kernel(__nv_bfloat16* __restrict__ X, const float* __restrict__
 
 __global__ void muon_scale_kernel(__nv_bfloat16* __restrict__ X, const float* __restrict__ total2, size_t per_mat,
                                   size_t n) {
+  if ((per_mat & 7) == 0) {                 // 16-byte vectors never straddle two matrices
+    const size_t n8 = n >> 3, per_mat8 = per_mat >> 3;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+      const int mat = (int)(i / per_mat8);
+      const float nrm = bf16_round(sqrtf(total2[mat]));
+      const float den = bf16_round(bf16_round(nrm * 1.01f) + 1e-6f);
+      float f[8];
+      unpack8(reinterpret_cast<const uint4*>(X)[i], f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = f[e] / den;
+      reinterpret_cast<uint4*>(X)[i] = pack8(f);
+    }
+    return;
+  }
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const int mat = (int)(i / per_mat);
     const float nrm = bf16_round(sqrtf(total2[mat]));
@@ -146,10 +196,20 @@ __global__ void muon_scale_kernel(__nv_bfloat16* __restrict__ X, const float* __
 __global__ void __launch_bounds__(128)
 muon_sumsq_rows_kernel(const __nv_bfloat16* __restrict__ X, float* __restrict__ ss, long long rows, int c) {
   const int lane = threadIdx.x & 31;
+  const bool vec = (c & 7) == 0;
   for (long long row = blockIdx.x * 4ll + (threadIdx.x >> 5); row < rows; row += gridDim.x * 4ll) {
     const __nv_bfloat16* xr = X + row * c;
     float s = 0.f;
-    for (int j = lane; j < c; j += 32) { const float f = __bfloat162float(xr[j]); s += f * f; }
+    if (vec) {
+      for (int j = lane * 8; j < c; j += 256) {
+        float f[8];
+        unpack8(*reinterpret_cast<const uint4*>(xr + j), f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s += f[e] * f[e];
+      }
+    } else {
+      for (int j = lane; j < c; j += 32) { const float f = __bfloat162float(xr[j]); s += f * f; }
+    }
     s = warp_sum(s);
     if (lane == 0) ss[row] = s;
   }
@@ -211,6 +271,38 @@ __global__ void muon_apply_kernel(float* __restrict__ p, const __nv_bfloat16* __
                                   const float* __restrict__ scale, __nv_bfloat16* __restrict__ shadow, int r, int c,
                                   int per_row, float lr, float wd, size_t n) {
   const size_t per_mat = (size_t)r * c;
+  if ((c & 7) == 0) {                       // 8 elements per thread: they share a row
+    const size_t n8 = n >> 3, per_mat8 = per_mat >> 3;
+    const int c8 = c >> 3;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n8; i += (size_t)gridDim.x * blockDim.x) {
+      const size_t mat = i / per_mat8;
+      const size_t rem = i - mat * per_mat8;
+      const int row = (int)(rem / c8), col = (int)(rem - (size_t)row * c8) * 8;
+      float xv[8], pv[8], sc[8];
+      unpack8(reinterpret_cast<const uint4*>(X)[i], xv);
+      const float4 p0 = reinterpret_cast<const float4*>(p)[2 * i], p1 = reinterpret_cast<const float4*>(p)[2 * i + 1];
+      pv[0] = p0.x; pv[1] = p0.y; pv[2] = p0.z; pv[3] = p0.w; pv[4] = p1.x; pv[5] = p1.y; pv[6] = p1.z; pv[7] = p1.w;
+      if (per_row) {
+        const float sv = scale[mat * r + row];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sc[e] = sv;
+      } else {
+        const float4 s0 = *reinterpret_cast<const float4*>(scale + mat * c + col);
+        const float4 s1 = *reinterpret_cast<const float4*>(scale + mat * c + col + 4);
+        sc[0] = s0.x; sc[1] = s0.y; sc[2] = s0.z; sc[3] = s0.w; sc[4] = s1.x; sc[5] = s1.y; sc[6] = s1.z; sc[7] = s1.w;
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float gv = xv[e] * sc[e];
+        const float mask = (gv * pv[e] >= 0.f) ? 1.f : 0.f;
+        pv[e] -= lr * gv + lr * wd * pv[e] * mask;
+      }
+      reinterpret_cast<float4*>(p)[2 * i] = make_float4(pv[0], pv[1], pv[2], pv[3]);
+      reinterpret_cast<float4*>(p)[2 * i + 1] = make_float4(pv[4], pv[5], pv[6], pv[7]);
+      if (shadow) reinterpret_cast<uint4*>(shadow)[i] = pack8(pv);
+    }
+    return;
+  }
   for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const size_t mat = i / per_mat;
     const size_t rem = i - mat * per_mat;

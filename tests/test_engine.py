@@ -178,3 +178,47 @@ def test_engine_matches_naive_generation_at_temperature_zero():
     fast = [c[0] for c, _ in Engine(model, ByteTok()).generate(prompt, num_samples=1, max_tokens=24, temperature=0.0)]
     stop = next((i for i, t in enumerate(fast) if t in (260, 261)), len(fast) - 1)
     assert naive[:stop + 1] == fast[:stop + 1]
+
+
+def test_paged_cache_fork_shares_full_prompt_pages_and_copies_the_partial_one():
+    """Page-table bookkeeping on CPU tensors: after a prefill through the contiguous prompt view and a fork, every row
+    reads back the prompt in position order, full prompt pages are shared, each row has its own page for the tail."""
+    import torch
+    from nanochat_b200.engine import PagedKVCache
+    L, H, D, P = 2, 2, 8, 16
+    cache = PagedKVCache(batch_size=3, num_heads=H, seq_len=96, head_dim=D, num_layers=L, device="cpu",
+                         dtype=torch.float32, page_tokens=P)
+    prompt, new = 37, 20                                  # 2 full pages + 5 tokens
+    cache.reserve(prompt, new)
+    assert cache.shared_pages == 3 and cache.private_pages == 2
+    view = cache.begin_prompt(prompt)
+    assert view.max_seq_len == 48 and view.batch_size == 1
+    want = []
+    for layer in range(L):
+        k, v = view.get_layer_cache(layer)
+        kk, vv = torch.randn(1, prompt, H, D), torch.randn(1, prompt, H, D)
+        k[:, :prompt] = kk
+        v[:, :prompt] = vv
+        want.append((kk[0], vv[0]))
+    view.advance(prompt)
+    cache.fork(view)
+    assert cache.get_pos() == prompt and cache.cache_seqlens.tolist() == [prompt] * 3
+    table = cache.table
+    assert all(table[r, :2].tolist() == [0, 1] for r in range(3))
+    tails = table[:, 2].tolist()
+    assert len(set(tails)) == 3 and min(tails) >= cache.shared_pages
+    assert (table[:, 4:] == cache.spare_page).all()       # nothing mapped past the reserved pages
+    for layer in range(L):
+        for row in range(3):
+            k, v = cache.gather_row(layer, row)
+            assert torch.equal(k, want[layer][0]) and torch.equal(v, want[layer][1])
+    # a row appending into its tail page does not touch the other rows or the shared pages
+    cache.k_pool[0, tails[1], prompt % P] = 7.0
+    k0, _ = cache.gather_row(0, 0)
+    assert torch.equal(k0, want[0][0])
+    # a larger request grows the pool and moves its version (a captured decode graph is rebuilt then)
+    version = cache.pool_version
+    cache.reserve(prompt, 50)
+    assert cache.pool_version == version + 1 and cache.private_pages == 4
+    cache.reserve(20, 10)
+    assert cache.pool_version == version + 1              # smaller requests reuse the pool
