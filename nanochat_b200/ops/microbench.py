@@ -244,7 +244,7 @@ def main():
     if os.path.exists("MEASURED_PEAKS.json"):
         with open("MEASURED_PEAKS.json") as f:
             peak = json.load(f).get("bf16_tflops")
-        if peak:
+        if peak and "tflops" in res:
             res["frac_of_measured_bf16_peak"] = res["tflops"] / peak
     print(json.dumps(res))
 
