@@ -301,8 +301,13 @@ void softcap_logits(const Tensor& logits, Tensor& out, int64_t V, double cap) {
 }
 
 // ---------------------------------------------------------------------------- decode
+static std::pair<const void*, long long> next_weights(const optional<Tensor>& t) {
+  if (!t.has_value() || !t->defined() || !t->is_contiguous()) return {nullptr, 0};
+  return {t->data_ptr(), (long long)t->numel() * (long long)t->element_size()};
+}
+
 void gemv_rows(const Tensor& x, const Tensor& W, Tensor& out, const optional<Tensor>& aux, int64_t epi,
-               bool norm_input) {
+               bool norm_input, const optional<Tensor>& next_w) {
   check_bf16(x, "x"); check_bf16(W, "W"); check_bf16(out, "out");
   TORCH_CHECK(x.dim() == 2 && W.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && W.stride(1) == 1 &&
               out.stride(1) == 1, "gemv: 2-D row-major tensors");
@@ -315,12 +320,13 @@ void gemv_rows(const Tensor& x, const Tensor& W, Tensor& out, const optional<Ten
     ap = aux->data_ptr(); lda = aux->stride(0);
   }
   NC_CHECK(nc::gemv_rows(x.data_ptr(), x.stride(0), W.data_ptr(), W.stride(0), out.data_ptr(), out.stride(0), ap, lda,
-                         (int)x.size(0), (int)W.size(0), (int)x.size(1), (int)epi, norm_input ? 1 : 0, cur_stream()));
+                         (int)x.size(0), (int)W.size(0), (int)x.size(1), (int)epi, norm_input ? 1 : 0,
+                         next_weights(next_w).first, next_weights(next_w).second, cur_stream()));
 }
 
 // x, x0, xm, xn: (B, K) bf16 (xn: only its first 16 channels are written); lam_r, lam_0: fp32 (layers); W: (N, K); out: (B, N).
 void gemv_rows_mix(const Tensor& x, const Tensor& x0, const Tensor& lam_r, const Tensor& lam_0, int64_t layer,
-                   const Tensor& W, Tensor& out, Tensor& xm, Tensor& xn) {
+                   const Tensor& W, Tensor& out, Tensor& xm, Tensor& xn, const optional<Tensor>& next_w) {
   check_bf16(x, "x"); check_bf16(x0, "x0"); check_bf16(W, "W"); check_bf16(out, "out"); check_bf16(xm, "xm"); check_bf16(xn, "xn");
   TORCH_CHECK(x.dim() == 2 && W.dim() == 2 && out.dim() == 2 && x.stride(1) == 1 && x0.stride(1) == 1 && W.stride(1) == 1 &&
               out.stride(1) == 1 && xm.stride(1) == 1 && xn.stride(1) == 1, "gemv_rows_mix: 2-D row-major tensors");
@@ -333,7 +339,7 @@ void gemv_rows_mix(const Tensor& x, const Tensor& x0, const Tensor& lam_r, const
   NC_CHECK(nc::gemv_rows_mix(x.data_ptr(), x.stride(0), x0.data_ptr(), x0.stride(0), lam_r.data_ptr<float>(),
                              lam_0.data_ptr<float>(), (int)layer, W.data_ptr(), W.stride(0), out.data_ptr(), out.stride(0),
                              xm.data_ptr(), xm.stride(0), xn.data_ptr(), xn.stride(0), 16, (int)x.size(0), (int)W.size(0),
-                             (int)x.size(1), cur_stream()));
+                             (int)x.size(1), next_weights(next_w).first, next_weights(next_w).second, cur_stream()));
 }
 
 // ids: int64 (B) or (B, 1); wte: (V, C) bf16; gate_w: fp32 (n_gate); lam: fp32 (1); prev, out: (B, C) bf16.
@@ -593,8 +599,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("gemm_pick_bn", &gemm_pick_bn);
   m.def("sample_next_token", &sample_next_token);
-  m.def("gemv_rows", &gemv_rows);
-  m.def("gemv_rows_mix", &gemv_rows_mix);
+  m.def("gemv_rows", &gemv_rows, py::arg("x"), py::arg("W"), py::arg("out"), py::arg("aux"), py::arg("epi"),
+        py::arg("norm_input"), py::arg("next_w") = py::none());
+  m.def("gemv_rows_mix", &gemv_rows_mix, py::arg("x"), py::arg("x0"), py::arg("lam_r"), py::arg("lam_0"), py::arg("layer"),
+        py::arg("W"), py::arg("out"), py::arg("xm"), py::arg("xn"), py::arg("next_w") = py::none());
   m.def("decode_embed", &decode_embed);
   m.def("decode_qkv_post", &decode_qkv_post, py::arg("qkv"), py::arg("H"), py::arg("Hkv"), py::arg("cos"), py::arg("sin"),
         py::arg("seqlens"), py::arg("xn"), py::arg("wg"), py::arg("ve"), py::arg("idx"), py::arg("k_cache"),

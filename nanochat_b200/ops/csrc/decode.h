@@ -20,8 +20,11 @@ struct KvPages {
 
 // out[b, n] = epi(sum_k xe[b, k] * W[n, k]) + aux[b, n]   for b < B <= 8 (aux optional). K, ldx, ldw multiples of 8.
 // norm_input != 0: xe = rmsnorm(x) (the normalisation is folded into the dot products), else xe = x.
+// next_w / next_bytes (optional, 16-byte aligned): memory the kernel AFTER this one will stream (its weight matrix);
+// this kernel's CTAs prefetch it into L2 before their own work.
 cudaError_t gemv_rows(const void* x, long long ldx, const void* W, long long ldw, void* out, long long ldo,
-                      const void* aux, long long ldaux, int B, int N, int K, int epi, int norm_input, cudaStream_t s);
+                      const void* aux, long long ldaux, int B, int N, int K, int epi, int norm_input,
+                      const void* next_w, long long next_bytes, cudaStream_t s);
 
 // The layer's first GEMV with the residual mix and the norm folded in: xm = bf16(lam_r[layer] * x + lam_0[layer] * x0),
 // out[b, n] = sum_k rmsnorm(xm)[b, k] * W[n, k]. Also writes xm (B x K) and the first head_cols channels of
@@ -29,7 +32,7 @@ cudaError_t gemv_rows(const void* x, long long ldx, const void* W, long long ldw
 cudaError_t gemv_rows_mix(const void* x, long long ldx, const void* x0, long long ldx0, const float* lam_r,
                           const float* lam_0, int layer, const void* W, long long ldw, void* out, long long ldo,
                           void* xm, long long ldxm, void* xn_head, long long ldxn, int head_cols, int B, int N, int K,
-                          cudaStream_t s);
+                          const void* next_w, long long next_bytes, cudaStream_t s);
 
 // out[b] = e + lam * sigmoid(e[:n_gate] . gate_w) * prev[b], e = rmsnorm(wte[ids[b]]); prev[b] <- e. C, ldw, ldp, ldo
 // multiples of 8; n_gate <= 32; ids outside [0, vocab) are clamped.

@@ -20,6 +20,7 @@ import torch
 from nanochat_b200 import common, ops
 from nanochat_b200.ops import reference as ref_ops
 
+LM_HEAD_PREFETCH_ROWS = 16384     # rows of lm_head (54 MB at 1664 wide) the last layer prefetches: what L2 can hold
 MAX_ROWS = 64          # rows of one decode graph; up to GEMV_ROWS of them use the weight-streaming GEMV
 GEMV_ROWS = 8
 # Up to this many rows the layer's mix + norm is folded into the QKV GEMV (one launch fewer per layer). Every CTA of
@@ -27,6 +28,8 @@ GEMV_ROWS = 8
 # than the launch it saves once the rows make it arithmetic-bound. Measured on d26: 1 row +4.8 %, 2 rows +2 %,
 # 4 rows -5 %, 8 rows -4 % tokens per second.
 FOLD_MIX_ROWS = int(os.environ.get("NANOCHAT_DECODE_FOLD_ROWS", "2"))
+# every GEMV of the step prefetches the next kernel's weight matrix into L2 (NANOCHAT_DECODE_PREFETCH=0: off, A/B runs)
+PREFETCH_NEXT = os.environ.get("NANOCHAT_DECODE_PREFETCH", "1") != "0"
 
 
 class DecodeGraph:
@@ -105,10 +108,12 @@ class DecodeGraph:
         self._captured_where = where
 
     # --------------------------------------------------------------------- step
-    def _linear(self, x, w, out, aux=None, relu2=False, norm_input=False):
-        """out = epi(norm?(x) @ w^T) (+ aux): GEMV for a few rows, tensor-core GEMM otherwise."""
+    def _linear(self, x, w, out, aux=None, relu2=False, norm_input=False, next_w=None):
+        """out = epi(norm?(x) @ w^T) (+ aux): GEMV for a few rows, tensor-core GEMM otherwise. `next_w`: the weight
+        matrix the following kernel will stream; the GEMV's CTAs prefetch it into L2 (decode is latency-bound per
+        kernel, so keeping HBM busy across kernel boundaries is what raises the weight-streaming rate)."""
         if self.use_gemv:
-            self.C_.gemv_rows(x, w, out, aux, 1 if relu2 else 0, norm_input)
+            self.C_.gemv_rows(x, w, out, aux, 1 if relu2 else 0, norm_input, next_w if PREFETCH_NEXT else None)
             return
         nat = self.nat
         if norm_input:
@@ -130,12 +135,15 @@ class DecodeGraph:
         backout_layer = m.config.n_layer // 2
         scale = 1.0 / (128 ** 0.5)
         for i, w in enumerate(self.w):
+            # what the kernel after this layer's last GEMV streams: the next layer's QKV weights, or the head of lm_head
+            after = self.w[i + 1]["qkv"] if i + 1 < len(self.w) else self.lm_head[:LM_HEAD_PREFETCH_ROWS]
             if self.use_gemv and B <= FOLD_MIX_ROWS:
                 # mix + norm folded into the QKV GEMV; its first CTA writes xm and the gate's slice of xn
-                C_.gemv_rows_mix(x, x0, m.resid_lambdas, m.x0_lambdas, i, w["qkv"], self.qkv, self.xm, self.xn)
+                C_.gemv_rows_mix(x, x0, m.resid_lambdas, m.x0_lambdas, i, w["qkv"], self.qkv, self.xm, self.xn,
+                                 w["o"] if PREFETCH_NEXT else None)
             else:
                 C_.mixnorm_fwd(x, x0, m.resid_lambdas, m.x0_lambdas, i, self.xm, self.xn, None)
-                self._linear(self.xn, w["qkv"], self.qkv)
+                self._linear(self.xn, w["qkv"], self.qkv, next_w=w["o"])
             ve = m.value_embeds[str(i)].weight if str(i) in m.value_embeds else None
             kc, vc = cache.get_layer_cache(i)
             # a paged cache: one layer's page pools + the rows' page table; the row capacity bounds the append
@@ -148,10 +156,10 @@ class DecodeGraph:
             window = window if 0 <= window < cache.max_seq_len else -1
             C_.decode_attn(self.qkv[:, :nq], kc, vc, cache.cache_seqlens, H, Hkv, window, scale, self.scratch, self.y,
                            table)
-            self._linear(self.y, w["o"], self.xa, aux=self.xm)
-            self._linear(self.xa, w["fc"], self.h, relu2=True, norm_input=True)   # GEMV: norm(xa) folded in
+            self._linear(self.y, w["o"], self.xa, aux=self.xm, next_w=w["fc"])
+            self._linear(self.xa, w["fc"], self.h, relu2=True, norm_input=True, next_w=w["pr"])   # GEMV: norm(xa) folded in
             out = self.x_backout if i == backout_layer else self.xs[i & 1]
-            self._linear(self.h, w["pr"], out, aux=self.xa)
+            self._linear(self.h, w["pr"], out, aux=self.xa, next_w=after)
             x = out
         C_.backout_norm_fwd(x, self.x_backout, m.backout_lambda.detach().float(), self.xn)
         self._linear(self.xn, self.lm_head, self.logits_bf16)
