@@ -171,43 +171,104 @@ __device__ __forceinline__ void store_tile_row(const GemmKernelArgs& args, uint3
 // (residual, relu^2 derivative input) comes in the same way, through the same tile.
 constexpr int EPI_STAGE_BYTES = 32 * 128;          // per epilogue warp
 
-template <int BN>
+//
+// The auxiliary loads run one group ahead of their use: the 32 x 128 B of the NEXT group (of this tile, or the first group
+// of the warp's next tile) are requested into registers before the current group is converted, so their DRAM latency
+// passes under the tensor-memory reads, the conversion and the stores instead of in front of them. With a short reduction
+// (K = 1664) the epilogue sets the tile time, and a load waited for at the head of every group more than doubled it.
+struct AuxAhead {
+  uint4 v[8];
+};
+
+struct TileAt {
+  int b, row0, n0;
+  bool valid;
+};
+
+__device__ __forceinline__ bool aux_bf16_used(const GemmKernelArgs& args) {
+  return args.aux != nullptr && !args.c_f32 && args.epi != EPI_RELU2;
+}
+
+__device__ __forceinline__ void aux_request(const GemmKernelArgs& args, AuxAhead& ahead, const TileAt& at, int g, int c_end,
+                                            int lane) {
+  const __nv_bfloat16* xbase = reinterpret_cast<const __nv_bfloat16*>(args.aux) + at.b * args.bsaux;
+  const int sub_r = lane >> 3, unit = lane & 7;
+  const int nch = min(4, c_end - g);
+  const int col = at.n0 + g * 16 + unit * 8;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int r = it * 4 + sub_r;
+    ahead.v[it] = make_uint4(0, 0, 0, 0);
+    if (at.row0 + r < args.M && unit < nch * 2 && col + 8 <= args.N)
+      ahead.v[it] = *reinterpret_cast<const uint4*>(xbase + static_cast<long long>(at.row0 + r) * args.ldaux + col);
+  }
+}
+
+// One line of the next tile's auxiliary operand per lane goes to L2 ahead of time (the warp's 32 rows x its columns).
+__device__ __forceinline__ void aux_prefetch_l2(const GemmKernelArgs& args, const TileAt& at, int c_begin, int c_end, int lane) {
+  const int col = at.n0 + c_begin * 16;
+  const int cols = min((c_end - c_begin) * 16, args.N - col);
+  if (at.valid && at.row0 + lane < args.M && cols >= 8) {
+    const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(args.aux) + at.b * args.bsaux +
+                             static_cast<long long>(at.row0 + lane) * args.ldaux + col;
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(static_cast<uint32_t>((cols & ~7) * 2)) : "memory");
+  }
+}
+
+template <int BN, bool AHEAD>
 __device__ __forceinline__ void store_tile_bf16_staged(const GemmKernelArgs& args, uint32_t taddr, int b, int row0, int n0,
                                                        float alpha, float beta, float& amax, int c_begin, int c_end,
-                                                       uint8_t* stage, int lane) {
+                                                       uint8_t* stage, int lane, AuxAhead& ahead, const TileAt& next) {
   __nv_bfloat16* cbase = reinterpret_cast<__nv_bfloat16*>(args.C) + b * args.bsc;
   const __nv_bfloat16* xbase = args.aux ? reinterpret_cast<const __nv_bfloat16*>(args.aux) + b * args.bsaux : nullptr;
-  const bool use_aux = xbase != nullptr && args.epi != EPI_RELU2;
+  const bool use_aux = aux_bf16_used(args);
   const int sub_r = lane >> 3, unit = lane & 7;     // coalesced phase: 4 rows x 8 units (16 B) per instruction
 #pragma unroll 1
   for (int g = c_begin; g < c_end; g += 4) {
     const int nch = min(4, c_end - g);              // 16-column chunks in this group
     const int col0 = n0 + g * 16;
     if (use_aux) {
+      if constexpr (AHEAD) {
 #pragma unroll
-      for (int it = 0; it < 8; ++it) {
-        const int r = it * 4 + sub_r;
-        const int col = col0 + unit * 8;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row0 + r < args.M && unit < nch * 2 && col + 8 <= args.N)
-          v = *reinterpret_cast<const uint4*>(xbase + static_cast<long long>(row0 + r) * args.ldaux + col);
-        *reinterpret_cast<uint4*>(stage + r * 128 + ((unit ^ (r & 7)) << 4)) = v;
+        for (int it = 0; it < 8; ++it) {
+          const int r = it * 4 + sub_r;
+          *reinterpret_cast<uint4*>(stage + r * 128 + ((unit ^ (r & 7)) << 4)) = ahead.v[it];
+        }
+        __syncwarp();
+        if (g + 4 < c_end) aux_request(args, ahead, TileAt{b, row0, n0, true}, g + 4, c_end, lane);
+        else if (next.valid) aux_request(args, ahead, next, c_begin, c_end, lane);
+      } else {
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int r = it * 4 + sub_r;
+          const int col = col0 + unit * 8;
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (row0 + r < args.M && unit < nch * 2 && col + 8 <= args.N)
+            v = *reinterpret_cast<const uint4*>(xbase + static_cast<long long>(row0 + r) * args.ldaux + col);
+          *reinterpret_cast<uint4*>(stage + r * 128 + ((unit ^ (r & 7)) << 4)) = v;
+        }
+        __syncwarp();
       }
-      __syncwarp();
     }
-    uint32_t acc[4][16];
+    // Accumulator columns come out of tensor memory 64 at a time; with loads in flight for the next group only 32 at a
+    // time, so that the registers holding those loads are not spilled (a spill waits for the load it was meant to hide).
+    constexpr int BATCH = AHEAD ? 2 : 4;
+#pragma unroll 1
+    for (int c0 = 0; c0 < 4; c0 += BATCH) {
+    uint32_t acc[BATCH][16];
 #pragma unroll
-    for (int cc = 0; cc < 4; ++cc)
-      if (cc < nch) tmem_ld16(taddr + (g + cc) * 16, acc[cc]);
+    for (int ci = 0; ci < BATCH; ++ci)
+      if (c0 + ci < nch) tmem_ld16(taddr + (g + c0 + ci) * 16, acc[ci]);
     tmem_wait_ld();
 #pragma unroll
-    for (int cc = 0; cc < 4; ++cc) {
+    for (int ci = 0; ci < BATCH; ++ci) {
+      const int cc = c0 + ci;
       if (cc < nch) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           float vv[8];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) vv[j] = __uint_as_float(acc[cc][h * 8 + j]) * alpha;
+          for (int j = 0; j < 8; ++j) vv[j] = __uint_as_float(acc[ci][h * 8 + j]) * alpha;
           uint8_t* slot = stage + lane * 128 + (((cc * 2 + h) ^ (lane & 7)) << 4);
           if (args.epi == EPI_RELU2) {
 #pragma unroll
@@ -235,6 +296,7 @@ __device__ __forceinline__ void store_tile_bf16_staged(const GemmKernelArgs& arg
                                                        pack_bf16(vv[4], vv[5]), pack_bf16(vv[6], vv[7]));
         }
       }
+    }
     }
     __syncwarp();
 #pragma unroll
@@ -313,7 +375,7 @@ __device__ __forceinline__ void store_tile_f32_staged(const GemmKernelArgs& args
   }
 }
 
-template <int BN, bool A_MN, bool B_MN, bool FP8>
+template <int BN, bool A_MN, bool B_MN, bool FP8, bool AHEAD = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmKernelArgs args) {
@@ -423,8 +485,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (args.scale_a) alpha *= __ldg(args.scale_a);
     if (args.scale_b) alpha *= __ldg(args.scale_b);
     const float beta = args.beta;
+    const bool use_aux = AHEAD && aux_bf16_used(args);     // auxiliary loads run ahead of their use (see AuxAhead)
+    AuxAhead ahead;
+    auto tile_at = [&](int t) {
+      TileAt at{0, 0, 0, t < total_tiles};
+      if (at.valid) {
+        int tb, tmb, tnb; tile_coords(t, args, tb, tmb, tnb);
+        at.b = tb; at.row0 = tmb * BM + quad * 32; at.n0 = tnb * BN;
+      }
+      return at;
+    };
+    if (use_aux && blockIdx.x < total_tiles) aux_request(args, ahead, tile_at(blockIdx.x), c_begin, c_end, lane);
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int b, mb, nb; tile_coords(t, args, b, mb, nb);
+      const TileAt next = use_aux ? tile_at(t + gridDim.x) : TileAt{0, 0, 0, false};
+      if (use_aux) aux_prefetch_l2(args, next, c_begin, c_end, lane);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, args.status, ST_WAIT_TMEM_FULL, t)) { ok = false; break; }
       tc_fence_after();
       const int row = mb * BM + quad * 32 + lane;
@@ -436,8 +511,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       else if (args.c_f32)
         store_tile_row<BN>(args, taddr, b, row, n0, alpha, beta, amax, c_begin, c_end);
       else
-        store_tile_bf16_staged<BN>(args, taddr, b, mb * BM + quad * 32, n0, alpha, beta, amax, c_begin, c_end,
-                                   epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane);
+        store_tile_bf16_staged<BN, AHEAD>(args, taddr, b, mb * BM + quad * 32, n0, alpha, beta, amax, c_begin, c_end,
+                                          epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane, ahead, next);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -604,6 +679,8 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
     float amax = 0.f;
     const float alpha = args.alpha, beta = args.beta;
+    AuxAhead ahead;                                         // this kernel reads its auxiliary operand in place
+    const TileAt next{0, 0, 0, false};
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int b, mb, nb; tile_coords(t, args, b, mb, nb);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, args.status, ST_WAIT_TMEM_FULL, t)) { ok = false; break; }
@@ -617,8 +694,8 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       else if (args.c_f32)
         store_tile_row<BN>(args, taddr, b, row, n0, alpha, beta, amax, c_begin, c_end);
       else
-        store_tile_bf16_staged<BN>(args, taddr, b, mb * BM + quad * 32, n0, alpha, beta, amax, c_begin, c_end,
-                                   epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane);
+        store_tile_bf16_staged<BN, false>(args, taddr, b, mb * BM + quad * 32, n0, alpha, beta, amax, c_begin, c_end,
+                                          epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane, ahead, next);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -676,7 +753,7 @@ struct PairCfg {
   static_assert(BN % 32 == 0 || BN == 208, "pair tiles: N/2 must stay a multiple of 8");
 };
 
-template <int BN, bool A_MN, bool B_MN, bool FP8>
+template <int BN, bool A_MN, bool B_MN, bool FP8, bool AHEAD = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmKernelArgs args) {
@@ -793,8 +870,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (args.scale_a) alpha *= __ldg(args.scale_a);
     if (args.scale_b) alpha *= __ldg(args.scale_b);
     const float beta = args.beta;
+    const bool use_aux = AHEAD && aux_bf16_used(args);
+    AuxAhead ahead;
+    auto tile_at = [&](int t) {
+      TileAt at{0, 0, 0, t < total_tiles};
+      if (at.valid) {
+        int tb, tmb, tnb; tile_coords(t, args, tb, tmb, tnb);
+        at.b = tb; at.row0 = tmb * (2 * BM) + rank * BM + quad * 32; at.n0 = tnb * BN;
+      }
+      return at;
+    };
+    if (use_aux && pair < total_tiles) aux_request(args, ahead, tile_at(pair), c_begin, c_end, lane);
     for (int t = pair; t < total_tiles && ok; t += n_pairs) {
       int b, mb, nb; tile_coords(t, args, b, mb, nb);
+      const TileAt next = use_aux ? tile_at(t + n_pairs) : TileAt{0, 0, 0, false};
+      if (use_aux) aux_prefetch_l2(args, next, c_begin, c_end, lane);
       if (!mbar_wait(&acc_full[acc], acc_phase, abort_flag, args.status, ST_WAIT_TMEM_FULL, t)) { ok = false; break; }
       tc_fence_after();
       const int row = mb * (2 * BM) + rank * BM + quad * 32 + lane;
@@ -805,8 +895,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       else if (args.c_f32)
         store_tile_row<BN>(args, taddr, b, row, nb * BN, alpha, beta, amax, c_begin, c_end);
       else
-        store_tile_bf16_staged<BN>(args, taddr, b, mb * (2 * BM) + rank * BM + quad * 32, nb * BN, alpha, beta, amax,
-                                   c_begin, c_end, epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane);
+        store_tile_bf16_staged<BN, AHEAD>(args, taddr, b, mb * (2 * BM) + rank * BM + quad * 32, nb * BN, alpha, beta,
+                                          amax, c_begin, c_end, epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane, ahead, next);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
@@ -851,13 +941,16 @@ static int f32_staged_default() {
   return v;
 }
 
-template <int BN, bool A_MN, bool B_MN, bool FP8>
+// bf16 output with an auxiliary operand that the epilogue combines with the product (not relu^2, which needs none)
+static bool aux_ahead_wanted(const GemmDesc& d) { return d.aux != nullptr && !d.c_f32 && d.epi != EPI_RELU2; }
+
+template <int BN, bool A_MN, bool B_MN, bool FP8, bool AHEAD = false>
 static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t stream) {
   using C = Cfg<BN, A_MN, B_MN, FP8>;
   constexpr int BK = C::BK;
   constexpr int ELT = C::ELT;
   static PerDeviceOnce configured;
-  auto kern = gemm_kernel<BN, A_MN, B_MN, FP8>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, FP8, AHEAD>;
   cudaError_t ce = configured.once(
       [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES); });
   if (ce != cudaSuccess) return ce;
@@ -901,6 +994,11 @@ static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t strea
 
 template <bool A_MN, bool B_MN, bool FP8>
 static cudaError_t launch_bn(int bn, const GemmDesc& d, int* status, cudaStream_t s) {
+  // the activation-gradient layout with an auxiliary operand (the MLP's relu^2 derivative) has kernels of its own
+  if constexpr (!A_MN && B_MN) {
+    if (aux_ahead_wanted(d) && bn == 256) return launch_cfg<256, A_MN, B_MN, FP8, true>(d, status, s);
+    if (aux_ahead_wanted(d) && bn == 128) return launch_cfg<128, A_MN, B_MN, FP8, true>(d, status, s);
+  }
   switch (bn) {
     case 256: return launch_cfg<256, A_MN, B_MN, FP8>(d, status, s);
     case 208: return launch_cfg<208, A_MN, B_MN, FP8>(d, status, s);
@@ -911,13 +1009,13 @@ static cudaError_t launch_bn(int bn, const GemmDesc& d, int* status, cudaStream_
   }
 }
 
-template <int BN, bool A_MN, bool B_MN, bool FP8>
+template <int BN, bool A_MN, bool B_MN, bool FP8, bool AHEAD = false>
 static cudaError_t launch_pair_cfg(const GemmDesc& d, int* status, cudaStream_t stream) {
   using C = PairCfg<BN, A_MN, B_MN, FP8>;
   constexpr int BK = C::BK;
   constexpr int ELT = Cfg<BN, A_MN, B_MN, FP8>::ELT;
   static PerDeviceOnce configured;
-  auto kern = gemm_pair_kernel<BN, A_MN, B_MN, FP8>;
+  auto kern = gemm_pair_kernel<BN, A_MN, B_MN, FP8, AHEAD>;
   cudaError_t ce = configured.once(
       [&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES); });
   if (ce != cudaSuccess) return ce;
@@ -971,6 +1069,10 @@ static cudaError_t launch_pair_cfg(const GemmDesc& d, int* status, cudaStream_t 
 
 template <bool A_MN, bool B_MN, bool FP8>
 static cudaError_t launch_pair_bn(int bn, const GemmDesc& d, int* status, cudaStream_t s) {
+  if constexpr (!A_MN && B_MN) {
+    if (aux_ahead_wanted(d) && bn == 256) return launch_pair_cfg<256, A_MN, B_MN, FP8, true>(d, status, s);
+    if (aux_ahead_wanted(d) && bn == 128) return launch_pair_cfg<128, A_MN, B_MN, FP8, true>(d, status, s);
+  }
   switch (bn) {
     case 256: return launch_pair_cfg<256, A_MN, B_MN, FP8>(d, status, s);
     case 208: return launch_pair_cfg<208, A_MN, B_MN, FP8>(d, status, s);

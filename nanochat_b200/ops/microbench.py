@@ -77,9 +77,15 @@ def bench_gemm(args, nat):
         kw = dict(a_mn=wg, b_mn=args.layout != "fwd", bn=args.bn, pair=args.pair, scale_a=sa, scale_b=sb)
         if wg:
             kw.update(aux=C, beta=1.0)
+        elif args.epi != "linear":     # the MLP's fused epilogues: relu^2 on the way out, or its derivative from the saved output
+            kw.update(epi={"relu2": nat.EPI_RELU2, "mul2sqrt": nat.EPI_MUL2SQRT}[args.epi])
+            if args.epi == "mul2sqrt":
+                kw.update(aux=torch.rand(m, n, device=dev).to(bf16))
+        if args.amax:
+            kw.update(amax_out=torch.zeros(1, device=dev))
         ms = _time(lambda: nat.gemm(A, B, C, **kw), args.iters, args.warmup)
-        return dict(op=f"gemm/{args.layout}", dtype=args.dtype, pair=args.pair, m=m, n=n, k=k, bn=args.bn, ms=ms,
-                    tflops=2.0 * m * n * k / ms / 1e9)
+        return dict(op=f"gemm/{args.layout}", dtype=args.dtype, pair=args.pair, epi=args.epi, m=m, n=n, k=k, bn=args.bn,
+                    ms=ms, tflops=2.0 * m * n * k / ms / 1e9)
     if args.layout == "fwd":        # y[m,n] = x[m,k] W[n,k]^T
         A = torch.randn(m, k, device=dev).to(bf16)
         B = torch.randn(n, k, device=dev).to(bf16)
@@ -230,6 +236,8 @@ def main():
     ap.add_argument("--layout", default="fwd", choices=["fwd", "dgrad", "wgrad"])
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8", "mxfp8"], help="GEMM operand type")
     ap.add_argument("--pair", type=int, default=-1, help="GEMM: 1 = CTA-pair kernel, 0 = single-CTA kernel, -1 = library choice")
+    ap.add_argument("--epi", default="linear", choices=["linear", "relu2", "mul2sqrt"], help="GEMM (fp8 / --pair): fused epilogue")
+    ap.add_argument("--amax", type=int, default=0, help="GEMM (fp8 / --pair): 1 = the epilogue also reports max|output|")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=13)
