@@ -44,6 +44,7 @@ struct GemmKernelArgs {
   int epi;
   int c_f32;
   int f32_staged;           // fp32 output through the staging tile (whole 128-byte lines) instead of per-row pieces
+  int c_tma;                // bf16 output leaves the staging tile as TMA stores (the kernel's third tensor map covers C)
   int m_blocks, n_blocks, group_m;
   uint32_t idesc;
   int* status;
@@ -218,7 +219,8 @@ __device__ __forceinline__ void aux_prefetch_l2(const GemmKernelArgs& args, cons
 template <int BN, bool AHEAD>
 __device__ __forceinline__ void store_tile_bf16_staged(const GemmKernelArgs& args, uint32_t taddr, int b, int row0, int n0,
                                                        float alpha, float beta, float& amax, int c_begin, int c_end,
-                                                       uint8_t* stage, int lane, AuxAhead& ahead, const TileAt& next) {
+                                                       uint8_t* stage, int lane, AuxAhead& ahead, const TileAt& next,
+                                                       const CUtensorMap* tmC) {
   __nv_bfloat16* cbase = reinterpret_cast<__nv_bfloat16*>(args.C) + b * args.bsc;
   const __nv_bfloat16* xbase = args.aux ? reinterpret_cast<const __nv_bfloat16*>(args.aux) + b * args.bsaux : nullptr;
   const bool use_aux = aux_bf16_used(args);
@@ -227,6 +229,10 @@ __device__ __forceinline__ void store_tile_bf16_staged(const GemmKernelArgs& arg
   for (int g = c_begin; g < c_end; g += 4) {
     const int nch = min(4, c_end - g);              // 16-column chunks in this group
     const int col0 = n0 + g * 16;
+    if (tmC) {                                      // the previous group's TMA store has read the tile
+      if (lane == 0) tma_store_wait_read<0>();
+      __syncwarp();
+    }
     if (use_aux) {
       if constexpr (AHEAD) {
 #pragma unroll
@@ -297,6 +303,14 @@ __device__ __forceinline__ void store_tile_bf16_staged(const GemmKernelArgs& arg
         }
       }
     }
+    }
+    if (tmC && nch == 4) {
+      // The tile's layout (16-byte units XOR-ed with the row index) is the 128-byte TMA swizzle: one lane hands all 4 KB to
+      // the copy engine, which clips rows beyond M and columns beyond N; the warp goes on to the next group meanwhile.
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) { tma_store_3d(tmC, stage, col0, row0, b); tma_store_commit(); }
+      continue;
     }
     __syncwarp();
 #pragma unroll
@@ -378,19 +392,19 @@ __device__ __forceinline__ void store_tile_f32_staged(const GemmKernelArgs& args
 template <int BN, bool A_MN, bool B_MN, bool FP8, bool AHEAD = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmKernelArgs args) {
+            const __grid_constant__ CUtensorMap tmC, const GemmKernelArgs args) {
   using C = Cfg<BN, A_MN, B_MN, FP8>;
   constexpr int BK = C::BK;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES;            // 8 x 4 KB, 1024-byte aligned (TMA swizzle atom)
+  uint64_t* full = reinterpret_cast<uint64_t*>(epi_stage + C::EPI_BYTES);
   uint64_t* empty = full + C::STAGES;
   uint64_t* acc_full = empty + C::STAGES;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES + 512;      // 8 x 4 KB, 128-byte aligned
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -403,7 +417,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); if (args.c_tma) tma_prefetch_desc(&tmC); }
   if (warp == 1) { tmem_alloc(tmem_slot, C::TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
@@ -478,7 +492,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // ---------------------------------------------------------------- epilogue
     const int quad = warp & 3;
     constexpr int CHUNKS = BN / 16, SPLIT = (CHUNKS + 1) / 2;
-    const int c_begin = (warp - 2) < 4 ? 0 : SPLIT, c_end = (warp - 2) < 4 ? SPLIT : CHUNKS;
+    // with TMA stores a warp's columns are split into whole 64-column groups where possible (a partial group is stored by hand)
+    const int split = (args.c_tma && CHUNKS > 8) ? (SPLIT + 3) / 4 * 4 : SPLIT;
+    const int c_begin = (warp - 2) < 4 ? 0 : split, c_end = (warp - 2) < 4 ? split : CHUNKS;
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
     float amax = 0.f;
     float alpha = args.alpha;
@@ -512,12 +528,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         store_tile_row<BN>(args, taddr, b, row, n0, alpha, beta, amax, c_begin, c_end);
       else
         store_tile_bf16_staged<BN, AHEAD>(args, taddr, b, mb * BM + quad * 32, n0, alpha, beta, amax, c_begin, c_end,
-                                          epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane, ahead, next);
+                                          epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane, ahead, next,
+                                          args.c_tma ? &tmC : nullptr);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    if (args.c_tma && lane == 0) tma_store_wait<0>();     // the warp's last stores have left shared memory and landed
     if (args.amax_out) {
       // non-negative floats order like their bit patterns
 #pragma unroll
@@ -695,7 +713,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         store_tile_row<BN>(args, taddr, b, row, n0, alpha, beta, amax, c_begin, c_end);
       else
         store_tile_bf16_staged<BN, false>(args, taddr, b, mb * BM + quad * 32, n0, alpha, beta, amax, c_begin, c_end,
-                                          epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane, ahead, next);
+                                          epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane, ahead, next, nullptr);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);
@@ -756,19 +774,19 @@ struct PairCfg {
 template <int BN, bool A_MN, bool B_MN, bool FP8, bool AHEAD = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmKernelArgs args) {
+                 const __grid_constant__ CUtensorMap tmC, const GemmKernelArgs args) {
   using C = PairCfg<BN, A_MN, B_MN, FP8>;
   constexpr int BK = C::BK;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES;            // 8 x 4 KB, 1024-byte aligned (TMA swizzle atom)
+  uint64_t* full = reinterpret_cast<uint64_t*>(epi_stage + C::EPI_BYTES);
   uint64_t* empty = full + C::STAGES;
   uint64_t* acc_full = empty + C::STAGES;
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  uint8_t* epi_stage = smem + C::STAGES * C::STAGE_BYTES + 512;      // 8 x 4 KB, 128-byte aligned
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -784,7 +802,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     *abort_flag = 0;
     fence_mbar_init();
   }
-  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); }
+  if (warp == 0 && lane == 0) { tma_prefetch_desc(&tmA); tma_prefetch_desc(&tmB); if (args.c_tma) tma_prefetch_desc(&tmC); }
   if (warp == 1) { tmem_alloc_pair(tmem_slot, C::TMEM_COLS); tmem_relinquish_pair(); }
   tc_fence_before();
   cluster_sync_all();                               // both CTAs' barriers exist before anyone signals them
@@ -863,7 +881,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
     const int quad = warp & 3;
     constexpr int CHUNKS = BN / 16, SPLIT = (CHUNKS + 1) / 2;
-    const int c_begin = (warp - 2) < 4 ? 0 : SPLIT, c_end = (warp - 2) < 4 ? SPLIT : CHUNKS;
+    // with TMA stores a warp's columns are split into whole 64-column groups where possible (a partial group is stored by hand)
+    const int split = (args.c_tma && CHUNKS > 8) ? (SPLIT + 3) / 4 * 4 : SPLIT;
+    const int c_begin = (warp - 2) < 4 ? 0 : split, c_end = (warp - 2) < 4 ? split : CHUNKS;
     int acc = 0; uint32_t acc_phase = 0; bool ok = true;
     float amax = 0.f;
     float alpha = args.alpha;
@@ -896,12 +916,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         store_tile_row<BN>(args, taddr, b, row, nb * BN, alpha, beta, amax, c_begin, c_end);
       else
         store_tile_bf16_staged<BN, AHEAD>(args, taddr, b, mb * (2 * BM) + rank * BM + quad * 32, nb * BN, alpha, beta,
-                                          amax, c_begin, c_end, epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane, ahead, next);
+                                          amax, c_begin, c_end, epi_stage + (warp - 2) * EPI_STAGE_BYTES, lane, ahead, next,
+                                          args.c_tma ? &tmC : nullptr);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));
       if (++acc == 2) { acc = 0; acc_phase ^= 1; }
     }
+    if (args.c_tma && lane == 0) tma_store_wait<0>();     // the warp's last stores have left shared memory and landed
     if (args.amax_out) {
 #pragma unroll
       for (int w = 16; w > 0; w >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, w));
@@ -939,6 +961,21 @@ static int f32_staged_default() {
     return (e && e[0] == 'd') ? 0 : 1;
   }();
   return v;
+}
+
+// Tensor map over a bf16 output for the epilogue's TMA stores: boxes of 32 rows x 64 columns (one warp's staging tile).
+// Returns false, and leaves a placeholder in *tm, where the output cannot be stored that way (fp32, unaligned base or
+// pitch, narrower than a box); the kernel then writes it with ordinary stores.
+static bool make_c_tmap(const GemmDesc& d, const CUtensorMap& placeholder, CUtensorMap* tm) {
+  static const bool enabled = [] { const char* e = getenv("NANOCHAT_GEMM_TMA_STORE"); return !e || atoi(e) != 0; }();
+  *tm = placeholder;
+  if (!enabled || d.c_f32 || d.N < 64 || d.M < 32) return false;
+  if ((reinterpret_cast<uintptr_t>(d.C) & 15) || (d.ldc & 7) || (d.batch > 1 && (d.bsc & 7))) return false;
+  uint64_t dims[3] = {static_cast<uint64_t>(d.N), static_cast<uint64_t>(d.M), static_cast<uint64_t>(d.batch)};
+  uint64_t str[2] = {static_cast<uint64_t>(d.ldc) * 2,
+                     d.batch > 1 ? static_cast<uint64_t>(d.bsc) * 2 : static_cast<uint64_t>(d.ldc) * 2 * dims[1]};
+  uint32_t box[3] = {64, 32, 1};
+  return make_tmap(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d.C, dims, str, box);
 }
 
 // bf16 output with an auxiliary operand that the epilogue combines with the product (not relu^2, which needs none)
@@ -980,6 +1017,8 @@ static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t strea
   a.C = d.C; a.ldc = d.ldc; a.bsc = d.bsc;
   a.aux = d.aux; a.ldaux = d.ldaux; a.bsaux = d.bsaux;
   a.alpha = d.alpha; a.beta = d.beta; a.epi = d.epi; a.c_f32 = d.c_f32; a.f32_staged = f32_staged_default();
+  CUtensorMap tmC;
+  a.c_tma = make_c_tmap(d, tmA, &tmC);
   a.scale_a = d.scale_a; a.scale_b = d.scale_b; a.amax_out = d.amax_out;
   a.m_blocks = (d.M + BM - 1) / BM;
   a.n_blocks = (d.N + BN - 1) / BN;
@@ -988,7 +1027,7 @@ static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t strea
   a.status = status;
   const long long tiles = 1ll * a.m_blocks * a.n_blocks * d.batch;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-  kern<<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, a);
+  kern<<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmC, a);
   return cudaGetLastError();
 }
 
@@ -1045,6 +1084,8 @@ static cudaError_t launch_pair_cfg(const GemmDesc& d, int* status, cudaStream_t 
   a.C = d.C; a.ldc = d.ldc; a.bsc = d.bsc;
   a.aux = d.aux; a.ldaux = d.ldaux; a.bsaux = d.bsaux;
   a.alpha = d.alpha; a.beta = d.beta; a.epi = d.epi; a.c_f32 = d.c_f32; a.f32_staged = f32_staged_default();
+  CUtensorMap tmC;
+  a.c_tma = make_c_tmap(d, tmA, &tmC);
   a.scale_a = d.scale_a; a.scale_b = d.scale_b; a.amax_out = d.amax_out;
   a.m_blocks = (d.M + 2 * BM - 1) / (2 * BM);
   a.n_blocks = (d.N + BN - 1) / BN;
@@ -1064,7 +1105,7 @@ static cudaError_t launch_pair_cfg(const GemmDesc& d, int* status, cudaStream_t 
   attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, a);
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmC, a);
 }
 
 template <bool A_MN, bool B_MN, bool FP8>
@@ -1205,6 +1246,7 @@ static cudaError_t launch_mx(const GemmDesc& d, const MxScales& sf, int* status,
   a.C = d.C; a.ldc = d.ldc; a.bsc = 0;
   a.aux = d.aux; a.ldaux = d.ldaux; a.bsaux = 0;
   a.alpha = d.alpha; a.beta = d.beta; a.epi = d.epi; a.c_f32 = d.c_f32; a.f32_staged = f32_staged_default();
+  a.c_tma = 0;
   a.scale_a = nullptr; a.scale_b = nullptr; a.amax_out = d.amax_out;
   a.m_blocks = (d.M + BM - 1) / BM;
   a.n_blocks = (d.N + BN - 1) / BN;
