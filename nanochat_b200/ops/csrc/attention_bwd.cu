@@ -401,25 +401,57 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
   }
 }
 
-// delta[b,h,t] = sum_d dO * O ; one warp per (b,t,h) row
-__global__ void __launch_bounds__(128)
+// delta[b,h,t] = sum_d dO * O. A warp owns 32 consecutive tokens of one (b, h): a row (128 values = 256 B of each
+// tensor) is read by a half-warp with 16-byte loads, eight rows' loads are in flight per warp, and the 32 sums leave as
+// one 128-byte store (delta is (B, H, T), so a warp per token would scatter 4-byte writes T apart).
+constexpr int DELTA_WARPS = 4;
+__global__ void __launch_bounds__(DELTA_WARPS * 32)
 attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                   long long o_bat, long long o_tok, long long o_head, long long g_bat, long long g_tok,
                   long long g_head, float* __restrict__ delta, int B, int T, int H) {
-  const int lane = threadIdx.x & 31;
-  const long long rows = (long long)B * T * H;
-  for (long long row = blockIdx.x * 4ll + (threadIdx.x >> 5); row < rows; row += gridDim.x * 4ll) {
-    const int h = (int)(row % H);
-    const long long bt = row / H;
-    const int t = (int)(bt % T);
-    const int b = (int)(bt / T);
-    const uint2 a = *reinterpret_cast<const uint2*>(o + b * o_bat + t * o_tok + h * o_head + lane * 4);
-    const uint2 g = *reinterpret_cast<const uint2*>(d_o + b * g_bat + t * g_tok + h * g_head + lane * 4);
-    float2 a0 = unpack_bf16(a.x), a1 = unpack_bf16(a.y), g0 = unpack_bf16(g.x), g1 = unpack_bf16(g.y);
-    float s = a0.x * g0.x + a0.y * g0.y + a1.x * g1.x + a1.y * g1.y;
+  const int lane = threadIdx.x & 31, half = lane >> 4, sub = lane & 15;
+  const int t_blocks = (T + 31) / 32;
+  const long long units = (long long)B * H * t_blocks;
+  for (long long u = blockIdx.x * (long long)DELTA_WARPS + (threadIdx.x >> 5); u < units;
+       u += gridDim.x * (long long)DELTA_WARPS) {
+    const int tb = (int)(u % t_blocks);
+    const long long bh = u / t_blocks;
+    const int h = (int)(bh % H), b = (int)(bh / H);
+    const int t0 = tb * 32;
+    const __nv_bfloat16* op = o + b * o_bat + h * o_head + sub * 8;
+    const __nv_bfloat16* gp = d_o + b * g_bat + h * g_head + sub * 8;
+    float mine = 0.f;
 #pragma unroll
-    for (int w = 16; w > 0; w >>= 1) s += __shfl_xor_sync(0xffffffffu, s, w);
-    if (lane == 0) delta[((long long)b * H + h) * T + t] = s;
+    for (int i0 = 0; i0 < 16; i0 += 4) {
+      uint4 a[4], g[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int t = t0 + 2 * (i0 + j) + half;
+        a[j] = g[j] = make_uint4(0, 0, 0, 0);
+        if (t < T) {
+          a[j] = *reinterpret_cast<const uint4*>(op + t * o_tok);
+          g[j] = *reinterpret_cast<const uint4*>(gp + t * g_tok);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t aw[4] = {a[j].x, a[j].y, a[j].z, a[j].w}, gw[4] = {g[j].x, g[j].y, g[j].z, g[j].w};
+        float s = 0.f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 x = unpack_bf16(aw[q]), y = unpack_bf16(gw[q]);
+          s += x.x * y.x + x.y * y.y;
+        }
+#pragma unroll
+        for (int w = 8; w > 0; w >>= 1) s += __shfl_xor_sync(0xffffffffu, s, w);
+        const float other = __shfl_xor_sync(0xffffffffu, s, 16);
+        // lower half holds the sum of token 2i, upper half of token 2i + 1; lane r keeps token t0 + r
+        const int i = i0 + j;
+        if (lane == 2 * i) mine = half ? other : s;
+        if (lane == 2 * i + 1) mine = half ? s : other;
+      }
+    }
+    if (t0 + lane < T) delta[((long long)b * H + h) * T + t0 + lane] = mine;
   }
 }
 
@@ -453,10 +485,13 @@ cudaError_t attention_bwd(const AttnBwdDesc& d, int* status, cudaStream_t stream
              map4(&k64, f.k, f.Tk, f.Hkv, f.B, f.k_tok, f.k_head, f.k_bat, 64) &&
              map4(&v64, f.v, f.Tk, f.Hkv, f.B, f.v_tok, f.v_head, f.v_bat, 64);
   if (!okm) return cudaErrorInvalidValue;
+  // the pre-pass reads O with 16-byte loads (dO has passed the encoder's checks above)
+  if ((reinterpret_cast<uintptr_t>(f.o) & 15) || (f.o_tok & 7) || (f.o_head & 7) || (f.o_bat & 7)) return cudaErrorInvalidValue;
   {
-    const long long rows = (long long)f.B * f.Tq * f.H;
-    const int grid = (int)((rows + 3) / 4 < 148 * 16 ? (rows + 3) / 4 : 148 * 16);
-    attn_delta_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)f.o, (const __nv_bfloat16*)d.d_o, f.o_bat,
+    const long long units = (long long)f.B * f.H * ((f.Tq + 31) / 32);
+    const long long blocks = (units + DELTA_WARPS - 1) / DELTA_WARPS;
+    const int grid = (int)(blocks < 148 * 16 ? blocks : 148 * 16);
+    attn_delta_kernel<<<grid, DELTA_WARPS * 32, 0, stream>>>((const __nv_bfloat16*)f.o, (const __nv_bfloat16*)d.d_o, f.o_bat,
                                                 f.o_tok, f.o_head, d.do_bat, d.do_tok, d.do_head, d.delta, f.B,
                                                 f.Tq, f.H);
   }

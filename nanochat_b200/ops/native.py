@@ -21,6 +21,7 @@ Reference semantics: nanochat/gpt.py:84-153,459-521 (forward math); the oracle f
 every function here is `ops/reference.py`.
 """
 
+import itertools
 import math
 import weakref
 
@@ -586,12 +587,20 @@ def _contiguous_rows(ws):
     return torch.as_strided(first, (rows, K), (K, 1))
 
 
+# d loss / d x0 gets a contribution from every layer that mixes x0 in. The layers' backward passes add into one running
+# buffer per forward pass instead of handing autograd one full-size tensor each: the first layer to see an x0 tensor in
+# the forward pass (the last to run backward) owns the pass and returns the total, the others return nothing.
+_dx0_running = {}      # pass id -> gradient of x0 summed over the layers whose backward has run
+_x0_pass_ids = itertools.count(1)
+_x0_open = set()       # passes whose owning layer has not run its backward yet
+
+
 class _LayerFn(Function):
     """One transformer block: mix+norm, attention (with VE gating, rotary, QK-norm), MLP."""
 
     @staticmethod
     def forward(ctx, x, x0, idx, cos, sin, resid_lambdas, x0_lambdas, layer, wq, wk, wv, wo, wfc, wpr,
-                wgate, ve_w, window, n_head, n_kv_head, kv_sink=None):
+                wgate, ve_w, window, n_head, n_kv_head, kv_sink=None, x0_pass=(0, True)):
         B, T, C = x.shape
         M = B * T
         D = C // n_head
@@ -667,6 +676,7 @@ class _LayerFn(Function):
 
         ctx.f8 = f8
         ctx.meta = (B, T, C, D, n_head, n_kv_head, layer, window, has_ve)
+        ctx.x0_pass = x0_pass
         ctx.save_for_backward(x2, x02, idx_c, cos2, sin2, resid_lambdas, x0_lambdas, wq, wk, wv, wo, wfc, wpr,
                               wgate, ve_w, xm, xn, qkv, rstd, y2, lse, xa, xn2, h)
         return xo.view(B, T, C)
@@ -804,23 +814,42 @@ class _LayerFn(Function):
 
         # ---- mix + norm
         dx = torch.empty(M, C, dtype=BF16, device=dev)
-        dx0 = torch.empty(M, C, dtype=BF16, device=dev)
+        pass_id, owns_pass = ctx.x0_pass
+        dx0 = _dx0_running.pop(pass_id, None) if pass_id else None
+        accumulate = dx0 is not None
+        if dx0 is None:
+            dx0 = torch.empty(M, C, dtype=BF16, device=dev)
         amax_dx = _zeroed_scalar(dev) if f8 is not None else None
-        _C.mixnorm_bwd(dxn, dxa, dgate_x, xm, x2, x02, resid_lambdas, x0_lambdas, layer, dx, dx0, False,
+        _C.mixnorm_bwd(dxn, dxa, dgate_x, xm, x2, x02, resid_lambdas, x0_lambdas, layer, dx, dx0, accumulate,
                        _grad_buffer(resid_lambdas), _grad_buffer(x0_lambdas), amax_dx)
         if amax_dx is not None:
             _amax_hints[dx.data_ptr()] = amax_dx
-        return (dx.view(B, T, C), dx0.view(B, T, C)) + (None,) * 18
+        if not owns_pass:
+            _dx0_running[pass_id] = dx0
+            return (dx.view(B, T, C), None) + (None,) * 19
+        _x0_open.discard(pass_id)
+        return (dx.view(B, T, C), dx0.view(B, T, C)) + (None,) * 19
 
 
 def layer_forward(block, x, x0, idx, ve_weight, cos_sin, window_size, resid_lambdas, x0_lambdas, layer, kv_sink=None):
     attn, mlp = block.attn, block.mlp
+    pass_id, owns_pass = 0, True
+    if torch.is_grad_enabled() and x0.requires_grad:
+        pass_id = getattr(x0, "_nc_x0_pass", None)
+        owns_pass = pass_id not in _x0_open       # first layer to take this x0 (or the pass it belonged to has finished)
+        if owns_pass:
+            if len(_x0_open) > 64:                # passes whose backward never ran
+                _x0_open.clear()
+            for stale in [k for k in _dx0_running if k not in _x0_open]:
+                del _dx0_running[stale]
+            pass_id = x0._nc_x0_pass = next(_x0_pass_ids)
+            _x0_open.add(pass_id)
     return _LayerFn.apply(
         x, x0, idx, cos_sin[0], cos_sin[1], resid_lambdas, x0_lambdas, layer,
         attn.c_q.weight, attn.c_k.weight, attn.c_v.weight, attn.c_proj.weight,
         mlp.c_fc.weight, mlp.c_proj.weight,
         attn.ve_gate.weight if ve_weight is not None else None, ve_weight,
-        window_size[0], attn.n_head, attn.n_kv_head, kv_sink)
+        window_size[0], attn.n_head, attn.n_kv_head, kv_sink, (pass_id, owns_pass))
 
 
 # ------------------------------------------------------------------------ head function
