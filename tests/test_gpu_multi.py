@@ -18,11 +18,12 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("shape", ["4,256", "26,128"])
+@pytest.mark.parametrize("shape", ["4,256", "26,128", "1,256"])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_fused_p2p_optimizer_matches_nccl(world, shape, tmp_path):
     """shape = layers,width. "26,128" is the flagship's ownership pattern at toy width: Muon groups of 104, 26 and 26
-    matrices, so with 8 ranks they own 13 / 4 / 4 and the last ranks own fewer or none."""
+    matrices, so with 8 ranks they own 13 / 4 / 4 and the last ranks own fewer or none. "1,256" has Muon groups of a single
+    matrix: every rank but the first owns nothing of them, already with 2 ranks."""
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     out = str(tmp_path / "p2p.json")
