@@ -248,7 +248,8 @@ void amax_bf16(const Tensor& x, Tensor& amax) {
   NC_CHECK(nc::amax_bf16(x.data_ptr(), x.stride(0), (int)x.size(0), (int)x.size(1), amax.data_ptr<float>(), cur_stream()));
 }
 // q: fp8 (e4m3fn or e5m2) dense (rows, cols); inv_scale: fp32 scalar that receives the de-quantisation factor.
-void quantize_bf16(const Tensor& x, const Tensor& amax, Tensor& q, Tensor& inv_scale) {
+// square: quantise x^2 instead of x, `amax` holding max|x|.
+void quantize_bf16(const Tensor& x, const Tensor& amax, Tensor& q, Tensor& inv_scale, bool square) {
   check_bf16(x, "x");
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "quantize: 2-D, innermost contiguous");
   const bool e5 = q.scalar_type() == at::kFloat8_e5m2;
@@ -258,7 +259,7 @@ void quantize_bf16(const Tensor& x, const Tensor& amax, Tensor& q, Tensor& inv_s
               inv_scale.numel() == 1, "scalars");
   const c10::cuda::CUDAGuard guard(x.device());
   NC_CHECK(nc::quantize_bf16(x.data_ptr(), x.stride(0), (int)x.size(0), (int)x.size(1), amax.data_ptr<float>(),
-                             q.data_ptr(), inv_scale.data_ptr<float>(), e5 ? 1 : 0, cur_stream()));
+                             q.data_ptr(), inv_scale.data_ptr<float>(), e5 ? 1 : 0, square ? 1 : 0, cur_stream()));
 }
 
 void cast_f32_bf16(const Tensor& src, Tensor& dst) {
@@ -611,7 +612,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("Hkv"), py::arg("window"), py::arg("scale"), py::arg("scratch"), py::arg("y"), py::arg("table") = py::none());
   m.def("decode_attn_scratch", &decode_attn_scratch);
   m.def("amax_bf16", &amax_bf16);
-  m.def("quantize_bf16", &quantize_bf16);
+  m.def("quantize_bf16", &quantize_bf16, py::arg("x"), py::arg("amax"), py::arg("q"), py::arg("inv_scale"),
+        py::arg("square") = false);
   m.def("gemm_mx", &gemm_mx);
   m.def("mx_quantize", &mx_quantize);
   m.def("read_status", &read_status);

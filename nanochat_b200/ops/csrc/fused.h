@@ -41,7 +41,7 @@ cudaError_t cast_f32_bf16(const float* src, void* dst, size_t n, cudaStream_t s)
 // *inv_scale = amax/FMAX; e5m2 selects the 5-bit-exponent format (FMAX 57344) instead of e4m3 (448).
 cudaError_t amax_bf16(const void* x, long long ld, int rows, int cols, float* amax, cudaStream_t s);
 cudaError_t quantize_bf16(const void* x, long long ld, int rows, int cols, const float* amax, void* q,
-                          float* inv_scale, int e5m2, cudaStream_t s);
+                          float* inv_scale, int e5m2, int square, cudaStream_t s);
 
 // ---- soft-capped cross entropy over bf16 logits (loss.cu)
 // loss[row] = logsumexp(cap*tanh(l/cap)) - cap*tanh(l[target]/cap); 0 for target < 0. lse is saved.

@@ -136,6 +136,9 @@ __device__ __forceinline__ void store_tile_row(const GemmKernelArgs& args, uint3
             if (args.epi == EPI_RELU2) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) { float tpos = fmaxf(vv[j], 0.f); vv[j] = tpos * tpos; }
+            } else if (args.epi == EPI_RELU) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) vv[j] = fmaxf(vv[j], 0.f);
             } else if (xrow) {
               uint4 xa = *reinterpret_cast<const uint4*>(xrow + h * 8);
               const uint32_t xs[4] = {xa.x, xa.y, xa.z, xa.w};
@@ -145,6 +148,9 @@ __device__ __forceinline__ void store_tile_row(const GemmKernelArgs& args, uint3
                 if (args.epi == EPI_MUL2SQRT) {
                   vv[2 * j] *= 2.f * sqrtf(f.x);
                   vv[2 * j + 1] *= 2.f * sqrtf(f.y);
+                } else if (args.epi == EPI_MULAUX) {
+                  vv[2 * j] *= f.x;
+                  vv[2 * j + 1] *= f.y;
                 } else {
                   vv[2 * j] += beta * f.x;
                   vv[2 * j + 1] += beta * f.y;
@@ -187,7 +193,7 @@ struct TileAt {
 };
 
 __device__ __forceinline__ bool aux_bf16_used(const GemmKernelArgs& args) {
-  return args.aux != nullptr && !args.c_f32 && args.epi != EPI_RELU2;
+  return args.aux != nullptr && !args.c_f32 && args.epi != EPI_RELU2 && args.epi != EPI_RELU;
 }
 
 __device__ __forceinline__ void aux_request(const GemmKernelArgs& args, AuxAhead& ahead, const TileAt& at, int g, int c_end,
@@ -279,6 +285,9 @@ __device__ __forceinline__ void store_tile_bf16_staged(const GemmKernelArgs& arg
           if (args.epi == EPI_RELU2) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) { const float tpos = fmaxf(vv[j], 0.f); vv[j] = tpos * tpos; }
+          } else if (args.epi == EPI_RELU) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) vv[j] = fmaxf(vv[j], 0.f);
           } else if (use_aux) {
             const uint4 xa = *reinterpret_cast<const uint4*>(slot);
             const uint32_t xs[4] = {xa.x, xa.y, xa.z, xa.w};
@@ -288,6 +297,9 @@ __device__ __forceinline__ void store_tile_bf16_staged(const GemmKernelArgs& arg
               if (args.epi == EPI_MUL2SQRT) {
                 vv[2 * j] *= 2.f * sqrtf(f.x);
                 vv[2 * j + 1] *= 2.f * sqrtf(f.y);
+              } else if (args.epi == EPI_MULAUX) {
+                vv[2 * j] *= f.x;
+                vv[2 * j + 1] *= f.y;
               } else {
                 vv[2 * j] += beta * f.x;
                 vv[2 * j + 1] += beta * f.y;
@@ -979,7 +991,9 @@ static bool make_c_tmap(const GemmDesc& d, const CUtensorMap& placeholder, CUten
 }
 
 // bf16 output with an auxiliary operand that the epilogue combines with the product (not relu^2, which needs none)
-static bool aux_ahead_wanted(const GemmDesc& d) { return d.aux != nullptr && !d.c_f32 && d.epi != EPI_RELU2; }
+static bool aux_ahead_wanted(const GemmDesc& d) {
+  return d.aux != nullptr && !d.c_f32 && d.epi != EPI_RELU2 && d.epi != EPI_RELU;
+}
 
 template <int BN, bool A_MN, bool B_MN, bool FP8, bool AHEAD = false>
 static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t stream) {
@@ -1033,9 +1047,11 @@ static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t strea
 
 template <bool A_MN, bool B_MN, bool FP8>
 static cudaError_t launch_bn(int bn, const GemmDesc& d, int* status, cudaStream_t s) {
-  // the activation-gradient layout with an auxiliary operand (the MLP's relu^2 derivative) has kernels of its own
-  if constexpr (!A_MN && B_MN) {
+  // forward and activation-gradient layouts with a bf16 auxiliary operand (residual add, the MLP's relu^2 derivative)
+  // have kernels of their own, which request that operand ahead of its use
+  if constexpr (!A_MN) {
     if (aux_ahead_wanted(d) && bn == 256) return launch_cfg<256, A_MN, B_MN, FP8, true>(d, status, s);
+    if (aux_ahead_wanted(d) && bn == 208) return launch_cfg<208, A_MN, B_MN, FP8, true>(d, status, s);
     if (aux_ahead_wanted(d) && bn == 128) return launch_cfg<128, A_MN, B_MN, FP8, true>(d, status, s);
   }
   switch (bn) {
@@ -1110,8 +1126,9 @@ static cudaError_t launch_pair_cfg(const GemmDesc& d, int* status, cudaStream_t 
 
 template <bool A_MN, bool B_MN, bool FP8>
 static cudaError_t launch_pair_bn(int bn, const GemmDesc& d, int* status, cudaStream_t s) {
-  if constexpr (!A_MN && B_MN) {
+  if constexpr (!A_MN) {
     if (aux_ahead_wanted(d) && bn == 256) return launch_pair_cfg<256, A_MN, B_MN, FP8, true>(d, status, s);
+    if (aux_ahead_wanted(d) && bn == 208) return launch_pair_cfg<208, A_MN, B_MN, FP8, true>(d, status, s);
     if (aux_ahead_wanted(d) && bn == 128) return launch_pair_cfg<128, A_MN, B_MN, FP8, true>(d, status, s);
   }
   switch (bn) {

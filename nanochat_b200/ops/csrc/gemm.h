@@ -10,6 +10,8 @@ enum GemmEpilogue : int {
   EPI_LINEAR = 0,    // C = alpha*acc + beta*aux           (aux optional, same dtype as C)
   EPI_RELU2 = 1,     // C = relu(alpha*acc)^2              (bf16 C)
   EPI_MUL2SQRT = 2,  // C = alpha*acc * 2*sqrt(aux)        (bf16 C; backward of relu^2 from its output)
+  EPI_RELU = 3,      // C = relu(alpha*acc)                (bf16 C; the fp8 MLP keeps relu(x) and squares it while quantising)
+  EPI_MULAUX = 4,    // C = alpha*acc * aux                (bf16 C; backward of relu^2 from relu(x), with alpha carrying the 2)
 };
 
 // C[b] (M x N, row-major, leading dim ldc) = epilogue(alpha * A[b] * B[b]^T, aux[b])

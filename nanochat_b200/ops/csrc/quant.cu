@@ -45,12 +45,15 @@ amax_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int rows, in
   }
 }
 
-template <bool E5M2>
+// SQUARE: the tensor quantised is x^2 (x = relu output of the MLP's up projection, kept in bf16 for the backward pass;
+// its square is the down projection's input and exists only in fp8); `amax` then holds max|x| and max|x^2| is its square.
+template <bool E5M2, bool SQUARE>
 __global__ void __launch_bounds__(256)
 quantize_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int rows, int cols,
                      const float* __restrict__ amax, uint8_t* __restrict__ q, float* __restrict__ inv_scale) {
   constexpr float FMAX = E5M2 ? 57344.f : 448.f;
-  const float a = fmaxf(__ldg(amax), 1e-12f);
+  const float a_in = __ldg(amax);
+  const float a = fmaxf(SQUARE ? a_in * a_in : a_in, 1e-12f);
   const float scale = FMAX / a;
   if (blockIdx.x == 0 && threadIdx.x == 0) *inv_scale = a / FMAX;
   const int vec_per_row = cols >> 4;      // 16 elements per thread step: 32 B in, 16 B out
@@ -64,6 +67,7 @@ quantize_bf16_kernel(const __nv_bfloat16* __restrict__ x, long long ld, int rows
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float2 lo = unpack_bf16(w[2 * j]), hi = unpack_bf16(w[2 * j + 1]);
+      if (SQUARE) { lo.x *= lo.x; lo.y *= lo.y; hi.x *= hi.x; hi.y *= hi.y; }
       lo.x *= scale; lo.y *= scale; hi.x *= scale; hi.y *= scale;
       const __nv_fp8x2_storage_t p0 = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, E5M2 ? __NV_E5M2 : __NV_E4M3);
       const __nv_fp8x2_storage_t p1 = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, E5M2 ? __NV_E5M2 : __NV_E4M3);
@@ -87,13 +91,15 @@ cudaError_t amax_bf16(const void* x, long long ld, int rows, int cols, float* am
 }
 
 cudaError_t quantize_bf16(const void* x, long long ld, int rows, int cols, const float* amax, void* q,
-                          float* inv_scale, int e5m2, cudaStream_t s) {
+                          float* inv_scale, int e5m2, int square, cudaStream_t s) {
   if ((cols & 15) || (ld & 7)) return cudaErrorInvalidValue;
   const int grid = quant_grid((long long)rows * (cols >> 4));
   auto* xp = reinterpret_cast<const __nv_bfloat16*>(x);
   auto* qp = reinterpret_cast<uint8_t*>(q);
-  if (e5m2) quantize_bf16_kernel<true><<<grid, 256, 0, s>>>(xp, ld, rows, cols, amax, qp, inv_scale);
-  else      quantize_bf16_kernel<false><<<grid, 256, 0, s>>>(xp, ld, rows, cols, amax, qp, inv_scale);
+  if (e5m2 && square) return cudaErrorInvalidValue;          // squared tensors are forward activations: e4m3
+  if (e5m2)        quantize_bf16_kernel<true, false><<<grid, 256, 0, s>>>(xp, ld, rows, cols, amax, qp, inv_scale);
+  else if (square) quantize_bf16_kernel<false, true><<<grid, 256, 0, s>>>(xp, ld, rows, cols, amax, qp, inv_scale);
+  else             quantize_bf16_kernel<false, false><<<grid, 256, 0, s>>>(xp, ld, rows, cols, amax, qp, inv_scale);
   return cudaGetLastError();
 }
 

@@ -78,9 +78,10 @@ def bench_gemm(args, nat):
         if wg:
             kw.update(aux=C, beta=1.0)
         elif args.epi != "linear":     # the MLP's fused epilogues: relu^2 on the way out, or its derivative from the saved output
-            kw.update(epi={"relu2": nat.EPI_RELU2, "mul2sqrt": nat.EPI_MUL2SQRT}[args.epi])
-            if args.epi == "mul2sqrt":
-                kw.update(aux=torch.rand(m, n, device=dev).to(bf16))
+            kw.update(epi={"relu2": nat.EPI_RELU2, "mul2sqrt": nat.EPI_MUL2SQRT, "relu": nat.EPI_RELU,
+                           "mulaux": nat.EPI_MULAUX, "residual": nat.EPI_LINEAR}[args.epi])
+            if args.epi in ("mul2sqrt", "mulaux", "residual"):
+                kw.update(aux=torch.rand(m, n, device=dev).to(bf16), beta=1.0)
         if args.amax:
             kw.update(amax_out=torch.zeros(1, device=dev))
         ms = _time(lambda: nat.gemm(A, B, C, **kw), args.iters, args.warmup)
@@ -236,7 +237,7 @@ def main():
     ap.add_argument("--layout", default="fwd", choices=["fwd", "dgrad", "wgrad"])
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8", "mxfp8"], help="GEMM operand type")
     ap.add_argument("--pair", type=int, default=-1, help="GEMM: 1 = CTA-pair kernel, 0 = single-CTA kernel, -1 = library choice")
-    ap.add_argument("--epi", default="linear", choices=["linear", "relu2", "mul2sqrt"], help="GEMM (fp8 / --pair): fused epilogue")
+    ap.add_argument("--epi", default="linear", choices=["linear", "relu2", "mul2sqrt", "relu", "mulaux", "residual"], help="GEMM (fp8 / --pair): fused epilogue")
     ap.add_argument("--amax", type=int, default=0, help="GEMM (fp8 / --pair): 1 = the epilogue also reports max|output|")
     ap.add_argument("--batch", type=int, default=16)
     ap.add_argument("--seq", type=int, default=2048)

@@ -13,7 +13,8 @@ cross entropy. Consequences:
     `.grad` buffer (fp32 += A^T B), embedding-table gradients into fp32 `grad32`
     buffers by atomic scatter; these Functions therefore return None for parameters;
   * relu^2 is the epilogue of the c_fc GEMM, its derivative the epilogue of the c_proj
-    dgrad GEMM (2*sqrt(out) recovers relu(h) from the saved output), residual adds are
+    dgrad GEMM (2*sqrt(out) recovers relu(h) from the saved output; the fp8 path saves
+    relu(h) itself and squares it while quantising), residual adds are
     GEMM epilogues, and rotary + QK-norm + value-embedding gating is one in-place pass
     over the fused QKV buffer.
 
@@ -33,7 +34,7 @@ from nanochat_b200.utils.build import load_cuda_extension
 
 _C = load_cuda_extension()
 
-EPI_LINEAR, EPI_RELU2, EPI_MUL2SQRT = 0, 1, 2
+EPI_LINEAR, EPI_RELU2, EPI_MUL2SQRT, EPI_RELU, EPI_MULAUX = 0, 1, 2, 3, 4
 BF16 = torch.bfloat16
 
 # 'native' = tcgen05 flash attention kernels, 'sdpa' = PyTorch SDPA (oracle for A/B runs)
@@ -191,14 +192,15 @@ def _zeroed_scalar(device):
     return s
 
 
-def quantize(x2, dtype=E4M3, amax=None):
-    """(fp8 copy, de-quantisation scale) of a bf16 matrix; `amax` = device scalar holding max|x| if already known."""
+def quantize(x2, dtype=E4M3, amax=None, square=False):
+    """(fp8 copy, de-quantisation scale) of a bf16 matrix; `amax` = device scalar holding max|x| if already known.
+    square=True quantises x^2 (e4m3 only) without that tensor ever existing in bf16."""
     if amax is None:
         amax = _zeroed_scalar(x2.device)
         _C.amax_bf16(x2, amax)
     q = torch.empty(x2.shape, dtype=dtype, device=x2.device)
     inv = torch.empty(1, dtype=torch.float32, device=x2.device)
-    _C.quantize_bf16(x2, amax, q, inv)
+    _C.quantize_bf16(x2, amax, q, inv, square)
     return q, inv
 
 
@@ -662,9 +664,11 @@ class _LayerFn(Function):
             _C.norm_fwd(xa, xn2, amax_xn2)
             x2q8, s2 = quantize(xn2, amax=amax_xn2)
             w8, sw = fp8_weight(shadow_of(wfc))
+            # h holds relu(.) here, not its square: the square (the down projection's input) exists only in fp8, written
+            # by the quantiser, and the backward pass multiplies by 2 h instead of 2 sqrt(h^2)
             amax_h = _zeroed_scalar(dev)
-            gemm(x2q8, w8, h, epi=EPI_RELU2, scale_a=s2, scale_b=sw, amax_out=amax_h)
-            hq8, sh = quantize(h, amax=amax_h)
+            gemm(x2q8, w8, h, epi=EPI_RELU, scale_a=s2, scale_b=sw, amax_out=amax_h)
+            hq8, sh = quantize(h, amax=amax_h, square=True)
             w8, sw = fp8_weight(shadow_of(wpr))
             gemm(hq8, w8, xo, aux=xa, beta=1.0, scale_a=sh, scale_b=sw)
             f8 = (xq8, sx, yq8, sy, x2q8, s2, hq8, sh)
@@ -704,7 +708,7 @@ class _LayerFn(Function):
             g8, sg = quantize(dxo2, E5M2, amax=hint)
             w8, sw = fp8_weight(shadow_of(wpr))
             amax_dh = _zeroed_scalar(dev)
-            gemm(g8, w8, dh, b_mn=True, aux=h, epi=EPI_MUL2SQRT, scale_a=sg, scale_b=sw, amax_out=amax_dh)
+            gemm(g8, w8, dh, b_mn=True, aux=h, epi=EPI_MULAUX, alpha=2.0, scale_a=sg, scale_b=sw, amax_out=amax_dh)
             _accumulate_wgrad(wpr, g8, hq8, sg, sh)
             del g8, hq8
             dh8, sdh = quantize(dh, E5M2, amax=amax_dh)
