@@ -51,7 +51,7 @@ float* opt_scalar(const optional<Tensor>& t) {
 // Operands are bf16, or 8-bit floats (e4m3 / e5m2, both operands) with optional per-tensor scales.
 void gemm(const Tensor& A, const Tensor& B, Tensor& C, const optional<Tensor>& aux, bool a_mn, bool b_mn,
           double alpha, double beta, int64_t epi, int64_t bn, int64_t pair, const optional<Tensor>& scale_a,
-          const optional<Tensor>& scale_b, const optional<Tensor>& amax_out) {
+          const optional<Tensor>& scale_b, const optional<Tensor>& amax_out, bool symmetric) {
   const bool fp8 = A.scalar_type() == at::kFloat8_e4m3fn || A.scalar_type() == at::kFloat8_e5m2;
   if (fp8) {
     TORCH_CHECK(A.is_cuda() && B.is_cuda(), "fp8 operands must be CUDA tensors");
@@ -85,6 +85,7 @@ void gemm(const Tensor& A, const Tensor& B, Tensor& C, const optional<Tensor>& a
     d.aux = aux->data_ptr(); d.ldaux = aux->stride(nd - 2); d.bsaux = nd == 3 ? aux->stride(0) : 0;
   }
   d.alpha = (float)alpha; d.beta = (float)beta; d.epi = (int)epi; d.bn = (int)bn; d.pair = (int)pair;
+  d.symmetric = symmetric ? 1 : 0;
   auto scalar = [&](const optional<Tensor>& t, const char* n) -> float* {
     if (!t.has_value() || !t->defined()) return nullptr;
     TORCH_CHECK(t->is_cuda() && t->scalar_type() == at::kFloat && t->numel() == 1, n, " must be a CUDA fp32 scalar");
@@ -100,6 +101,16 @@ void gemm(const Tensor& A, const Tensor& B, Tensor& C, const optional<Tensor>& a
   } else {
     NC_CHECK(nc::gemm_bf16(d, status_ptr(A), cur_stream()));
   }
+}
+
+// Copies the upper triangle of every (n, n) matrix of a bf16 (n, n) or (batch, n, n) tensor over its lower triangle.
+void symmetrize(Tensor& C) {
+  check_bf16(C, "C");
+  const int nd = C.dim();
+  TORCH_CHECK((nd == 2 || nd == 3) && C.size(nd - 1) == C.size(nd - 2) && C.stride(nd - 1) == 1, "symmetrize: square matrices");
+  const c10::cuda::CUDAGuard guard(C.device());
+  NC_CHECK(nc::symmetrize_bf16(C.data_ptr(), (int)C.size(nd - 1), C.stride(nd - 2), nd == 3 ? C.stride(0) : 0,
+                               nd == 3 ? (int)C.size(0) : 1, cur_stream()));
 }
 
 // MXFP8: A (M, K) and B (N, K) row-major fp8, sfa / sfb uint8 in the blocked scale layout (see gemm.h), C (M, N).
@@ -597,7 +608,10 @@ void p2p_small_adamw(const std::vector<int64_t>& grads, int64_t grad_off, Tensor
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
-  m.def("gemm", &gemm);
+  m.def("gemm", &gemm, py::arg("A"), py::arg("B"), py::arg("C"), py::arg("aux"), py::arg("a_mn"), py::arg("b_mn"),
+        py::arg("alpha"), py::arg("beta"), py::arg("epi"), py::arg("bn"), py::arg("pair"), py::arg("scale_a"),
+        py::arg("scale_b"), py::arg("amax_out"), py::arg("symmetric") = false);
+  m.def("symmetrize", &symmetrize);
   m.def("gemm_pick_bn", &gemm_pick_bn);
   m.def("sample_next_token", &sample_next_token);
   m.def("gemv_rows", &gemv_rows, py::arg("x"), py::arg("W"), py::arg("out"), py::arg("aux"), py::arg("epi"),

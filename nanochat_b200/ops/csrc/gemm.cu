@@ -46,6 +46,8 @@ struct GemmKernelArgs {
   int f32_staged;           // fp32 output through the staging tile (whole 128-byte lines) instead of per-row pieces
   int c_tma;                // bf16 output leaves the staging tile as TMA stores (the kernel's third tensor map covers C)
   int m_blocks, n_blocks, group_m;
+  int tiles_per_batch;      // m_blocks * n_blocks, or the tiles on and above the diagonal of a symmetric output
+  int symmetric;            // C = C^T by construction (X X^T, A A): tiles below the diagonal are skipped, the caller mirrors
   uint32_t idesc;
   int* status;
 };
@@ -78,9 +80,16 @@ struct Cfg {
 };
 
 __device__ __forceinline__ void tile_coords(int t, const GemmKernelArgs& a, int& b, int& mb, int& nb) {
-  int per_batch = a.m_blocks * a.n_blocks;
+  int per_batch = a.tiles_per_batch;
   b = t / per_batch;
   int r = t - b * per_batch;
+  if (a.symmetric) {          // square tiles, row by row over the upper triangle: (0,0..T-1), (1,1..T-1), ...
+    int row_len = a.n_blocks;
+    mb = 0;
+    while (r >= row_len) { r -= row_len; ++mb; --row_len; }
+    nb = mb + r;
+    return;
+  }
   int group_tiles = a.group_m * a.n_blocks;
   int g = r / group_tiles;
   int first_m = g * a.group_m;
@@ -421,7 +430,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = (args.K + BK - 1) / BK;
-  const int total_tiles = args.m_blocks * args.n_blocks * args.batch;
+  const int total_tiles = args.tiles_per_batch * args.batch;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -625,7 +634,7 @@ gemm_mx_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int num_kb = sf.k_blocks;
-  const int total_tiles = args.m_blocks * args.n_blocks * args.batch;
+  const int total_tiles = args.tiles_per_batch * args.batch;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -806,7 +815,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int pair = blockIdx.x >> 1;
   const int n_pairs = gridDim.x >> 1;
   const int num_kb = (args.K + BK - 1) / BK;
-  const int total_tiles = args.m_blocks * args.n_blocks * args.batch;   // m_blocks counts 256-row blocks
+  const int total_tiles = args.tiles_per_batch * args.batch;   // m_blocks counts 256-row blocks
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -1037,9 +1046,11 @@ static cudaError_t launch_cfg(const GemmDesc& d, int* status, cudaStream_t strea
   a.m_blocks = (d.M + BM - 1) / BM;
   a.n_blocks = (d.N + BN - 1) / BN;
   a.group_m = group_m_override(16);
+  a.symmetric = d.symmetric && BN == BM && d.M == d.N;          // square tiles only; otherwise every tile is computed
+  a.tiles_per_batch = a.symmetric ? a.n_blocks * (a.n_blocks + 1) / 2 : a.m_blocks * a.n_blocks;
   a.idesc = FP8 ? umma_idesc_f8(BM, BN, A_MN, B_MN, d.a_e5m2, d.b_e5m2) : umma_idesc_bf16(BM, BN, A_MN, B_MN);
   a.status = status;
-  const long long tiles = 1ll * a.m_blocks * a.n_blocks * d.batch;
+  const long long tiles = 1ll * a.tiles_per_batch * d.batch;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   kern<<<grid, GEMM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmC, a);
   return cudaGetLastError();
@@ -1106,9 +1117,11 @@ static cudaError_t launch_pair_cfg(const GemmDesc& d, int* status, cudaStream_t 
   a.m_blocks = (d.M + 2 * BM - 1) / (2 * BM);
   a.n_blocks = (d.N + BN - 1) / BN;
   a.group_m = group_m_override(8);
+  a.symmetric = d.symmetric && BN == 2 * BM && d.M == d.N;      // 256 x 256 tiles only
+  a.tiles_per_batch = a.symmetric ? a.n_blocks * (a.n_blocks + 1) / 2 : a.m_blocks * a.n_blocks;
   a.idesc = FP8 ? umma_idesc_f8(2 * BM, BN, A_MN, B_MN, d.a_e5m2, d.b_e5m2) : umma_idesc_bf16(2 * BM, BN, A_MN, B_MN);
   a.status = status;
-  const long long tiles = 1ll * a.m_blocks * a.n_blocks * d.batch;
+  const long long tiles = 1ll * a.tiles_per_batch * d.batch;
   const int max_pairs = sm_count() / 2;
   const int pairs = static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
   cudaLaunchConfig_t cfg = {};
@@ -1195,6 +1208,7 @@ static GemmPlan gemm_plan(const GemmDesc& d, bool fp8) {
   double best_score = -1;
   const bool pair_ok = d.pair > 0 || (d.pair < 0 && env_pair > 0 && d.M > 2 * BM);
   const bool single_ok = d.pair <= 0;
+  if (d.symmetric && d.M == d.N && d.bn == 0) return pair_ok ? GemmPlan{256, true} : GemmPlan{128, false};   // square tiles
   static const int cand[5] = {256, 208, 128, 64, 32};
   static const double eff1[5] = {1.0, 0.98, 0.86, 0.62, 0.36};
   static const double eff2[3] = {1.14, 1.08, 0.95};
@@ -1214,6 +1228,36 @@ static GemmPlan gemm_plan(const GemmDesc& d, bool fp8) {
     }
   }
   return best;
+}
+
+// Upper triangle -> lower triangle, 32 x 32 blocks transposed through shared memory. Block (bi, bj) with bj > bi is read
+// from rows bi, columns bj and written to rows bj, columns bi; diagonal blocks mirror inside themselves.
+__global__ void __launch_bounds__(256)
+symmetrize_bf16_kernel(__nv_bfloat16* __restrict__ C, int n, long long ld, long long bs) {
+  __shared__ __nv_bfloat16 tile[32][33];
+  const int bi = blockIdx.y, bj = blockIdx.x;
+  if (bj < bi) return;
+  __nv_bfloat16* base = C + static_cast<long long>(blockIdx.z) * bs;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;          // 32 x 8 threads
+#pragma unroll
+  for (int r = ty; r < 32; r += 8) {
+    const int row = bi * 32 + r, col = bj * 32 + tx;
+    if (row < n && col < n) tile[r][tx] = base[static_cast<long long>(row) * ld + col];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = ty; r < 32; r += 8) {
+    const int row = bj * 32 + r, col = bi * 32 + tx;               // destination: transposed block
+    if (row < n && col < n && row > col) base[static_cast<long long>(row) * ld + col] = tile[tx][r];
+  }
+}
+
+cudaError_t symmetrize_bf16(void* C, int n, long long ld, long long bs, int batch, cudaStream_t stream) {
+  if (n <= 0 || batch <= 0) return cudaErrorInvalidValue;
+  const int blocks = (n + 31) / 32;
+  if (batch > 65535 || blocks > 65535) return cudaErrorInvalidValue;
+  symmetrize_bf16_kernel<<<dim3(blocks, blocks, batch), 256, 0, stream>>>(reinterpret_cast<__nv_bfloat16*>(C), n, ld, bs);
+  return cudaGetLastError();
 }
 
 cudaError_t gemm_bf16(const GemmDesc& d, int* status, cudaStream_t stream) {
@@ -1268,6 +1312,8 @@ static cudaError_t launch_mx(const GemmDesc& d, const MxScales& sf, int* status,
   a.m_blocks = (d.M + BM - 1) / BM;
   a.n_blocks = (d.N + BN - 1) / BN;
   a.group_m = group_m_override(16);
+  a.symmetric = 0;
+  a.tiles_per_batch = a.m_blocks * a.n_blocks;
   a.idesc = umma_idesc_mxf8(BM, BN, d.a_e5m2, d.b_e5m2, 0, 0);
   a.status = status;
   MxKernelScales ks;

@@ -38,7 +38,14 @@ struct GemmDesc {
   int a_e5m2 = 0, b_e5m2 = 0;
   // CTA-pair kernel (256 x BN tiles on two SMs): 1 = use it, 0 = never, -1 = let the library decide
   int pair = -1;
+  // 1 = the product is symmetric by construction (X X^T, A A with A symmetric; M == N): only the square tiles on and
+  // above the diagonal are computed (57 % of them at 1664 / 256) and the part of C below those tiles is left untouched;
+  // `symmetrize_bf16` then copies the upper triangle over the lower one.
+  int symmetric = 0;
 };
+
+// C[b][j][i] = C[b][i][j] for j > i: bf16 (batch, n, n) with row pitch ld and batch stride bs (elements).
+cudaError_t symmetrize_bf16(void* C, int n, long long ld, long long bs, int batch, cudaStream_t stream);
 
 cudaError_t gemm_bf16(const GemmDesc& d, int* status, cudaStream_t stream);
 

@@ -23,6 +23,7 @@ every function here is `ops/reference.py`.
 """
 
 import itertools
+import os
 import math
 import weakref
 
@@ -133,11 +134,15 @@ def mark_shadow_fresh(w):
 # -------------------------------------------------------------------------------- GEMM
 
 def gemm(A, B, out, *, a_mn=False, b_mn=False, aux=None, alpha=1.0, beta=0.0, epi=EPI_LINEAR, bn=0, pair=-1,
-         scale_a=None, scale_b=None, amax_out=None):
+         scale_a=None, scale_b=None, amax_out=None, symmetric=False):
     """out = epilogue(alpha * A @ B^T, aux); see csrc/gemm.h for the operand conventions. A and B are bf16, or
     both 8-bit floats with optional device-scalar scales (multiplied into alpha by the kernel). `pair` selects
-    the CTA-pair kernel (1), the single-CTA kernel (0) or the library's choice (-1)."""
-    _C.gemm(A, B, out, aux, a_mn, b_mn, alpha, beta, epi, bn, pair, scale_a, scale_b, amax_out)
+    the CTA-pair kernel (1), the single-CTA kernel (0) or the library's choice (-1). symmetric=True: the product is
+    symmetric by construction; only the tiles on and above the diagonal are computed and the upper triangle is then
+    copied over the lower one."""
+    _C.gemm(A, B, out, aux, a_mn, b_mn, alpha, beta, epi, bn, pair, scale_a, scale_b, amax_out, symmetric)
+    if symmetric:
+        _C.symmetrize(out)
     return out
 
 
@@ -985,15 +990,19 @@ def polar_express_native(X, ns_steps):
     A = _scratch("ns_A", (k, n, n), BF16, X.device)
     Bm = _scratch("ns_B", (k, n, n), BF16, X.device)
     Y = _scratch("ns_Y", (k, r, c), BF16, X.device)
+    # below ~1024 the skipped tiles are worth less than the extra mirror launches (512 x 1024: 0.16 -> 0.24 ms)
+    sym = n >= 1024 and os.environ.get("NANOCHAT_NS_SYMMETRIC", "1") != "0"
     cur, nxt = X, Y
     for a, b, cc in ref_ops.POLAR_EXPRESS_COEFFS[:ns_steps]:
+        # A and B are symmetric: their GEMMs compute the tiles on and above the diagonal only (reference: the XX^T
+        # kernels credited in dev/LOG.md:606 and nanochat/optim.py:147-154)
         if tall:
-            gemm(cur, cur, A, a_mn=True, b_mn=True)                  # A = X^T X
-            gemm(A, A, Bm, aux=A, alpha=cc, beta=b)                  # B = b A + c A A   (A symmetric)
+            gemm(cur, cur, A, a_mn=True, b_mn=True, symmetric=sym)   # A = X^T X
+            gemm(A, A, Bm, aux=A, alpha=cc, beta=b, symmetric=sym)   # B = b A + c A A   (A symmetric)
             gemm(cur, Bm, nxt, aux=cur, alpha=1.0, beta=a)           # X = a X + X B     (B symmetric)
         else:
-            gemm(cur, cur, A)                                        # A = X X^T
-            gemm(A, A, Bm, aux=A, alpha=cc, beta=b)
+            gemm(cur, cur, A, symmetric=sym)                         # A = X X^T
+            gemm(A, A, Bm, aux=A, alpha=cc, beta=b, symmetric=sym)
             gemm(Bm, cur, nxt, b_mn=True, aux=cur, alpha=1.0, beta=a)  # X = a X + B X
         cur, nxt = nxt, cur
     return cur

@@ -110,3 +110,28 @@ def test_gemm_amax_output(nat):
     amax = torch.zeros(1, device="cuda")
     nat.gemm(A, B, out, amax_out=amax)
     assert abs(amax.item() - out.float().abs().max().item()) <= 1e-2 * amax.item()
+
+
+@pytest.mark.parametrize("batch,n,k,tall", [(3, 640, 320, False), (2, 384, 512, False), (2, 1664, 256, False),
+                                            (2, 904, 448, True), (1, 128, 64, False)])
+def test_symmetric_output_gemm_matches_the_full_product(nat, batch, n, k, tall):
+    """X X^T (or X^T X) computed on the tiles on and above the diagonal only, then mirrored, is the full product;
+    the second Newton-Schulz product b A + c A A (auxiliary operand, alpha, beta) likewise."""
+    X = (_mk((batch, k, n) if tall else (batch, n, k), seed=5) / k ** 0.5).to(BF16)
+    kw = dict(a_mn=True, b_mn=True) if tall else {}
+    full = torch.empty(batch, n, n, dtype=BF16, device="cuda")
+    nat.gemm(X, X, full, **kw)
+    sym = torch.full((batch, n, n), float("nan"), dtype=BF16, device="cuda")   # untouched elements would show
+    nat.gemm(X, X, sym, symmetric=True, **kw)
+    nat.check_status(sym)
+    ref = X.float().transpose(1, 2) @ X.float() if tall else X.float() @ X.float().transpose(1, 2)
+    assert _rel_err(full, ref) < 1e-2
+    assert torch.equal(sym, sym.transpose(1, 2))
+    assert torch.equal(torch.triu(sym), torch.triu(full))
+    full2 = torch.empty_like(full)
+    nat.gemm(full, full, full2, aux=full, alpha=0.7, beta=-1.3)
+    sym2 = torch.full_like(full, float("nan"))
+    nat.gemm(sym, sym, sym2, aux=sym, alpha=0.7, beta=-1.3, symmetric=True)
+    nat.check_status(sym2)
+    assert not sym2.float().isnan().any()
+    assert _rel_err(sym2, full2) < 1e-2
