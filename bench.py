@@ -293,7 +293,8 @@ def run_ours(args):
         for p in model.transformer.h.parameters():
             if p.dim() == 2 and min(p.shape) >= 8:
                 n, m = min(p.shape), max(p.shape)
-                ns_flops += 5 * (2.0 * n * n * m + 2.0 * n ** 3 + 2.0 * n * n * m)
+                # X X^T and A A are symmetric: half of their 2 n^2 m and 2 n^3 FLOPs are needed; B X is not
+                ns_flops += 5 * (1.0 * n * n * m + 1.0 * n ** 3 + 2.0 * n * n * m)
         bytes_in = (world - 1) / world * n_all * 4          # fp32 gradient slices arriving from the peers: pushed by
         #                                                     the last micro-batch's backward pass, outside the update
         bytes_out = (world - 1) / world * n_all * 2         # bf16 parameters stored to the peers by the update kernels
