@@ -135,3 +135,34 @@ def test_symmetric_output_gemm_matches_the_full_product(nat, batch, n, k, tall):
     nat.check_status(sym2)
     assert not sym2.float().isnan().any()
     assert _rel_err(sym2, full2) < 1e-2
+
+
+@pytest.mark.parametrize("pair", [0, 1])
+@pytest.mark.parametrize("b_mn", [False, True])
+@pytest.mark.parametrize("M,N,K,bn", [(512, 416, 192, 208), (768, 512, 128, 256), (600, 1664, 256, 208), (384, 384, 64, 128)])
+def test_fused_epilogues_with_an_auxiliary_operand(nat, M, N, K, bn, b_mn, pair):
+    """Residual add, relu, multiply-by-auxiliary and 2 sqrt(auxiliary): the kernels that request the auxiliary tile
+    ahead of its use (forward and activation-gradient layouts, 256 / 208 / 128-wide tiles), in place and out of place."""
+    A = (_mk((M, K), seed=11) / K ** 0.5).to(BF16)
+    B = _mk((K, N) if b_mn else (N, K), seed=12).to(BF16)
+    aux = _mk((M, N), seed=13).abs().to(BF16)
+    prod = A.float() @ (B.float() if b_mn else B.float().t())
+    kw = dict(b_mn=b_mn, bn=bn, pair=pair)
+    cases = {
+        "residual": (dict(aux=aux, beta=0.5, alpha=1.5), 1.5 * prod + 0.5 * aux.float()),
+        "mulaux": (dict(aux=aux, epi=nat.EPI_MULAUX, alpha=2.0), 2.0 * prod * aux.float()),
+        "mul2sqrt": (dict(aux=aux, epi=nat.EPI_MUL2SQRT), prod * 2.0 * aux.float().sqrt()),
+        "relu": (dict(epi=nat.EPI_RELU), prod.clamp_min(0)),
+        "relu2": (dict(epi=nat.EPI_RELU2), prod.clamp_min(0) ** 2),
+    }
+    for name, (extra, want) in cases.items():
+        C = torch.empty(M, N, dtype=BF16, device="cuda")
+        amax = torch.zeros(1, device="cuda")
+        nat.gemm(A, B, C, amax_out=amax, **kw, **extra)
+        nat.check_status(C)
+        assert _rel_err(C, want) < 1e-2, name
+        assert abs(amax.item() - C.float().abs().max().item()) <= 1e-2 * amax.item() + 1e-6, name
+    inplace = aux.clone()                                   # accumulate into the auxiliary operand itself
+    nat.gemm(A, B, inplace, aux=inplace, beta=1.0, **kw)
+    nat.check_status(inplace)
+    assert _rel_err(inplace, prod + aux.float()) < 1e-2
