@@ -15,9 +15,12 @@ namespace nc {
 constexpr int CE_THREADS = 256;
 
 __device__ __forceinline__ float softcap(float l, float cap, float inv_cap) {
-  // cap * tanh(l/cap) via one exp: tanh(u) = 1 - 2/(exp(2u)+1)
-  const float e = __expf(2.f * l * inv_cap);
-  return cap * (1.f - __fdividef(2.f, e + 1.f));
+  // cap * tanh(l/cap) with the hardware tanh (one MUFU instruction instead of an exp and a reciprocal; both CE kernels
+  // are bound by that unit). Its relative error of about 2^-11 moves a capped logit by at most 0.007, a tenth of the
+  // bf16 rounding the logits already carry.
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(l * inv_cap));
+  return cap * t;
 }
 
 __device__ __forceinline__ float block_sum(float v, float* smem) {
