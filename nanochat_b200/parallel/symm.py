@@ -306,12 +306,13 @@ class SymmComm:
 
     @torch.no_grad()
     def fused_step(self, opt):
-        """Two streams between two device barriers. The LINK stream pulls: first the gradients of each Muon group
-        (averaged into the momentum kernel), then the reduce + AdamW + write-back kernels of the embedding tables
-        and lm_head; its kernels are NVLink-bound and run on a capped number of small CTAs. The COMPUTE stream (the
-        caller's) orthogonalises each Muon group on the tensor cores as soon as that group's pull has landed and
-        stores the updated bf16 matrices to every rank from the update kernel itself. So the Newton-Schulz GEMMs of
-        one group run while the next groups' gradients and the AdamW traffic cross NVLink."""
+        """The whole sharded update between two device barriers. The gradients are already in their owners' staging
+        slots (pushed by the last micro-batch's weight-gradient GEMM epilogues and by the table copy kernels), so
+        after the first barrier everything reads local memory: per Muon group the owner sums its W slots inside the
+        momentum kernel, orthogonalises the stack on the tensor cores and stores the updated bf16 matrices to every
+        rank from the update kernel; the AdamW kernels do the same for the row-sharded tables and lm_head. With
+        `self.overlap` (off by default: measured no gain) the slot sums and AdamW kernels run on a second stream
+        beside the Newton-Schulz GEMMs; otherwise everything is issued on the caller's stream."""
         C = self.nat._C
         gp, bp = self.grad_pool, self.bf16_pool
         tr = self.trace
