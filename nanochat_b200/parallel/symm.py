@@ -21,10 +21,10 @@ result does not depend on timing).
 All-gather = the update kernels' write-back: AdamW (`p2p_adamw`) and the Muon update
 (`p2p_muon_apply`) store the new bf16 values into every rank's shadow / table from registers.
 
-A step is bracketed by two device-side barriers (bounded waits, status word). Between them two
-streams run: the link stream sums + updates + writes back the AdamW tensors (NVLink-store bound,
-capped number of small CTAs) while the caller's stream orthogonalises the Muon groups on the tensor
-cores. The fp32 masters stay with their owners; `sync_masters()` makes every replica's masters
+A step is bracketed by two device-side barriers (bounded waits, status word). Between them the slot
+sums, AdamW updates and write-backs and the Muon groups' Newton-Schulz GEMMs run on the caller's stream
+(NANOCHAT_OPT_OVERLAP=1 moves the memory-bound kernels to a second stream with a capped number of CTAs;
+measured at 2 and 4 GPUs it gains nothing, so it is off by default). The fp32 masters stay with their owners; `sync_masters()` makes every replica's masters
 consistent on demand (checkpointing), using NCCL broadcasts since that is rare and off the hot path.
 
 If a step's gradients were not produced through that last-micro-batch path (a driver that calls
