@@ -287,13 +287,26 @@ qkv_post_fwd_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, int H, int Hk
 #pragma unroll
       for (int j = 0; j < 8; ++j) s[j] = tmp[j];
     }
+    // The update is in place, so the compiler may not move an item's loads above the previous item's stores; the next
+    // item's two 16-byte pieces are requested by hand before the current item is worked on (every item lives at
+    // row + item * 128, rotary heads and value heads alike).
+    uint4 na = make_uint4(0, 0, 0, 0), nb = na;
+    if (grp < n_items) {
+      na = *(reinterpret_cast<const uint4*>(row + (size_t)grp * 128) + sub);
+      nb = *(reinterpret_cast<const uint4*>(row + (size_t)grp * 128) + 8 + sub);
+    }
     for (int base = 0; base < n_items; base += 4) {
       const int item = base + grp;
+      const uint4 ca = na, cb = nb;
+      if (item + 4 < n_items) {
+        na = *(reinterpret_cast<const uint4*>(row + (size_t)(item + 4) * 128) + sub);
+        nb = *(reinterpret_cast<const uint4*>(row + (size_t)(item + 4) * 128) + 8 + sub);
+      }
       if (item < n_rot) {
         __nv_bfloat16* h = row + (size_t)item * 128;
         float a[8], b[8];
-        unpack8(*(reinterpret_cast<const uint4*>(h) + sub), a);
-        unpack8(*(reinterpret_cast<const uint4*>(h) + 8 + sub), b);
+        unpack8(ca, a);
+        unpack8(cb, b);
         float ss = 0.f;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -319,8 +332,8 @@ qkv_post_fwd_kernel(__nv_bfloat16* __restrict__ qkv, long long ld, int H, int Hk
         const float gate = bf16_round(3.f * bf16_round(1.f / (1.f + __expf(-z))));
         const __nv_bfloat16* e = ve + (size_t)idx[tok] * (Hkv * 128) + hv * 128;
         float a[8], b[8], ea[8], eb[8];
-        unpack8(*(reinterpret_cast<const uint4*>(h) + sub), a);
-        unpack8(*(reinterpret_cast<const uint4*>(h) + 8 + sub), b);
+        unpack8(ca, a);
+        unpack8(cb, b);
         unpack8(__ldg(reinterpret_cast<const uint4*>(e) + sub), ea);
         unpack8(__ldg(reinterpret_cast<const uint4*>(e) + 8 + sub), eb);
 #pragma unroll
@@ -361,16 +374,35 @@ qkv_post_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __res
     float c[8], s[8];
     unpack8(__ldg(reinterpret_cast<const uint4*>(cos_t + (size_t)t * 64) + sub), c);
     unpack8(__ldg(reinterpret_cast<const uint4*>(sin_t + (size_t)t * 64) + sub), s);
+    // in place on dqkv: the next item's gradient pieces (and, for rotary heads, its forward outputs) are requested
+    // before the current item's results are stored (see the forward kernel)
+    uint4 nga = make_uint4(0, 0, 0, 0), ngb = nga, nya = nga, nyb = nga;
+    if (grp < n_items) {
+      nga = *(reinterpret_cast<const uint4*>(drow + (size_t)grp * 128) + sub);
+      ngb = *(reinterpret_cast<const uint4*>(drow + (size_t)grp * 128) + 8 + sub);
+      if (grp < n_rot) {
+        nya = *(reinterpret_cast<const uint4*>(row + (size_t)grp * 128) + sub);
+        nyb = *(reinterpret_cast<const uint4*>(row + (size_t)grp * 128) + 8 + sub);
+      }
+    }
     for (int base = 0; base < n_items; base += 4) {
       const int item = base + grp;
+      const uint4 cga = nga, cgb = ngb, cya = nya, cyb = nyb;
+      if (item + 4 < n_items) {
+        nga = *(reinterpret_cast<const uint4*>(drow + (size_t)(item + 4) * 128) + sub);
+        ngb = *(reinterpret_cast<const uint4*>(drow + (size_t)(item + 4) * 128) + 8 + sub);
+        if (item + 4 < n_rot) {
+          nya = *(reinterpret_cast<const uint4*>(row + (size_t)(item + 4) * 128) + sub);
+          nyb = *(reinterpret_cast<const uint4*>(row + (size_t)(item + 4) * 128) + 8 + sub);
+        }
+      }
       if (item < n_rot) {
-        const __nv_bfloat16* h = row + (size_t)item * 128;
         __nv_bfloat16* dh = drow + (size_t)item * 128;
         float ya[8], yb[8], ga[8], gb[8];
-        unpack8(*(reinterpret_cast<const uint4*>(h) + sub), ya);
-        unpack8(*(reinterpret_cast<const uint4*>(h) + 8 + sub), yb);
-        unpack8(*(reinterpret_cast<const uint4*>(dh) + sub), ga);
-        unpack8(*(reinterpret_cast<const uint4*>(dh) + 8 + sub), gb);
+        unpack8(cya, ya);
+        unpack8(cyb, yb);
+        unpack8(cga, ga);
+        unpack8(cgb, gb);
         const float rstd = rstd_in[(size_t)tok * n_rot + item];
         float dot = 0.f;
 #pragma unroll
@@ -392,14 +424,13 @@ qkv_post_bwd_kernel(__nv_bfloat16* __restrict__ dqkv, const __nv_bfloat16* __res
         *(reinterpret_cast<uint4*>(dh) + 8 + sub) = pack8(gb);
       } else if (item < n_items) {
         const int hv = item - n_rot;
-        const __nv_bfloat16* dh = drow + (size_t)(n_rot + hv) * 128;
         const float z = ve_gate_value(xn + (size_t)tok * ld_xn, wg + hv * 12);
         const float sg = 1.f / (1.f + __expf(-z));
         const float gate = 3.f * sg;
         const size_t erow = (size_t)idx[tok] * (Hkv * 128) + hv * 128;
         float ga[8], gb[8], ea[8], eb[8];
-        unpack8(*(reinterpret_cast<const uint4*>(dh) + sub), ga);
-        unpack8(*(reinterpret_cast<const uint4*>(dh) + 8 + sub), gb);
+        unpack8(cga, ga);
+        unpack8(cgb, gb);
         unpack8(__ldg(reinterpret_cast<const uint4*>(ve + erow) + sub), ea);
         unpack8(__ldg(reinterpret_cast<const uint4*>(ve + erow) + 8 + sub), eb);
         float dg = 0.f;
