@@ -19,7 +19,7 @@ namespace nc {
 constexpr int ROW_WARPS = 4;  // warps (rows in flight) per CTA
 
 template <int NV>
-__global__ void __launch_bounds__(ROW_WARPS * 32)
+__global__ void __launch_bounds__(ROW_WARPS * 32, 6)
 mixnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ x0,
                    const float* __restrict__ lam_r, const float* __restrict__ lam_0, int layer,
                    __nv_bfloat16* __restrict__ xm, __nv_bfloat16* __restrict__ xn, float* __restrict__ amax_xn,
