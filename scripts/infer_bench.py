@@ -35,24 +35,30 @@ def weight_bytes(model):
 
 def bench_generate(engine, prompt_tokens, batch_size, decode_tokens, temperature, top_k=None):
     device = engine.model.get_device()
-    gc.collect()                     # a cyclic collection landing inside the first-token timing reads as 0.1-0.4 s of TTFT
-    torch.cuda.reset_peak_memory_stats(device)
-    torch.cuda.synchronize(device)
-    gen = engine.generate(prompt_tokens, num_samples=batch_size, max_tokens=decode_tokens,
-                          temperature=temperature, top_k=top_k)
-    t0 = time.perf_counter()
-    next(gen)
-    torch.cuda.synchronize(device)
-    ttft = time.perf_counter() - t0
-    steps = []
-    while True:
-        t0 = time.perf_counter()
-        try:
-            next(gen)
-        except StopIteration:
-            break
+    # A cyclic collection landing inside a timed call reads as 0.1-0.5 s of TTFT or of one decode step (seen at batch 64,
+    # where it halved the reported tokens/s): collect first, then keep the collector off for the timed generation.
+    gc.collect()
+    gc.disable()
+    try:
+        torch.cuda.reset_peak_memory_stats(device)
         torch.cuda.synchronize(device)
-        steps.append(time.perf_counter() - t0)
+        gen = engine.generate(prompt_tokens, num_samples=batch_size, max_tokens=decode_tokens,
+                              temperature=temperature, top_k=top_k)
+        t0 = time.perf_counter()
+        next(gen)
+        torch.cuda.synchronize(device)
+        ttft = time.perf_counter() - t0
+        steps = []
+        while True:
+            t0 = time.perf_counter()
+            try:
+                next(gen)
+            except StopIteration:
+                break
+            torch.cuda.synchronize(device)
+            steps.append(time.perf_counter() - t0)
+    finally:
+        gc.enable()
     return dict(ttft=ttft, step_times=steps, peak_vram=torch.cuda.max_memory_allocated(device))
 
 
