@@ -116,18 +116,26 @@ def dist_env():
 
 
 def timed_region(torch, dist, world, steps, run_step):
-    """Times `steps` calls of run_step() on the device; returns the max over ranks in milliseconds."""
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(steps):
-        run_step()
-    t1.record()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
+    """Times `steps` calls of run_step() on the device; returns the max over ranks in milliseconds. The cyclic
+    garbage collector is kept off inside the region, in both arms, as the reference's training loop does after its
+    first step (scripts/base_train.py:588-594 there): a collection pausing one rank's host thread stalls every rank."""
+    import gc
+    gc.collect()
+    gc.disable()
+    try:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            run_step()
+        t1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+    finally:
+        gc.enable()
     ms = torch.tensor([t0.elapsed_time(t1)], device="cuda", dtype=torch.float64)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
