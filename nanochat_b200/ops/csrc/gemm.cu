@@ -187,7 +187,6 @@ __device__ __forceinline__ void store_tile_row(const GemmKernelArgs& args, uint3
 // (residual, relu^2 derivative input) comes in the same way, through the same tile.
 constexpr int EPI_STAGE_BYTES = 32 * 128;          // per epilogue warp
 
-//
 // The auxiliary loads run one group ahead of their use: the 32 x 128 B of the NEXT group (of this tile, or the first group
 // of the warp's next tile) are requested into registers before the current group is converted, so their DRAM latency
 // passes under the tensor-memory reads, the conversion and the stores instead of in front of them. With a short reduction
